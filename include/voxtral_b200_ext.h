@@ -1,0 +1,80 @@
+/*
+ * voxtral_b200_ext.h - additions to the reference-compatible ABI.
+ *
+ * None of these has a counterpart in mudler/voxtral-tts.c. They exist so that a
+ * replacement for the reference's decoder / acoustic stages can run a whole
+ * audio frame in one launch instead of 15 host round trips, and so that tests
+ * and benchmarks can reach state the reference keeps private. The
+ * reference-compatible surface in voxtral_b200.h is unaffected.
+ *
+ * All pointers are host memory unless named d_*. Calls return 0 on success and
+ * a negative value on failure; vb200_last_status() gives the device status word
+ * (0 = fine) of the most recent launch.
+ */
+#ifndef VOXTRAL_B200_EXT_H
+#define VOXTRAL_B200_EXT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One whole frame as the orchestrator's loop body runs it
+ * (voxtral_tts.c:301-318): decoder step on `embed` at cache row `pos`, then
+ * semantic argmax, 7 Euler steps with both guidance branches batched, FSQ.
+ * noise36: the 36 normals tts_randn_fill would draw for this frame
+ * (voxtral_tts_acoustic.c:329); the caller owns the RNG and advances it only if
+ * codes[0] != 1, which reproduces the reference's "END frame draws nothing".
+ * hidden_out (3072, optional) receives the decoder output. */
+int vb200_frame(const float *embed, const float *noise36, int pos, float *hidden_out, int *codes37);
+
+/* The acoustic half alone (tts_acoustic_forward, voxtral_tts_acoustic.c:268-373)
+ * on a host hidden state. latent_out (36, optional): latent before quantisation. */
+int vb200_acoustic_frame(const float *llm_hidden, const float *noise36, int *codes37,
+                         float *latent_out);
+
+/* Same as vb200_frame, but the next decoder input is taken from the previous
+ * frame's codes on the device (sum of the 37 codebook rows,
+ * voxtral_tts_voice.c:292-315); needs vb200_upload_audio_embed first. */
+int vb200_frame_chained(const float *noise36, int pos, float *hidden_out, int *codes37);
+int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows);
+
+/* Copy rows [pos0, pos0+n) of one layer's K and V cache to / from the host
+ * ([n, 1024] fp32 each), e.g. to pre-fill a cache prefix. */
+int vb200_kv_write(int layer, int pos0, int n, const float *k_rows, const float *v_rows);
+int vb200_kv_read(int layer, int pos0, int n, float *k_rows, float *v_rows);
+
+/* Residual-stream tap for per-layer parity checks: when enabled, every decode
+ * step also stores the stream after attention and after the FFN of each layer.
+ * vb200_tap_read copies [26, 2, 3072] floats. */
+int vb200_tap_enable(int on);
+int vb200_tap_read(float *out);
+
+/* How the frame kernel splits a [N,K] matrix product with M activation rows
+ * over `n_cta` CTAs (host logic, usable without a GPU). out[0..6] = first row,
+ * end row, column passes, columns per pass, rows per chunk, row blocks, chunks of
+ * CTA `cta`; the return value is 0 when the shape is runnable, negative if not. */
+int vb200_debug_gemv_plan(int N, int K, int M, int swiglu, int cta, int n_cta, int *out);
+
+int vb200_last_status(void);
+int vb200_sm_count(void);
+/* Average device time, in milliseconds, of the engine launches since the last
+ * call with reset != 0 (CUDA events on the library's stream); n receives the
+ * number of launches averaged. */
+double vb200_engine_ms(int reset, int *n);
+
+/* Deterministic synthetic tensors (integer hash -> sum of 16 uniform bytes ->
+ * approximately normal), identical on every machine. value = mean + sigma * z.
+ * `stream` separates tensors (e.g. a CRC of the tensor name); `first` is the
+ * index of dst[0] inside the tensor, so rows can be produced on demand. */
+void vb200_synth_bf16(uint16_t *dst, size_t n, uint64_t seed, uint64_t stream, uint64_t first,
+                      float sigma);
+void vb200_synth_f32(float *dst, size_t n, uint64_t seed, uint64_t stream, uint64_t first,
+                     float mean, float sigma);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,45 @@
+"""Seeded inputs of the parity cases, shared by the golden generator and the tests.
+
+They follow BASELINE.json's configs: config 1 = one decoder step with a cache
+pre-filled with 64 positions of N(0,1); config 2 = one acoustic frame on a
+N(0,1) hidden state."""
+import numpy as np
+
+MODEL_SEED = 1234
+INPUT_SEED = 7
+
+
+def config1_inputs(pkg):
+    embed = pkg.synth_f32(3072, INPUT_SEED, "cfg1.embed")
+    kvk = pkg.synth_f32((26, 64, 1024), INPUT_SEED, "cfg1.kv_k")
+    kvv = pkg.synth_f32((26, 64, 1024), INPUT_SEED, "cfg1.kv_v")
+    return embed, kvk, kvv
+
+
+def config2_inputs(pkg):
+    return pkg.synth_f32(3072, INPUT_SEED, "cfg2.hidden"), 42
+
+
+def frames_inputs(pkg):
+    first = pkg.synth_f32(3072, INPUT_SEED, "frames.embed", 0.0, 0.02)
+    kvk = pkg.synth_f32((26, 5, 1024), INPUT_SEED, "frames.kv_k")
+    kvv = pkg.synth_f32((26, 5, 1024), INPUT_SEED, "frames.kv_v")
+    return first, kvk, kvv, 99, 3
+
+
+def primitive_inputs(pkg):
+    s = INPUT_SEED
+    return {
+        "x1": pkg.synth_f32(512, s, "prim.x1"),
+        "x3": pkg.synth_f32((3, 512), s, "prim.x3"),
+        "W": pkg.synth_bf16((96, 512), s, "prim.W"),
+        "bias": pkg.synth_f32(96, s, "prim.bias"),
+        "gain": pkg.synth_f32(512, s, "prim.gain", 1.0, 0.1),
+        "q": pkg.synth_f32(32 * 128, s, "prim.q", 0.0, 0.1),
+        "q3": pkg.synth_f32((3, 32 * 128), s, "prim.q3", 0.0, 0.1),
+        "k": pkg.synth_f32((225, 8 * 128), s, "prim.k", 0.0, 0.1),
+        "v": pkg.synth_f32((225, 8 * 128), s, "prim.v", 0.0, 0.1),
+        "rope_x": pkg.synth_f32((4, 8 * 128), s, "prim.rope_x"),
+        "gate": pkg.synth_f32(1024, s, "prim.gate"),
+        "up": pkg.synth_f32(1024, s, "prim.up"),
+    }

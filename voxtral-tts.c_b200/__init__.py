@@ -1,0 +1,378 @@
+"""Host-side binding of libvoxtral_b200.so for tests and benchmarks.
+
+The product is the C-ABI shared library (include/voxtral_b200.h and
+include/voxtral_b200_ext.h). This module only loads it with ctypes and mirrors
+the reference's call sequence (tts_cuda_init -> upload -> forward calls) in
+Python. There is no fallback: a missing library or a missing sm_100 GPU raises.
+
+The directory name is not a valid Python identifier; load it with
+importlib (see tests/conftest.py: load_package()).
+"""
+import ctypes as C
+import os
+import zlib
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libvoxtral_b200.so")
+
+DIM, DEC_LAYERS, AC_LAYERS = 3072, 26, 3
+HEADS, KV_HEADS, HEAD_DIM, HIDDEN = 32, 8, 128, 9216
+Q_DIM, KV_DIM = HEADS * HEAD_DIM, KV_HEADS * HEAD_DIM
+VOCAB, ACOUSTIC_DIM, SEM_PADDED, SEM_VALID_END = 131072, 36, 8320, 8194
+FLOW_STEPS, FSQ_LEVELS, CODES, CODE_END = 8, 21, 37, 1
+AUDIO_ROWS = 8194 + 36 * 23
+NORM_EPS, ROPE_THETA, CFG_ALPHA = 1e-5, 1e6, 1.2
+
+u16p = C.POINTER(C.c_uint16)
+f32p = C.POINTER(C.c_float)
+i32p = C.POINTER(C.c_int)
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [("wq", u16p), ("wk", u16p), ("wv", u16p), ("wo", u16p), ("attention_norm", f32p),
+                ("w1", u16p), ("w2", u16p), ("w3", u16p), ("ffn_norm", f32p)]
+
+
+class DecoderWeights(C.Structure):
+    _fields_ = [("tok_embeddings", u16p), ("layers", LayerWeights * DEC_LAYERS), ("norm", f32p)]
+
+
+class AcousticWeights(C.Structure):
+    _fields_ = [("time_inv_freq", f32p), ("input_proj", u16p), ("time_proj", u16p), ("llm_proj", u16p),
+                ("semantic_out", u16p), ("semantic_out_bias", f32p), ("acoustic_out", u16p), ("norm", f32p),
+                ("layers", LayerWeights * AC_LAYERS)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library. Raises when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing: run `python voxtral-tts.c_b200/build.py` "
+                           "(there is no CPU fallback)")
+    L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    sig = {
+        "tts_cuda_init": (C.c_int, [C.c_int]),
+        "tts_cuda_upload_llm_weights": (C.c_int, [C.c_void_p]),
+        "tts_cuda_upload_acoustic_weights": (C.c_int, [C.c_void_p]),
+        "tts_cuda_free": (None, []),
+        "tts_cuda_available": (C.c_int, []),
+        "tts_cuda_linear_bf16": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+        "tts_cuda_rms_norm": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float]),
+        "tts_cuda_apply_rope": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+        "tts_cuda_compute_rope_freqs": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float]),
+        "tts_cuda_silu_mul": (None, [C.c_void_p, C.c_void_p, C.c_int]),
+        "tts_cuda_add_inplace": (None, [C.c_void_p, C.c_void_p, C.c_int]),
+        "tts_cuda_causal_attention_decode": (None, [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float, C.c_int]),
+        "tts_cuda_causal_attention_prefill": (None, [C.c_void_p] * 4 + [C.c_int] * 5 + [C.c_float]),
+        "tts_cuda_bidirectional_attention": (None, [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float]),
+        "tts_cuda_embed_token": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+        "tts_cuda_llm_forward": (None, [C.c_void_p, C.c_void_p, C.c_int]),
+        "tts_cuda_llm_prefill": (None, [C.c_void_p, C.c_int, C.c_int]),
+        "tts_cuda_predict_velocity": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float]),
+        "tts_cuda_to_device": (None, [C.c_void_p, C.c_void_p, C.c_size_t]),
+        "tts_cuda_to_host": (None, [C.c_void_p, C.c_void_p, C.c_size_t]),
+        "tts_cuda_memset": (None, [C.c_void_p, C.c_int, C.c_size_t]),
+        "tts_cuda_alloc": (C.c_void_p, [C.c_size_t]),
+        "tts_cuda_free_ptr": (None, [C.c_void_p]),
+        "tts_cuda_sync": (None, []),
+        "vb200_frame": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+        "vb200_frame_chained": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+        "vb200_acoustic_frame": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+        "vb200_upload_audio_embed": (C.c_int, [C.c_void_p, C.c_int]),
+        "vb200_kv_write": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+        "vb200_kv_read": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+        "vb200_tap_enable": (C.c_int, [C.c_int]),
+        "vb200_tap_read": (C.c_int, [C.c_void_p]),
+        "vb200_debug_gemv_plan": (C.c_int, [C.c_int] * 6 + [i32p]),
+        "vb200_last_status": (C.c_int, []),
+        "vb200_sm_count": (C.c_int, []),
+        "vb200_engine_ms": (C.c_double, [C.c_int, i32p]),
+        "vb200_synth_bf16": (None, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float]),
+        "vb200_synth_f32": (None, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_float]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+EXPORTED_SYMBOLS_REFERENCE = [
+    "g_cuda", "tts_cuda_init", "tts_cuda_upload_llm_weights", "tts_cuda_upload_acoustic_weights",
+    "tts_cuda_free", "tts_cuda_available", "tts_cuda_linear_bf16", "tts_cuda_rms_norm", "tts_cuda_apply_rope",
+    "tts_cuda_compute_rope_freqs", "tts_cuda_silu_mul", "tts_cuda_add_inplace",
+    "tts_cuda_causal_attention_decode", "tts_cuda_causal_attention_prefill",
+    "tts_cuda_bidirectional_attention", "tts_cuda_embed_token", "tts_cuda_llm_forward", "tts_cuda_llm_prefill",
+    "tts_cuda_predict_velocity", "tts_cuda_to_device", "tts_cuda_to_host", "tts_cuda_memset", "tts_cuda_alloc",
+    "tts_cuda_free_ptr", "tts_cuda_sync",
+]
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# --------------------------------------------------------------------------
+# synthetic checkpoint (stands in for the real weights, which need the network)
+# --------------------------------------------------------------------------
+def stream_id(name):
+    return zlib.crc32(name.encode())
+
+
+def synth_bf16(shape, seed, name, sigma=0.02, first=0):
+    out = np.empty(shape, dtype=np.uint16)
+    lib().vb200_synth_bf16(_ptr(out), out.size, seed, stream_id(name), first, sigma)
+    return out
+
+
+def synth_f32(shape, seed, name, mean=0.0, sigma=1.0, first=0):
+    out = np.empty(shape, dtype=np.float32)
+    lib().vb200_synth_f32(_ptr(out), out.size, seed, stream_id(name), first, mean, sigma)
+    return out
+
+
+class SynthModel:
+    """Seeded random-init weights with the tensor names and shapes of the real
+    checkpoint (voxtral_tts_llm.c:50-95, voxtral_tts_acoustic.c:48-111,
+    voxtral_tts_voice.c:257-283). Matrices: BF16 ~N(0, 0.02). Norm gains:
+    1 + N(0, 0.02). The 131072-row token table is produced row by row on demand."""
+
+    def __init__(self, seed=1234, decoder=True, acoustic=True, semantic_bias=False, audio_table=True,
+                 dec_layers=DEC_LAYERS):
+        self.seed = seed
+        self.t = {}
+        self.dec_layers = dec_layers
+        if decoder:
+            for i in range(DEC_LAYERS):
+                # layers beyond dec_layers alias layer 0 (small-memory smoke runs only)
+                src = i if i < dec_layers else 0
+                self._layer(f"layers.{i}", f"layers.{src}")
+            self.t["norm.weight"] = synth_f32(DIM, seed, "norm.weight", 1.0, 0.02)
+        if acoustic:
+            p = "acoustic_transformer"
+            for i in range(AC_LAYERS):
+                self._layer(f"{p}.layers.{i}", f"{p}.layers.{i}")
+            self.t[f"{p}.input_projection.weight"] = synth_bf16((DIM, ACOUSTIC_DIM), seed, f"{p}.input_projection.weight")
+            self.t[f"{p}.time_projection.weight"] = synth_bf16((DIM, DIM), seed, f"{p}.time_projection.weight")
+            self.t[f"{p}.llm_projection.weight"] = synth_bf16((DIM, DIM), seed, f"{p}.llm_projection.weight")
+            self.t[f"{p}.semantic_codebook_output.weight"] = synth_bf16(
+                (SEM_PADDED, DIM), seed, f"{p}.semantic_codebook_output.weight")
+            self.t[f"{p}.acoustic_codebook_output.weight"] = synth_bf16(
+                (ACOUSTIC_DIM, DIM), seed, f"{p}.acoustic_codebook_output.weight")
+            self.t[f"{p}.norm.weight"] = synth_f32(DIM, seed, f"{p}.norm.weight", 1.0, 0.02)
+            if semantic_bias:
+                self.t[f"{p}.semantic_codebook_output.bias"] = synth_f32(
+                    SEM_PADDED, seed, f"{p}.semantic_codebook_output.bias", 0.0, 0.5)
+            # exp(-ln(10000) * i / 1536) in fp32, voxtral_tts_acoustic.c:49-57
+            i = np.arange(DIM // 2, dtype=np.float32)
+            theta = np.float32(10000.0)
+            self.t[f"{p}.time_embedding.inv_freq"] = np.exp(
+                (-np.log(theta, dtype=np.float32) * i / np.float32(DIM // 2)).astype(np.float32)).astype(np.float32)
+        if audio_table:
+            n = "mm_audio_embeddings.audio_codebook_embeddings.embeddings.weight"
+            self.t[n] = synth_bf16((AUDIO_ROWS, DIM), seed, n)
+
+    def _layer(self, name, src):
+        s = self.seed
+        if src != name:
+            for k in ("attention.wq", "attention.wk", "attention.wv", "attention.wo", "feed_forward.w1",
+                      "feed_forward.w2", "feed_forward.w3", "attention_norm", "ffn_norm"):
+                self.t[f"{name}.{k}.weight"] = self.t[f"{src}.{k}.weight"]
+            return
+        self.t[f"{name}.attention.wq.weight"] = synth_bf16((Q_DIM, DIM), s, f"{name}.attention.wq.weight")
+        self.t[f"{name}.attention.wk.weight"] = synth_bf16((KV_DIM, DIM), s, f"{name}.attention.wk.weight")
+        self.t[f"{name}.attention.wv.weight"] = synth_bf16((KV_DIM, DIM), s, f"{name}.attention.wv.weight")
+        self.t[f"{name}.attention.wo.weight"] = synth_bf16((DIM, Q_DIM), s, f"{name}.attention.wo.weight")
+        self.t[f"{name}.feed_forward.w1.weight"] = synth_bf16((HIDDEN, DIM), s, f"{name}.feed_forward.w1.weight")
+        self.t[f"{name}.feed_forward.w2.weight"] = synth_bf16((DIM, HIDDEN), s, f"{name}.feed_forward.w2.weight")
+        self.t[f"{name}.feed_forward.w3.weight"] = synth_bf16((HIDDEN, DIM), s, f"{name}.feed_forward.w3.weight")
+        self.t[f"{name}.attention_norm.weight"] = synth_f32(DIM, s, f"{name}.attention_norm.weight", 1.0, 0.02)
+        self.t[f"{name}.ffn_norm.weight"] = synth_f32(DIM, s, f"{name}.ffn_norm.weight", 1.0, 0.02)
+
+    def token_rows(self, ids):
+        """fp32 embedding rows of the token table (tts_embed_token_bf16,
+        voxtral_tts_kernels.c:55-59) for the given ids."""
+        out = np.empty((len(ids), DIM), dtype=np.float32)
+        name = "mm_audio_embeddings.tok_embeddings.weight"
+        for r, tid in enumerate(ids):
+            row = synth_bf16(DIM, self.seed, name, first=int(tid) * DIM)
+            out[r] = (row.astype(np.uint32) << 16).view(np.float32)
+        return out
+
+    def _fill_layer(self, L, name):
+        g = self.t
+        L.wq = g[f"{name}.attention.wq.weight"].ctypes.data_as(u16p)
+        L.wk = g[f"{name}.attention.wk.weight"].ctypes.data_as(u16p)
+        L.wv = g[f"{name}.attention.wv.weight"].ctypes.data_as(u16p)
+        L.wo = g[f"{name}.attention.wo.weight"].ctypes.data_as(u16p)
+        L.w1 = g[f"{name}.feed_forward.w1.weight"].ctypes.data_as(u16p)
+        L.w2 = g[f"{name}.feed_forward.w2.weight"].ctypes.data_as(u16p)
+        L.w3 = g[f"{name}.feed_forward.w3.weight"].ctypes.data_as(u16p)
+        L.attention_norm = g[f"{name}.attention_norm.weight"].ctypes.data_as(f32p)
+        L.ffn_norm = g[f"{name}.ffn_norm.weight"].ctypes.data_as(f32p)
+
+    def decoder_struct(self):
+        w = DecoderWeights()
+        for i in range(DEC_LAYERS):
+            self._fill_layer(w.layers[i], f"layers.{i}")
+        w.norm = self.t["norm.weight"].ctypes.data_as(f32p)
+        return w
+
+    def acoustic_struct(self):
+        p = "acoustic_transformer"
+        w = AcousticWeights()
+        g = self.t
+        w.time_inv_freq = g[f"{p}.time_embedding.inv_freq"].ctypes.data_as(f32p)
+        w.input_proj = g[f"{p}.input_projection.weight"].ctypes.data_as(u16p)
+        w.time_proj = g[f"{p}.time_projection.weight"].ctypes.data_as(u16p)
+        w.llm_proj = g[f"{p}.llm_projection.weight"].ctypes.data_as(u16p)
+        w.semantic_out = g[f"{p}.semantic_codebook_output.weight"].ctypes.data_as(u16p)
+        b = g.get(f"{p}.semantic_codebook_output.bias")
+        if b is not None:
+            w.semantic_out_bias = b.ctypes.data_as(f32p)
+        w.acoustic_out = g[f"{p}.acoustic_codebook_output.weight"].ctypes.data_as(u16p)
+        w.norm = g[f"{p}.norm.weight"].ctypes.data_as(f32p)
+        for i in range(AC_LAYERS):
+            self._fill_layer(w.layers[i], f"{p}.layers.{i}")
+        return w
+
+    def audio_table(self):
+        return self.t["mm_audio_embeddings.audio_codebook_embeddings.embeddings.weight"]
+
+
+# --------------------------------------------------------------------------
+# thin object over the C ABI (one context per process, like the reference)
+# --------------------------------------------------------------------------
+class Engine:
+    def __init__(self, kv_cache_max=512):
+        L = lib()
+        if L.tts_cuda_init(kv_cache_max) != 0:
+            raise RuntimeError("tts_cuda_init failed: an sm_100 GPU is required (no CPU fallback)")
+        self.L = L
+        self.kv_max = kv_cache_max
+        self._keep = []
+
+    def upload(self, model, decoder=True, acoustic=True, audio_table=False):
+        if decoder:
+            w = model.decoder_struct()
+            self._keep.append(w)
+            if self.L.tts_cuda_upload_llm_weights(C.byref(w)) != 0:
+                raise RuntimeError("tts_cuda_upload_llm_weights failed")
+        if acoustic:
+            w = model.acoustic_struct()
+            self._keep.append(w)
+            if self.L.tts_cuda_upload_acoustic_weights(C.byref(w)) != 0:
+                raise RuntimeError("tts_cuda_upload_acoustic_weights failed")
+        if audio_table:
+            t = model.audio_table()
+            if self.L.vb200_upload_audio_embed(_ptr(t), t.shape[0]) != 0:
+                raise RuntimeError("vb200_upload_audio_embed failed")
+
+    def _ok(self, what, rc=0):
+        if rc != 0 or self.L.vb200_last_status() != 0:
+            raise RuntimeError(f"{what} failed (rc={rc}, device status={self.L.vb200_last_status()})")
+
+    def llm_forward(self, embed, pos):
+        embed = np.ascontiguousarray(embed, dtype=np.float32)
+        out = np.empty(DIM, dtype=np.float32)
+        self.L.tts_cuda_llm_forward(_ptr(out), _ptr(embed), int(pos))
+        self._ok("tts_cuda_llm_forward")
+        return out
+
+    def prefill(self, embeds, start_pos=0):
+        embeds = np.ascontiguousarray(embeds, dtype=np.float32)
+        self.L.tts_cuda_llm_prefill(_ptr(embeds), embeds.shape[0], int(start_pos))
+        self._ok("tts_cuda_llm_prefill")
+
+    def predict_velocity(self, x_t, hidden, t):
+        x_t = np.ascontiguousarray(x_t, dtype=np.float32)
+        hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+        out = np.empty(ACOUSTIC_DIM, dtype=np.float32)
+        self.L.tts_cuda_predict_velocity(_ptr(out), _ptr(x_t), _ptr(hidden), float(t))
+        self._ok("tts_cuda_predict_velocity")
+        return out
+
+    def acoustic_frame(self, hidden, noise):
+        hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+        noise = np.ascontiguousarray(noise, dtype=np.float32)
+        codes = np.empty(CODES, dtype=np.int32)
+        latent = np.empty(ACOUSTIC_DIM, dtype=np.float32)
+        self._ok("vb200_acoustic_frame", self.L.vb200_acoustic_frame(_ptr(hidden), _ptr(noise), _ptr(codes), _ptr(latent)))
+        return codes, latent
+
+    def frame(self, embed, noise, pos, want_hidden=True):
+        noise = np.ascontiguousarray(noise, dtype=np.float32)
+        codes = np.empty(CODES, dtype=np.int32)
+        hidden = np.empty(DIM, dtype=np.float32) if want_hidden else None
+        hp = _ptr(hidden) if want_hidden else None
+        if embed is None:
+            rc = self.L.vb200_frame_chained(_ptr(noise), int(pos), hp, _ptr(codes))
+        else:
+            embed = np.ascontiguousarray(embed, dtype=np.float32)
+            rc = self.L.vb200_frame(_ptr(embed), _ptr(noise), int(pos), hp, _ptr(codes))
+        self._ok("vb200_frame", rc)
+        return codes, hidden
+
+    def kv_write(self, layer, pos0, k_rows, v_rows):
+        k_rows = np.ascontiguousarray(k_rows, dtype=np.float32)
+        v_rows = np.ascontiguousarray(v_rows, dtype=np.float32)
+        self._ok("vb200_kv_write", self.L.vb200_kv_write(layer, pos0, k_rows.shape[0], _ptr(k_rows), _ptr(v_rows)))
+
+    def kv_read(self, layer, pos0, n):
+        k = np.empty((n, KV_DIM), dtype=np.float32)
+        v = np.empty((n, KV_DIM), dtype=np.float32)
+        self._ok("vb200_kv_read", self.L.vb200_kv_read(layer, pos0, n, _ptr(k), _ptr(v)))
+        return k, v
+
+    def tap(self, on=True):
+        self._ok("vb200_tap_enable", self.L.vb200_tap_enable(1 if on else 0))
+
+    def tap_read(self):
+        out = np.empty((DEC_LAYERS, 2, DIM), dtype=np.float32)
+        self._ok("vb200_tap_read", self.L.vb200_tap_read(_ptr(out)))
+        return out
+
+    def engine_ms(self, reset=False):
+        n = C.c_int(0)
+        ms = self.L.vb200_engine_ms(1 if reset else 0, C.byref(n))
+        return ms, n.value
+
+    def close(self):
+        self.L.tts_cuda_free()
+
+
+class DeviceBuffer:
+    """A tts_cuda_alloc'd buffer (for the single-op entry points)."""
+
+    def __init__(self, array=None, nbytes=None):
+        L = lib()
+        self.L = L
+        if array is not None:
+            array = np.ascontiguousarray(array)
+            nbytes = array.nbytes
+        self.nbytes = max(int(nbytes), 4)
+        self.ptr = L.tts_cuda_alloc(self.nbytes)
+        if not self.ptr:
+            raise RuntimeError("tts_cuda_alloc failed")
+        if array is not None and array.nbytes:
+            L.tts_cuda_to_device(self.ptr, _ptr(array), array.nbytes)
+
+    def get(self, shape, dtype=np.float32):
+        out = np.empty(shape, dtype=dtype)
+        self.L.tts_cuda_sync()
+        if out.nbytes:
+            self.L.tts_cuda_to_host(_ptr(out), self.ptr, out.nbytes)
+        return out
+
+    def free(self):
+        if self.ptr:
+            self.L.tts_cuda_free_ptr(self.ptr)
+            self.ptr = None

@@ -1,0 +1,225 @@
+/*
+ * vb_abi.cu - the exported C symbols: the reference-compatible surface
+ * (include/voxtral_b200.h, names and meaning of voxtral_tts_cuda.h:82-185) and
+ * the additions of include/voxtral_b200_ext.h.
+ */
+#include "../../include/voxtral_b200.h"
+#include "../../include/voxtral_b200_ext.h"
+#include "vb_model.cuh"
+#include "vb_simple.cuh"
+
+#include <stddef.h>
+#include <stdio.h>
+#include <string.h>
+
+static_assert(sizeof(vb200_ref_cuda_ctx_t) == 2400, "must match tts_cuda_ctx_t (voxtral_tts_cuda.h:28-79)");
+static_assert(offsetof(vb200_ref_cuda_ctx_t, kv_k) == 2184, "K cache pointer offset of tts_cuda_ctx_t");
+static_assert(offsetof(vb200_ref_cuda_ctx_t, initialized) == 2396, "initialized flag offset of tts_cuda_ctx_t");
+static_assert(sizeof(vb200_layer_weights_t) == 72, "must match tts_dec_layer_t (voxtral_tts.h:101-114)");
+static_assert(sizeof(vb200_decoder_weights_t) == 8 + 26 * 72 + 8, "must match tts_decoder_t");
+static_assert(sizeof(vb200_acoustic_weights_t) == 8 * 8 + 3 * 72, "must match tts_acoustic_t");
+
+using namespace vb;
+
+extern "C" {
+
+vb200_ref_cuda_ctx_t g_cuda;
+
+int tts_cuda_init(int kv_cache_max) { return model_init(kv_cache_max); }
+int tts_cuda_upload_llm_weights(void *p) { return model_upload_llm((const vb200_decoder_weights_t *)p); }
+int tts_cuda_upload_acoustic_weights(void *p) { return model_upload_acoustic((const vb200_acoustic_weights_t *)p); }
+void tts_cuda_free(void) { model_free(); }
+int tts_cuda_available(void) { return g_cuda.initialized; }
+
+void tts_cuda_linear_bf16(float *y, const float *x, const uint16_t *W_bf16, int seq_len, int in_dim,
+                          int out_dim, const void *W_gpu) {
+    if (linear(y, x, W_bf16, seq_len, in_dim, out_dim, W_gpu))
+        fprintf(stderr, "voxtral_b200: tts_cuda_linear_bf16(%d,%d,%d) failed\n", seq_len, in_dim, out_dim);
+}
+
+void tts_cuda_rms_norm(float *d_out, const float *d_x, const float *d_weight, int seq_len, int dim, float eps) {
+    if (!model().inited) return;
+    rms_norm(d_out, d_x, d_weight, seq_len, dim, eps, model().st);
+}
+
+void tts_cuda_apply_rope(float *d_x, const float *d_freqs, int seq, int heads, int head_dim) {
+    if (!model().inited || !d_freqs) return;
+    rope_apply(d_x, d_freqs, seq, heads, head_dim, heads * head_dim, model().st);
+}
+
+void tts_cuda_compute_rope_freqs(float *d_freqs, int start_pos, int seq, int dim, float theta) {
+    if (!model().inited) return;
+    rope_table(d_freqs, start_pos, seq, dim, theta, model().st);
+}
+
+void tts_cuda_silu_mul(float *d_gate, const float *d_up, int n) {
+    if (!model().inited) return;
+    silu_mul(d_gate, d_up, n, model().st);
+}
+
+void tts_cuda_add_inplace(float *d_a, const float *d_b, int n) {
+    if (!model().inited) return;
+    add_inplace(d_a, d_b, n, model().st);
+}
+
+void tts_cuda_causal_attention_decode(float *d_out, const float *d_Q, const float *d_K_cache,
+                                      const float *d_V_cache, int seq_k, int n_heads, int n_kv_heads,
+                                      int head_dim, float scale, int kv_cache_stride) {
+    if (!model().inited || seq_k <= 0) return;
+    const int ldk = kv_cache_stride > 0 ? kv_cache_stride : n_kv_heads * head_dim;
+    if (attention_rows(d_out, d_Q, d_K_cache, d_V_cache, 1, seq_k, n_heads, n_kv_heads, head_dim, scale,
+                       seq_k - 1, 1, n_heads * head_dim, ldk, n_heads * head_dim, model().st))
+        fprintf(stderr, "voxtral_b200: unsupported attention shape (heads %d/%d, head_dim %d)\n", n_heads,
+                n_kv_heads, head_dim);
+}
+
+void tts_cuda_causal_attention_prefill(float *d_out, const float *d_Q, const float *d_K, const float *d_V,
+                                       int seq_len, int start_pos, int n_heads, int n_kv_heads, int head_dim,
+                                       float scale) {
+    if (!model().inited || seq_len <= 0) return;
+    if (attention_rows(d_out, d_Q, d_K, d_V, seq_len, start_pos + seq_len, n_heads, n_kv_heads, head_dim, scale,
+                       start_pos, 1, n_heads * head_dim, n_kv_heads * head_dim, n_heads * head_dim, model().st))
+        fprintf(stderr, "voxtral_b200: unsupported attention shape (heads %d/%d, head_dim %d)\n", n_heads,
+                n_kv_heads, head_dim);
+}
+
+void tts_cuda_bidirectional_attention(float *d_out, const float *d_Q, const float *d_K, const float *d_V,
+                                      int seq_len, int n_heads, int n_kv_heads, int head_dim, float scale) {
+    if (!model().inited || seq_len <= 0) return;
+    if (attention_rows(d_out, d_Q, d_K, d_V, seq_len, seq_len, n_heads, n_kv_heads, head_dim, scale, 0, 0,
+                       n_heads * head_dim, n_kv_heads * head_dim, n_heads * head_dim, model().st))
+        fprintf(stderr, "voxtral_b200: unsupported attention shape (heads %d/%d, head_dim %d)\n", n_heads,
+                n_kv_heads, head_dim);
+}
+
+void tts_cuda_embed_token(float *d_out, const void *d_embeddings_bf16, int token_id, int dim) {
+    if (!model().inited) return;
+    embed_token(d_out, (const uint16_t *)d_embeddings_bf16, token_id, dim, model().st);
+}
+
+void tts_cuda_llm_forward(float *out_hidden, const float *input_embed, int pos) {
+    if (llm_forward(out_hidden, input_embed, pos))
+        fprintf(stderr, "voxtral_b200: tts_cuda_llm_forward(pos=%d) failed\n", pos);
+}
+
+void tts_cuda_llm_prefill(const float *embeds, int seq_len, int start_pos) {
+    if (prefill(embeds, seq_len, start_pos))
+        fprintf(stderr, "voxtral_b200: tts_cuda_llm_prefill(%d rows at %d) failed\n", seq_len, start_pos);
+}
+
+void tts_cuda_predict_velocity(float *out_velocity, const float *x_t, const float *llm_hidden, float t_val) {
+    if (predict_velocity(out_velocity, x_t, llm_hidden, t_val))
+        fprintf(stderr, "voxtral_b200: tts_cuda_predict_velocity failed\n");
+}
+
+void tts_cuda_to_device(void *d_dst, const void *h_src, size_t bytes) {
+    cudaError_t e = cudaMemcpy(d_dst, h_src, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) fprintf(stderr, "voxtral_b200: copy to device failed: %s\n", cudaGetErrorString(e));
+}
+
+void tts_cuda_to_host(void *h_dst, const void *d_src, size_t bytes) {
+    cudaError_t e = cudaMemcpy(h_dst, d_src, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) fprintf(stderr, "voxtral_b200: copy to host failed: %s\n", cudaGetErrorString(e));
+}
+
+void tts_cuda_memset(void *d_ptr, int value, size_t bytes) { cudaMemset(d_ptr, value, bytes); }
+
+void *tts_cuda_alloc(size_t bytes) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+void tts_cuda_free_ptr(void *d_ptr) {
+    if (d_ptr) cudaFree(d_ptr);
+}
+
+void tts_cuda_sync(void) { cudaDeviceSynchronize(); }
+
+/* ---------------- additions ---------------- */
+
+int vb200_frame(const float *embed, const float *noise36, int pos, float *hidden_out, int *codes37) {
+    return frame(embed, noise36, pos, hidden_out, codes37, false);
+}
+
+int vb200_frame_chained(const float *noise36, int pos, float *hidden_out, int *codes37) {
+    return frame(nullptr, noise36, pos, hidden_out, codes37, true);
+}
+
+int vb200_acoustic_frame(const float *llm_hidden, const float *noise36, int *codes37, float *latent_out) {
+    return acoustic_frame(llm_hidden, noise36, codes37, latent_out);
+}
+
+int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows) {
+    return model_upload_audio_embed(table_bf16, rows);
+}
+
+static int kv_rows(int layer, int pos0, int n, float *k_rows, float *v_rows, bool to_device) {
+    Model &m = model();
+    if (!m.inited || layer < 0 || layer >= VB200_DEC_LAYERS || pos0 < 0 || n < 0 || pos0 + n > m.kv_max) return -1;
+    const size_t off = ((size_t)layer * m.kv_max + pos0) * VB200_KV_DIM;
+    const size_t bytes = (size_t)n * VB200_KV_DIM * sizeof(float);
+    cudaError_t e1, e2;
+    if (to_device) {
+        e1 = cudaMemcpy(m.kv_k + off, k_rows, bytes, cudaMemcpyHostToDevice);
+        e2 = cudaMemcpy(m.kv_v + off, v_rows, bytes, cudaMemcpyHostToDevice);
+    } else {
+        e1 = cudaMemcpy(k_rows, m.kv_k + off, bytes, cudaMemcpyDeviceToHost);
+        e2 = cudaMemcpy(v_rows, m.kv_v + off, bytes, cudaMemcpyDeviceToHost);
+    }
+    return (e1 == cudaSuccess && e2 == cudaSuccess) ? 0 : -1;
+}
+
+int vb200_kv_write(int layer, int pos0, int n, const float *k_rows, const float *v_rows) {
+    return kv_rows(layer, pos0, n, (float *)k_rows, (float *)v_rows, true);
+}
+
+int vb200_kv_read(int layer, int pos0, int n, float *k_rows, float *v_rows) {
+    return kv_rows(layer, pos0, n, k_rows, v_rows, false);
+}
+
+int vb200_tap_enable(int on) {
+    Model &m = model();
+    if (!m.inited) return -1;
+    m.tap_on = on != 0;
+    return model_rebuild_programs();
+}
+
+int vb200_tap_read(float *out) {
+    Model &m = model();
+    if (!m.inited) return -1;
+    return cudaMemcpy(out, m.tap, sizeof(float) * VB200_DEC_LAYERS * 2 * VB200_DIM, cudaMemcpyDeviceToHost) ==
+                   cudaSuccess
+               ? 0
+               : -1;
+}
+
+int vb200_debug_gemv_plan(int N, int K, int M, int swiglu, int cta, int n_cta, int *out) {
+    const int epi = swiglu ? VB_EPI_SWIGLU : VB_EPI_STORE;
+    const int rc = gemv_validate(N, K, M, epi, n_cta);
+    if (rc) return rc;
+    const GemvPlan p = gemv_plan(N, K, M, epi, cta, n_cta);
+    out[0] = p.r0; out[1] = p.r1; out[2] = p.passes; out[3] = p.seg_cols;
+    out[4] = p.rows_per_chunk; out[5] = p.row_blocks; out[6] = p.n_chunks;
+    return 0;
+}
+
+int vb200_last_status(void) { return model().last_status; }
+int vb200_sm_count(void) { return model().sm_count; }
+
+double vb200_engine_ms(int reset, int *n) {
+    Model &m = model();
+    const double avg = m.ms_n > 0 ? m.ms_sum / m.ms_n : 0.0;
+    if (n) *n = m.ms_n;
+    if (reset) {
+        m.ms_sum = 0.0;
+        m.ms_n = 0;
+        m.timing = true;
+    }
+    return avg;
+}
+
+} /* extern "C" */

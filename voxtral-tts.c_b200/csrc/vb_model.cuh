@@ -1,0 +1,113 @@
+/*
+ * vb_model.cuh - host-side state of the library: device buffers, repacked
+ * weights, op programs and the calls that run them.
+ */
+#ifndef VB_MODEL_CUH
+#define VB_MODEL_CUH
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <vector>
+
+#include "../../include/voxtral_b200.h"
+#include "vb_engine.cuh"
+
+namespace vb {
+
+/* One transformer layer in HBM. QKV rows are concatenated ([q | k | v] x dim) and
+ * gate/up rows interleaved (2i = gate_i, 2i+1 = up_i) so each is one GEMV. */
+struct LayerDev {
+    uint16_t *wqkv = nullptr;  /* [6144, 3072] */
+    uint16_t *wo = nullptr;    /* [3072, 4096] */
+    uint16_t *w13 = nullptr;   /* [18432, 3072] */
+    uint16_t *w2 = nullptr;    /* [3072, 9216] */
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+};
+
+/* Host -> device input block of one launch (one pinned copy). lat[0] is the noise. */
+struct DevIn {
+    VbDyn dyn;
+    float embed[VB200_DIM];
+    float lat[VB200_FLOW_STEPS][VB200_ACOUSTIC_DIM];
+    float hidden_in[VB200_DIM];   /* acoustic-only entry: hidden state from the host */
+    float temb[VB200_DIM];        /* single-pass entry: time embedding from the host */
+};
+
+/* Device -> host result block of one launch. */
+struct DevOut {
+    int status;
+    int codes[VB200_CODES + 3];
+    float hidden[VB200_DIM];
+    float vel[2][VB200_ACOUSTIC_DIM];
+};
+
+struct Program {
+    VbOp *d_ops = nullptr;
+    int n = 0;
+};
+
+struct Model {
+    bool inited = false;
+    bool llm_ready = false, ac_ready = false, embed_ready = false;
+    int device = 0, n_cta = 0, sm_count = 0;
+    cudaStream_t st = nullptr;
+    std::vector<void *> allocs;
+
+    LayerDev dec[VB200_DEC_LAYERS], ac[VB200_AC_LAYERS];
+    uint16_t *tok_emb = nullptr;
+    float *dec_norm = nullptr;
+    uint16_t *ac_input_proj = nullptr, *ac_time_proj = nullptr, *ac_llm_proj = nullptr;
+    uint16_t *ac_sem_out = nullptr, *ac_out = nullptr;
+    float *ac_sem_bias = nullptr, *ac_norm = nullptr;
+    uint16_t *audio_table = nullptr;
+    float dt[VB200_FLOW_STEPS];
+    std::vector<float> inv_freq;   /* host copy, for the time embedding */
+
+    float *kv_k = nullptr, *kv_v = nullptr;
+    int kv_max = 0;
+
+    /* activations */
+    float *x = nullptr, *qkv = nullptr, *attn = nullptr, *h = nullptr;
+    float *logits = nullptr, *ltok = nullptr, *ttok = nullptr;
+    float *X6 = nullptr, *qkv6 = nullptr, *attn6 = nullptr, *h6 = nullptr;
+    float *attn_scratch = nullptr, *tap = nullptr;
+    unsigned *tickets = nullptr, *bar = nullptr, *exitc = nullptr;
+    DevIn *d_in = nullptr;
+    DevOut *d_out = nullptr;
+    DevIn *h_in = nullptr;     /* pinned */
+    DevOut *h_out = nullptr;   /* pinned */
+    VbOp *d_op1 = nullptr;     /* slots for single-op programs */
+
+    bool tap_on = false;
+    Program p_llm, p_ac, p_frame, p_chain, p_pv;
+
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    double ms_sum = 0.0;
+    int ms_n = 0;
+    bool timing = false;
+    int last_status = 0;
+};
+
+Model &model();
+
+int model_init(int kv_cache_max);
+void model_free();
+int model_upload_llm(const vb200_decoder_weights_t *w);
+int model_upload_acoustic(const vb200_acoustic_weights_t *w);
+int model_upload_audio_embed(const uint16_t *table, int rows);
+int model_rebuild_programs();
+
+int run_program(const Program &p);   /* launch + status */
+int run_ops(const std::vector<VbOp> &ops);
+
+int llm_forward(float *out_hidden, const float *embed, int pos);
+int frame(const float *embed, const float *noise, int pos, float *hidden_out, int *codes, bool chained);
+int acoustic_frame(const float *hidden, const float *noise, int *codes, float *latent_out);
+int predict_velocity(float *out_v, const float *x_t, const float *hidden, float t);
+int linear(float *y, const float *x, const uint16_t *W_host, int M, int K, int N, const void *W_gpu);
+int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N);
+int prefill(const float *embeds, int seq_len, int start_pos);
+
+} // namespace vb
+
+#endif
