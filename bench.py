@@ -1,0 +1,377 @@
+#!/usr/bin/env python3
+"""Benchmark of the per-frame hot path: frames/s of (decoder step + acoustic frame).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json config 4, "full autoregressive utterance"): a 256-row prompt is
+prefilled, then frames are generated one after another; one step = one audio frame = one
+26-layer decoder step at a growing cache (256, 257, ...) + one acoustic frame (semantic
+argmax, 7 Euler steps x 2 guidance branches, FSQ) + re-embedding of the 37 codes. Weights are
+seeded random-init tensors of the real shapes (no checkpoint offline); an END code is treated
+as an ordinary code so that the frame count is fixed.
+
+value : frames/s with the whole loop resident on the device (inputs in HBM, no host traffic
+        inside the timed region), timed with CUDA events on the launching stream.
+e2e   : the same metric through the host-facing C-ABI call (vb200_frame: host embedding and
+        noise in, host hidden state and codes out, every frame) with the re-embedding on the
+        host, as the reference's frame loop does (voxtral_tts.c:301-318).
+N > 1 : independent utterances, one per GPU (weak scaling, no data-path collective).
+
+--impl reference times the reference's own CPU code for the same frames (oracle/_ref, the
+unmodified reference sources built with OpenBLAS; or the CPU restatement if that library is
+absent) on the host cores; it never touches a GPU.
+"""
+import argparse
+import ctypes as C
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG_DIR = os.path.join(ROOT, "voxtral-tts.c_b200")
+
+PROMPT_ROWS = 256
+W_LAYER = 232_783_872                      # BF16 bytes of one transformer layer's seven matrices
+LLM_WEIGHT_BYTES = 26 * W_LAYER
+LLM_NORM_BYTES = 651_264
+KV_WRITE_BYTES = 212_992
+ACOUSTIC_BYTES = 4_962_152_448             # semantic head + llm_proj once + 7 x (3 layers + small heads)
+REEMBED_BYTES = 37 * 3072 * 2
+
+
+def load_package():
+    name = "voxtral_tts_c_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(PKG_DIR, "__init__.py"),
+                                                  submodule_search_locations=[PKG_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def frame_bytes(pos):
+    """Algorithmic HBM bytes of one frame decoded at cache row `pos` (keys = pos + 1)."""
+    return (LLM_WEIGHT_BYTES + LLM_NORM_BYTES + 26 * (pos + 1) * 8192 + KV_WRITE_BYTES + ACOUSTIC_BYTES
+            + REEMBED_BYTES)
+
+
+def prompt_rows(pkg, model, seed):
+    """224 voice-embedding rows ~N(0,0.5) then 32 token rows with ids in [1000, 131072)."""
+    voice = pkg.synth_f32((224, pkg.DIM), seed, "bench.voice", 0.0, 0.5)
+    ids = 1000 + (pkg.synth_bf16(32, seed, "bench.ids").astype(np.int64) * 2 % (pkg.VOCAB - 1000))
+    return np.concatenate([voice, model.token_rows(ids)], axis=0)
+
+
+def noise_rows(seed, n):
+    """n x 36 normals from the reference's generator (xorshift64, shifts 13/7/17, Box-Muller
+    cosine branch; voxtral_tts_kernels.c:640-669), written out in numpy."""
+    mask = (1 << 64) - 1
+    s = seed if seed else 0x12345678ABCDEF01
+    out = np.empty(n * 36, dtype=np.float32)
+
+    def nxt():
+        nonlocal s
+        s ^= (s << 13) & mask
+        s ^= s >> 7
+        s ^= (s << 17) & mask
+        return np.float32(np.float32(s >> 11) * np.float32(1.0 / 9007199254740992.0))
+
+    for i in range(n * 36):
+        u1 = nxt()
+        while u1 < np.float32(1e-30):
+            u1 = nxt()
+        u2 = nxt()
+        out[i] = np.sqrt(np.float32(-2.0) * np.log(u1)) * np.cos(np.float32(6.2831853071795864) * u2)
+    return out.reshape(n, 36)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 8:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ----------------------------------------------------------------------------------------------
+# reference CPU arm and cpu_baseline
+# ----------------------------------------------------------------------------------------------
+def cpu_reference(pkg, model, kv_prefix, first_embed, noise, n_frames, budget_s):
+    """Times frames on the host with the reference's own CPU code. Returns a dict."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_bind
+    cores = os.cpu_count() or 1
+    ref = oracle_bind.load_ref("blas")
+    kind, what = "reference", "reference C sources, -DUSE_BLAS with scipy's OpenBLAS"
+    if ref is None:
+        ref = oracle_bind.load_ref("noblas")
+        what = "reference C sources, portable build without BLAS"
+    kvk, kvv = kv_prefix
+    pos0 = kvk.shape[1]
+    t_frames, done = 0.0, 0
+    if ref is not None:
+        ref.open(model, kv_max=pos0 + n_frames + 8)
+        k, v = ref.kv()
+        k[:, :pos0] = kvk
+        v[:, :pos0] = kvv
+        ref.set_kv_len(pos0)
+        ref.set_rng_state(1)
+        e = first_embed
+        h = ref.llm_forward(e)                 # warm-up step (pages the weights in), then rewind
+        ref.set_kv_len(pos0)
+        t_start = time.perf_counter()
+        while done < n_frames:
+            t0 = time.perf_counter()
+            h = ref.llm_forward(e)
+            codes = ref.acoustic_forward(h)
+            e = ref.audio_embed(codes)
+            t_frames += time.perf_counter() - t0
+            done += 1
+            if time.perf_counter() - t_start + t_frames / done > budget_s:
+                break
+        ref.close()
+    else:
+        kind, what = "port", "CPU restatement (oracle/vox_oracle.c, OpenMP over output rows)"
+        orc = oracle_bind.Oracle()
+        dec, ac = orc.decoder(model), orc.acoustic(model)
+        k = np.zeros((26, pos0 + n_frames + 8, 1024), dtype=np.float32)
+        v = np.zeros_like(k)
+        k[:, :pos0] = kvk
+        v[:, :pos0] = kvv
+        st, e = 1, first_embed
+        t_start = time.perf_counter()
+        while done < n_frames:
+            t0 = time.perf_counter()
+            h = orc.llm_forward(dec, k, v, pos0 + done, e)
+            codes, _, _, st = orc.acoustic_forward(ac, st, h)
+            e = orc.audio_embed(model.audio_table(), codes)
+            t_frames += time.perf_counter() - t0
+            done += 1
+            if time.perf_counter() - t_start + t_frames / done > budget_s:
+                break
+    fps = done / t_frames
+    return {"value": fps, "unit": "frames/s", "cores": cores, "kind": kind,
+            "sample": f"{done} frame(s) of the same workload (decoder step at {pos0}+ keys, acoustic frame, "
+                      f"re-embedding) after one warm-up decoder step; {what}; the M=1 decoder matvecs are "
+                      f"single-threaded by construction, the M=3 acoustic GEMMs use up to {cores} threads",
+            "ms_per_frame": 1000.0 / fps}
+
+
+# ----------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=212)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=0, help="frames of the host-ABI measurement (default: min(steps, 64))")
+    ap.add_argument("--cpu-budget", type=float, default=25.0, help="seconds of CPU-baseline frames")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    K, W = max(args.steps, 1), max(args.warmup, 0)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    config = {"workload": "config 4: 256-row prompt prefilled, then one utterance per GPU generates frames "
+                          "(decoder step at cache 256.. + acoustic frame 7 Euler x 2 CFG + re-embedding)",
+              "prompt_rows": PROMPT_ROWS, "frames": K, "utterances_per_gpu": 1, "parallelism": f"dp{world}",
+              "weights": "seeded random-init BF16 ~N(0,0.02), real shapes",
+              "l2_policy": "inputs larger than L2 (11 GB of weights stream per frame)"}
+
+    pkg = load_package()
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        model = pkg.SynthModel(seed=1234)
+        kvk = pkg.synth_f32((26, PROMPT_ROWS, 1024), 7, "bench.ref.kv_k")
+        kvv = pkg.synth_f32((26, PROMPT_ROWS, 1024), 7, "bench.ref.kv_v")
+        first = model.token_rows([24])[0]
+        budget = min(150.0, max(20.0, 6.0 * (K + W)))
+        r = cpu_reference(pkg, model, (kvk, kvv), first, None, K, budget)
+        config["cache_prefix"] = "synthetic N(0,1) rows (no GPU prefill in this arm)"
+        line = {"impl": "reference", "metric": "frames_per_s", "value": r["value"], "unit": "frames/s",
+                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": r["ms_per_frame"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": r["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the library has no CPU fallback "
+                         "(use --impl reference for the CPU reference arm)")
+    torch.cuda.set_device(local_rank)
+    os.environ["VB200_DEVICE"] = str(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        try:
+            torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
+        except Exception:
+            pass
+        os.environ.setdefault("OMP_NUM_THREADS", str(max(1, (os.cpu_count() or 8) // world)))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    model = pkg.SynthModel(seed=1234)
+    kv_max = PROMPT_ROWS + W + K + 72
+    eng = pkg.Engine(kv_cache_max=kv_max)
+    eng.upload(model, decoder=True, acoustic=True, audio_table=True)
+    eng.L.vb200_set_option(b"ignore_end", 1)
+
+    rows = prompt_rows(pkg, model, 100 + rank)
+    eng.prefill(rows, 0)
+    first = model.token_rows([24])[0]                      # embed(AUDIO), voxtral_tts.c:295
+    noise = noise_rows(1000 + rank, W + K)
+
+    # ---- value: device-resident loop -------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    Lb = eng.L
+    assert Lb.vb200_utterance_begin(first.ctypes.data, PROMPT_ROWS, noise.ctypes.data, W + K) == 0
+    codes = np.zeros((W + K, pkg.CODES), dtype=np.int32)
+    done, end, ms = C.c_int(0), C.c_int(0), C.c_float(0.0)
+    if W:
+        assert Lb.vb200_utterance_run(W) == 0
+    torch.cuda.synchronize()
+    barrier()
+    sampler.start()
+    assert Lb.vb200_utterance_run(K) == 0
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    assert Lb.vb200_utterance_end(codes.ctypes.data, C.byref(done), C.byref(end), C.byref(ms)) == 0
+    if done.value != W + K:
+        raise SystemExit(f"device loop ran {done.value} of {W + K} frames (status {Lb.vb200_last_status()})")
+    t_ms = torch.tensor([ms.value], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(t_ms.item())
+    value = world * K / (total_ms / 1000.0)
+
+    # ---- e2e: one host-facing call per frame, re-embedding on the host ------------------------
+    Ke = args.e2e_steps or min(K, 64)
+    table = model.audio_table()
+    offs = np.concatenate([[0], 8194 + 23 * np.arange(36)]).astype(np.int64)
+    eng.prefill(rows, 0)                                    # rewind the cache to the prompt
+    e = first.copy()
+    pos = PROMPT_ROWS
+    for f in range(min(W, 3)):
+        c, _ = eng.frame(e, noise[f], pos)
+        pos += 1
+        e = (table[offs + c].astype(np.uint32) << 16).view(np.float32).sum(axis=0, dtype=np.float32)
+    barrier()
+    t0 = time.perf_counter()
+    for f in range(Ke):
+        c, h = eng.frame(e, noise[min(W, 3) + f], pos)      # H2D embed+noise, kernel, D2H hidden+codes
+        pos += 1
+        e = (table[offs + c].astype(np.uint32) << 16).view(np.float32).sum(axis=0, dtype=np.float32)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t_e = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+    e2e_value = world * Ke / float(t_e.item())
+
+    # ---- roofline of the frame kernel -----------------------------------------------------------
+    peak, peak_src = measured_hbm_peak()
+    mean_bytes = float(np.mean([frame_bytes(PROMPT_ROWS + W + f) for f in range(K)]))
+    launch_ms = total_ms / K
+    achieved = mean_bytes / (launch_ms / 1000.0) / 1e9
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "frame_kernel_traffic.json")) as f:
+            traffic = json.load(f).get("dram_bytes_per_launch")
+    except Exception:
+        pass
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "kernel": "vb_engine_kernel (one launch = one frame)",
+                "algorithmic_bytes_per_launch": mean_bytes, "launch_ms": launch_ms, "peak_source": peak_src}
+
+    if rank != 0:
+        eng.close()
+        return
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        kvk = np.stack([eng.kv_read(l, 0, PROMPT_ROWS)[0] for l in range(26)])
+        kvv = np.stack([eng.kv_read(l, 0, PROMPT_ROWS)[1] for l in range(26)])
+        r = cpu_reference(pkg, model, (kvk, kvv), first, None, 8, args.cpu_budget)
+        cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    eng.close()
+
+    line = {"metric": "frames_per_s", "value": value, "unit": "frames/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 (BF16 weights, fp32 activations and accumulation)",
+            "data": "synthetic", "config": config, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "frames/s", "steps": Ke,
+                    "h2d_bytes_per_step": 16 + 3072 * 4 + 36 * 4, "d2h_bytes_per_step": 176 + 3072 * 4},
+            "gpu_launches": K, "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

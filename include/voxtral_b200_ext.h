@@ -41,6 +41,20 @@ int vb200_acoustic_frame(const float *llm_hidden, const float *noise36, int *cod
 int vb200_frame_chained(const float *noise36, int pos, float *hidden_out, int *codes37);
 int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows);
 
+/* The orchestrator's frame loop (voxtral_tts.c:301-321) kept on the device: no host
+ * round trip per frame. begin: first decoder input, first cache row, and the noise
+ * of all n_frames frames ([n_frames, 36]; the reference RNG draws 36 normals per
+ * frame in sequence). run: queue up to n more frames and return at once. end: wait,
+ * fetch codes [frames_done, 37] (an END frame is included and flagged through
+ * hit_end; the reference discards it) and the device time of the last run call. */
+int vb200_utterance_begin(const float *first_embed, int start_pos, const float *noise, int n_frames);
+int vb200_utterance_run(int n_frames);
+int vb200_utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
+/* Options by name. "ignore_end" (0/1): a device-resident run started after this call
+ * treats END as an ordinary code, for fixed-length timing runs. Returns -1 for an
+ * unknown name. */
+int vb200_set_option(const char *name, int value);
+
 /* Copy rows [pos0, pos0+n) of one layer's K and V cache to / from the host
  * ([n, 1024] fp32 each), e.g. to pre-fill a cache prefix. */
 int vb200_kv_write(int layer, int pos0, int n, const float *k_rows, const float *v_rows);

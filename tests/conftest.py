@@ -66,3 +66,19 @@ def ref_blas():
     if r is None:
         pytest.skip("oracle/_ref/libvoxref_blas.so not available")
     return r
+
+
+@pytest.fixture(scope="session")
+def synth_model(pkg):
+    from cases import MODEL_SEED
+    return pkg.SynthModel(seed=MODEL_SEED)
+
+
+@pytest.fixture(scope="session")
+def engine(pkg, synth_model):
+    """The process-wide GPU context (the library, like the reference, has one per process)
+    with the full synthetic checkpoint uploaded."""
+    e = pkg.Engine(kv_cache_max=512)
+    e.upload(synth_model, decoder=True, acoustic=True, audio_table=True)
+    yield e
+    e.close()

@@ -1,0 +1,88 @@
+"""GPU parity of the acoustic transformer: tts_cuda_predict_velocity (one pass) and the fused
+frame (semantic argmax, 7 Euler steps x 2 guidance branches, FSQ) against the CPU oracle and
+the golden fixtures: BASELINE config 2. Bars from the north star: identical semantic argmax,
+acoustic codes identical for >= 99 % of frames."""
+import os
+
+import numpy as np
+import pytest
+
+from cases import MODEL_SEED, config2_inputs
+from gpu_common import rel_l2
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def eng(engine):
+    return engine
+
+
+@pytest.fixture(scope="module")
+def model(synth_model):
+    return synth_model
+
+
+def test_predict_velocity(pkg, eng, oracle, model):
+    g = np.load(os.path.join(GOLD, "config2_acoustic.npz"))
+    hidden, _ = config2_inputs(pkg)
+    v = eng.predict_velocity(g["noise"], hidden, 0.0)
+    assert rel_l2(v, g["vel_t0_cond"]) < 2e-3
+    v = eng.predict_velocity(g["noise"], np.zeros_like(hidden), 3.0 / 7.0)
+    assert rel_l2(v, g["vel_t3_uncond"]) < 2e-3
+    ac = oracle.acoustic(model)
+    x = pkg.synth_f32(36, 3, "pvx")
+    for t in (0.0, 1.0 / 7.0, 0.5, 6.0 / 7.0):
+        assert rel_l2(eng.predict_velocity(x, hidden, t), oracle.predict_velocity(ac, x, hidden, t)) < 2e-3
+
+
+def test_config2_frame_codes(pkg, eng, oracle, model):
+    g = np.load(os.path.join(GOLD, "config2_acoustic.npz"))
+    hidden, seed = config2_inputs(pkg)
+    codes, latent = eng.acoustic_frame(hidden, g["noise"])
+    assert codes[0] == g["codes"][0]                  # identical semantic argmax
+    assert np.array_equal(codes, g["codes"])          # and here every acoustic code too
+    _, _, xf, _ = oracle.acoustic_forward(oracle.acoustic(model), oracle.seed(seed), hidden)
+    assert rel_l2(latent, xf) < 2e-3
+    codes2, _ = eng.acoustic_frame(hidden, g["noise"])
+    assert np.array_equal(codes, codes2)
+
+
+def test_many_frames_code_agreement(pkg, eng, oracle, model):
+    """24 hidden states and seeds: semantic codes all equal, >= 99 % of frames with all 36
+    acoustic codes equal (here: at most 0 of 24 may differ), latents within 2e-3."""
+    ac = oracle.acoustic(model)
+    frames, same = 24, 0
+    for f in range(frames):
+        hidden = pkg.synth_f32(3072, 500 + f, "mf.hidden")
+        st = oracle.seed(1000 + f)
+        noise, _ = oracle.randn(st, 36)
+        ref_codes, _, xf, _ = oracle.acoustic_forward(ac, st, hidden)
+        codes, latent = eng.acoustic_frame(hidden, noise)
+        assert codes[0] == ref_codes[0]
+        assert rel_l2(latent, xf) < 2e-3
+        same += int(np.array_equal(codes, ref_codes))
+    assert same >= int(np.ceil(0.99 * frames)), same
+
+
+def test_semantic_bias_and_end_code(pkg, eng, oracle, model):
+    """With a bias tensor (the optional branch, voxtral_tts_acoustic.c:76-78) and with a bias that
+    forces END: codes 1..36 are 2 and the caller's RNG is left alone."""
+    hidden, seed = config2_inputs(pkg)
+    name = "acoustic_transformer.semantic_codebook_output.bias"
+    st = oracle.seed(seed)
+    noise, _ = oracle.randn(st, 36)
+    try:
+        model.t[name] = pkg.synth_f32(8320, MODEL_SEED, name, 0.0, 0.5)
+        eng.upload(model, decoder=False, acoustic=True)
+        ref_codes, _, _, _ = oracle.acoustic_forward(oracle.acoustic(model), st, hidden)
+        codes, _ = eng.acoustic_frame(hidden, noise)
+        assert np.array_equal(codes, ref_codes)
+        model.t[name][1] = 1e6
+        eng.upload(model, decoder=False, acoustic=True)
+        codes, _ = eng.acoustic_frame(hidden, noise)
+        assert codes[0] == 1 and np.all(codes[1:] == 2)
+    finally:
+        del model.t[name]
+        eng.upload(model, decoder=False, acoustic=True)

@@ -86,6 +86,10 @@ def lib():
         "vb200_frame_chained": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
         "vb200_acoustic_frame": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
         "vb200_upload_audio_embed": (C.c_int, [C.c_void_p, C.c_int]),
+        "vb200_utterance_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
+        "vb200_utterance_run": (C.c_int, [C.c_int]),
+        "vb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
+        "vb200_utterance_end": (C.c_int, [C.c_void_p, i32p, i32p, f32p]),
         "vb200_kv_write": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
         "vb200_kv_read": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
         "vb200_tap_enable": (C.c_int, [C.c_int]),
@@ -320,6 +324,20 @@ class Engine:
             rc = self.L.vb200_frame(_ptr(embed), _ptr(noise), int(pos), hp, _ptr(codes))
         self._ok("vb200_frame", rc)
         return codes, hidden
+
+    def utterance(self, first_embed, start_pos, noise, n_frames=None, batch=None):
+        """Device-resident frame loop. Returns (codes [frames,37], hit_end, device_ms)."""
+        noise = np.ascontiguousarray(noise, dtype=np.float32).reshape(-1, ACOUSTIC_DIM)
+        n_frames = noise.shape[0] if n_frames is None else n_frames
+        first_embed = np.ascontiguousarray(first_embed, dtype=np.float32)
+        self._ok("vb200_utterance_begin",
+                 self.L.vb200_utterance_begin(_ptr(first_embed), int(start_pos), _ptr(noise), n_frames))
+        self._ok("vb200_utterance_run", self.L.vb200_utterance_run(n_frames if batch is None else batch))
+        codes = np.zeros((n_frames, CODES), dtype=np.int32)
+        done, end, ms = C.c_int(0), C.c_int(0), C.c_float(0.0)
+        self._ok("vb200_utterance_end",
+                 self.L.vb200_utterance_end(_ptr(codes), C.byref(done), C.byref(end), C.byref(ms)))
+        return codes[:done.value], bool(end.value), ms.value
 
     def kv_write(self, layer, pos0, k_rows, v_rows):
         k_rows = np.ascontiguousarray(k_rows, dtype=np.float32)

@@ -153,6 +153,22 @@ int vb200_acoustic_frame(const float *llm_hidden, const float *noise36, int *cod
     return acoustic_frame(llm_hidden, noise36, codes37, latent_out);
 }
 
+int vb200_utterance_begin(const float *first_embed, int start_pos, const float *noise, int n_frames) {
+    return utterance_begin(first_embed, start_pos, noise, n_frames);
+}
+
+int vb200_utterance_run(int n_frames) { return utterance_run(n_frames); }
+
+int vb200_set_option(const char *name, int value) {
+    if (!name) return -1;
+    if (!strcmp(name, "ignore_end")) { model().ignore_end = value != 0; return 0; }
+    return -1;
+}
+
+int vb200_utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms) {
+    return utterance_end(codes_out, frames_done, hit_end, device_ms);
+}
+
 int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows) {
     return model_upload_audio_embed(table_bf16, rows);
 }

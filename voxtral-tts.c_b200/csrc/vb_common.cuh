@@ -115,7 +115,8 @@ VB_DEVINL float vb_warp_sum(float v) {
 template <int V>
 VB_DEVINL int vb_warp_multi_sum(float (&v)[V], int lane) {
     int base = 0;
-    int count = V;
+    int count = V;    /* slots per lane, padding included (same on every lane) */
+    int real = V;     /* how many of this lane's slots carry actual values */
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         if (count > 1) {
@@ -130,13 +131,15 @@ VB_DEVINL int vb_warp_multi_sum(float (&v)[V], int lane) {
                     v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
             }
-            if (up) base += half;
+            if (up) { base += half; real = real > half ? real - half : 0; }
+            else real = real < half ? real : half;
             count = half;
         } else {
             v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
         }
     }
-    return base;
+    /* a lane that ended on a padding slot (odd counts on the way) owns no value */
+    return real > 0 ? base : V;
 }
 
 #endif

@@ -511,7 +511,13 @@ __device__ void op_ac_tokens(Ctx &c, const VbOp &op) {
     if (c.tid < A) {
         float xv;
         if (step == 0) {
-            xv = vb_ldcg(lat + c.tid);
+            if (op.p3) {
+                /* device-resident run: this frame's noise comes from the uploaded array */
+                xv = vb_ldcg((const float *)op.p3 + (size_t)c.a.dyn->frame * A + c.tid);
+                if (blockIdx.x == 0) lat[c.tid] = xv;
+            } else {
+                xv = vb_ldcg(lat + c.tid);
+            }
         } else {
             const float *vel = (const float *)op.p0;
             xv = euler_update(vb_ldcg(lat + (size_t)(step - 1) * A + c.tid), vb_ldcg(vel + c.tid),
@@ -593,8 +599,30 @@ __device__ void op_fsq(Ctx &c, const VbOp &op) {
         if (code < 0) code = 0;
         if (code >= levels) code = levels - 1;
         const int sem = __ldcg(codes);
-        codes[1 + c.tid] = (sem == 1) ? 2 : code + 2;
+        const int out = (sem == 1) ? 2 : code + 2;
+        codes[1 + c.tid] = out;
+        if (op.p3) { /* device-resident run: keep every frame's codes */
+            int *log = (int *)op.p3 + (size_t)c.a.dyn->frame * (A + 1);
+            log[1 + c.tid] = out;
+            if (c.tid == 0) log[0] = sem;
+        }
     }
+}
+
+/* End of one frame of a device-resident run (the loop of voxtral_tts.c:301-321
+ * without the host): the next frame decodes at the next cache row and reads the
+ * next noise row; an END code (or a full cache) stops the run. op.p0 = codes;
+ * i0 = frames the noise / code arrays hold; i1 != 0: END does not stop the run
+ * (fixed-length timing runs). CTA 0 only. */
+__device__ void op_advance(Ctx &c, const VbOp &op) {
+    if (blockIdx.x != 0 || c.tid != 0) return;
+    VbDyn *d = c.a.dyn;
+    const int sem = __ldcg((const int *)op.p0);
+    const int frame = d->frame + 1, pos = d->pos + 1;
+    d->frame = frame;
+    d->pos = pos;
+    if (sem == 1 && !op.i1) d->done = 2;                       /* END code */
+    else if (frame >= op.i0 || pos >= d->kv_max) d->done = 1;  /* arrays or cache exhausted */
 }
 
 /* Next decoder input from the 37 codes: sum of BF16 table rows in codebook order
@@ -628,6 +656,10 @@ __global__ void __launch_bounds__(kThreads, 1) vb_engine_kernel(EngineArgs a) {
     c.s = s; c.a = a;
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.chunk_counter = 0; c.barrier_epoch = 0;
+
+    /* A device-resident run that has produced END: its remaining queued launches do
+     * nothing. The flag was written by an earlier launch, so the whole grid agrees. */
+    if (a.dyn->done) return;
 
     if (c.tid == 0) {
         for (int i = 0; i < kSlots; i++) {
@@ -672,6 +704,7 @@ __global__ void __launch_bounds__(kThreads, 1) vb_engine_kernel(EngineArgs a) {
             case VB_OP_ARGMAX:      if (c.warp < kComputeWarps) op_argmax(c, op); break;
             case VB_OP_FSQ:         if (c.warp < kComputeWarps) op_fsq(c, op); break;
             case VB_OP_EMBED:       if (c.warp < kComputeWarps) op_embed(c, op); break;
+            case VB_OP_ADVANCE:     if (c.warp < kComputeWarps) op_advance(c, op); break;
             default: if (c.tid == 0) raise_abort(c, VB_ERR_BAD_OP); break;
             }
             if (!(op.flags & VB_F_NOSYNC) && oi + 1 < a.n_ops) grid_sync(c);

@@ -51,7 +51,7 @@ struct SmemLayout {
 struct EngineArgs {
     const VbOp *ops;
     int n_ops;
-    const VbDyn *dyn;
+    VbDyn *dyn;
     unsigned *bar_counter;   /* grid barrier arrivals, zero between launches */
     unsigned *exit_counter;  /* CTAs that finished; the last one re-zeroes both */
     int *status;             /* VbStatus, sticky until the host clears it */

@@ -83,6 +83,8 @@ int model_init(int kv_cache_max) {
     VB_CHECK(cudaStreamCreate(&m.st));
     VB_CHECK(cudaEventCreate(&m.ev0));
     VB_CHECK(cudaEventCreate(&m.ev1));
+    VB_CHECK(cudaEventCreate(&m.evr0));
+    VB_CHECK(cudaEventCreate(&m.evr1));
     m.n_cta = engine_max_ctas(m.device);
     if (m.n_cta <= 0) {
         fprintf(stderr, "voxtral_b200: frame kernel does not fit on this device\n");
@@ -162,6 +164,8 @@ void model_free() {
     if (m.h_out) cudaFreeHost(m.h_out);
     if (m.ev0) cudaEventDestroy(m.ev0);
     if (m.ev1) cudaEventDestroy(m.ev1);
+    if (m.evr0) cudaEventDestroy(m.evr0);
+    if (m.evr1) cudaEventDestroy(m.evr1);
     if (m.st) cudaStreamDestroy(m.st);
     m = Model();
     memset(&g_cuda, 0, sizeof(g_cuda));
@@ -170,8 +174,15 @@ void model_free() {
 /* ------------------------------------------------------------------ */
 /* weights                                                             */
 /* ------------------------------------------------------------------ */
+/* Uploads replace whatever an earlier upload left in the same slot. */
+template <typename T>
+static void drop(T **p) {
+    if (*p) { dev_release(*p); *p = nullptr; }
+}
+
 static int upload_bf16(uint16_t **dst, const uint16_t *src, size_t n) {
     if (!src) return -1;
+    drop(dst);
     if (dev_alloc(dst, n)) return -1;
     VB_CHECK(cudaMemcpy(*dst, src, n * 2, cudaMemcpyHostToDevice));
     return 0;
@@ -179,6 +190,7 @@ static int upload_bf16(uint16_t **dst, const uint16_t *src, size_t n) {
 
 static int upload_f32(float **dst, const float *src, size_t n) {
     if (!src) return -1;
+    drop(dst);
     if (dev_alloc(dst, n)) return -1;
     VB_CHECK(cudaMemcpy(*dst, src, n * 4, cudaMemcpyHostToDevice));
     return 0;
@@ -190,6 +202,8 @@ static int upload_layer(LayerDev &L, const vb200_layer_weights_t &w, uint16_t *t
     Model &m = g_model;
     if (!w.wq || !w.wk || !w.wv || !w.wo || !w.w1 || !w.w2 || !w.w3 || !w.attention_norm || !w.ffn_norm)
         return -1;
+    drop(&L.wqkv);
+    drop(&L.w13);
     if (dev_alloc(&L.wqkv, (size_t)QKV * D)) return -1;
     VB_CHECK(cudaMemcpy(L.wqkv, w.wq, (size_t)QD * D * 2, cudaMemcpyHostToDevice));
     VB_CHECK(cudaMemcpy(L.wqkv + (size_t)QD * D, w.wk, (size_t)KVD * D * 2, cudaMemcpyHostToDevice));
@@ -248,6 +262,7 @@ int model_upload_acoustic(const vb200_acoustic_weights_t *w) {
     if (!rc) rc = upload_bf16(&m.ac_sem_out, w->semantic_out, (size_t)VB200_SEM_PADDED * D);
     if (!rc) rc = upload_bf16(&m.ac_out, w->acoustic_out, (size_t)A * D);
     if (!rc) rc = upload_f32(&m.ac_norm, w->norm, D);
+    if (!w->semantic_out_bias) drop(&m.ac_sem_bias);
     if (!rc && w->semantic_out_bias) rc = upload_f32(&m.ac_sem_bias, w->semantic_out_bias, VB200_SEM_PADDED);
     if (!rc && !w->time_inv_freq) rc = -1;
     if (rc) {
@@ -387,7 +402,8 @@ static void build_ac_layers(std::vector<VbOp> &ops, int rows) {
 /* Acoustic frame (voxtral_tts_acoustic.c:283-372) with both guidance branches of
  * each Euler step batched as six rows. `hidden` is the decoder output on the
  * device; latents and velocities live in d_in / d_out. */
-static void build_acoustic(std::vector<VbOp> &ops, const float *hidden) {
+static void build_acoustic(std::vector<VbOp> &ops, const float *hidden, const float *noise_all = nullptr,
+                           int *codes_all = nullptr) {
     Model &m = g_model;
     VbOp o = op_gemv(1, VB200_SEM_PADDED, D, m.ac_sem_out, hidden, D, m.logits, VB200_SEM_PADDED, VB_EPI_STORE);
     o.bias = m.ac_sem_bias;
@@ -408,6 +424,7 @@ static void build_acoustic(std::vector<VbOp> &ops, const float *hidden) {
         o.type = VB_OP_AC_TOKENS; o.N = D; o.K = A; o.W = m.ac_input_proj; o.x = lat; o.p0 = vel;
         o.p1 = m.ttok; o.p2 = m.ltok; o.y = m.X6; o.ldy = D; o.i0 = s; o.i1 = 0;
         o.f0 = VB200_CFG_ALPHA; o.f1 = (s > 0) ? m.dt[s - 1] : 0.0f;
+        if (s == 0) o.p3 = (void *)noise_all;
         ops.push_back(o);
         build_ac_layers(ops, 6);
         /* final norm of token 0 of each branch (rows 0 and 3), then the velocity head */
@@ -418,6 +435,7 @@ static void build_acoustic(std::vector<VbOp> &ops, const float *hidden) {
     o = op_zero();
     o.type = VB_OP_FSQ; o.K = A; o.x = lat; o.p0 = vel; o.p2 = m.d_out->codes;
     o.i0 = steps; o.i1 = VB200_FSQ_LEVELS; o.f0 = VB200_CFG_ALPHA; o.f1 = m.dt[steps - 1];
+    o.p3 = codes_all;
     ops.push_back(o);
 }
 
@@ -444,7 +462,10 @@ static void build_predict_velocity(std::vector<VbOp> &ops) {
 static int validate(const std::vector<VbOp> &ops) {
     for (size_t i = 0; i < ops.size(); i++)
         if (ops[i].type == VB_OP_GEMV) {
-            const int rc = gemv_validate(ops[i].N, ops[i].K, ops[i].M, ops[i].epi, g_model.n_cta);
+            int rc = gemv_validate(ops[i].N, ops[i].K, ops[i].M, ops[i].epi, g_model.n_cta);
+            /* bulk copies and 128-bit loads need 16-byte aligned rows */
+            if (!rc && (((uintptr_t)ops[i].W | (uintptr_t)ops[i].x | (uintptr_t)ops[i].norm_w) & 15)) rc = -20;
+            if (!rc && ops[i].M > 1 && (ops[i].ldx & 3)) rc = -21;
             if (rc) {
                 fprintf(stderr, "voxtral_b200: op %zu (M=%d N=%d K=%d) not runnable: %d\n", i, ops[i].M, ops[i].N,
                         ops[i].K, rc);
@@ -562,7 +583,7 @@ int llm_forward(float *out_hidden, const float *embed, int pos) {
         fprintf(stderr, "voxtral_b200: position %d outside the %d-row cache\n", pos, m.kv_max);
         return -1;
     }
-    m.h_in->dyn.pos = pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.n_keys_cap = m.kv_max;
+    m.h_in->dyn.pos = pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.frame = 0; m.h_in->dyn.done = 0;
     memcpy(m.h_in->embed, embed, sizeof(float) * D);
     VB_CHECK(cudaMemcpyAsync(m.d_in, m.h_in, offsetof(DevIn, lat), cudaMemcpyHostToDevice, m.st));
     if (run_program(m.p_llm)) return -1;
@@ -579,7 +600,7 @@ int frame(const float *embed, const float *noise, int pos, float *hidden_out, in
         fprintf(stderr, "voxtral_b200: position %d outside the %d-row cache\n", pos, m.kv_max);
         return -1;
     }
-    m.h_in->dyn.pos = pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.n_keys_cap = m.kv_max;
+    m.h_in->dyn.pos = pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.frame = 0; m.h_in->dyn.done = 0;
     memcpy(m.h_in->lat[0], noise, sizeof(float) * A);
     if (chained) {
         VB_CHECK(cudaMemcpyAsync(&m.d_in->dyn, &m.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice, m.st));
@@ -628,6 +649,89 @@ int predict_velocity(float *out_v, const float *x_t, const float *hidden, float 
     if (finish(sizeof(DevOut))) return -1;
     memcpy(out_v, m.h_out->vel[0], sizeof(float) * A);
     return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* device-resident frame loop                                          */
+/* ------------------------------------------------------------------ */
+/* The orchestrator's loop (voxtral_tts.c:301-321) without host round trips: the
+ * noise of every frame is uploaded up front (the reference RNG is sequential and
+ * draws 36 values per frame that is not END), codes are re-embedded on the device,
+ * position and frame index advance in device memory, and an END code turns the
+ * remaining queued launches into no-ops. */
+int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames) {
+    Model &m = g_model;
+    if (!m.inited || !m.llm_ready || !m.ac_ready || !m.embed_ready) return -1;
+    if (n_frames <= 0 || start_pos < 0 || start_pos >= m.kv_max) return -1;
+    drop(&m.noise_all);
+    drop(&m.codes_all);
+    if (dev_alloc(&m.noise_all, (size_t)n_frames * A) || dev_alloc(&m.codes_all, (size_t)n_frames * VB200_CODES))
+        return -1;
+    VB_CHECK(cudaMemcpy(m.noise_all, noise_all, sizeof(float) * (size_t)n_frames * A, cudaMemcpyHostToDevice));
+    VB_CHECK(cudaMemset(m.codes_all, 0, sizeof(int) * (size_t)n_frames * VB200_CODES));
+    m.run_cap = n_frames;
+    m.run_launched = 0;
+
+    std::vector<VbOp> ops;
+    VbOp adv = op_zero();
+    adv.type = VB_OP_ADVANCE; adv.p0 = m.d_out->codes; adv.i0 = n_frames; adv.i1 = m.ignore_end ? 1 : 0;
+    build_llm(ops, m.d_in->embed, m.d_out->hidden);
+    build_acoustic(ops, m.d_out->hidden, m.noise_all, m.codes_all);
+    ops.push_back(adv);
+    if (upload_program(m.p_run_first, ops)) return -1;
+    ops.clear();
+    VbOp e = op_zero();
+    e.type = VB_OP_EMBED; e.N = D; e.W = m.audio_table; e.p0 = m.d_out->codes; e.y = m.d_in->embed;
+    e.i0 = VB200_CODES; e.i1 = 8194; e.i2 = 23;
+    ops.push_back(e);
+    build_llm(ops, m.d_in->embed, m.d_out->hidden);
+    build_acoustic(ops, m.d_out->hidden, m.noise_all, m.codes_all);
+    ops.push_back(adv);
+    if (upload_program(m.p_run_next, ops)) return -1;
+
+    m.h_in->dyn.pos = start_pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.frame = 0; m.h_in->dyn.done = 0;
+    memcpy(m.h_in->embed, first_embed, sizeof(float) * D);
+    VB_CHECK(cudaMemcpyAsync(m.d_in, m.h_in, offsetof(DevIn, lat), cudaMemcpyHostToDevice, m.st));
+    VB_CHECK(cudaStreamSynchronize(m.st));
+    return 0;
+}
+
+/* Queues n more frames; returns without waiting. */
+int utterance_run(int n) {
+    Model &m = g_model;
+    if (!m.noise_all || n < 0) return -1;
+    const bool timing = m.timing;
+    m.timing = false;                      /* one event pair around the whole batch instead */
+    cudaEventRecord(m.evr0, m.st);
+    for (int i = 0; i < n; i++) {
+        if (m.run_launched >= m.run_cap) break;
+        if (run_program(m.run_launched == 0 ? m.p_run_first : m.p_run_next)) return -1;
+        m.run_launched++;
+    }
+    cudaEventRecord(m.evr1, m.st);
+    m.timing = timing;
+    return 0;
+}
+
+/* Waits for the queued frames; codes_out receives [frames_done, 37]. A run that hit
+ * END reports the END frame too (the reference drops it, voxtral_tts.c:307-311). */
+int utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms) {
+    Model &m = g_model;
+    if (!m.noise_all) return -1;
+    VB_CHECK(cudaMemcpyAsync(m.h_out, m.d_out, offsetof(DevOut, hidden), cudaMemcpyDeviceToHost, m.st));
+    VB_CHECK(cudaMemcpyAsync(&m.h_in->dyn, &m.d_in->dyn, sizeof(VbDyn), cudaMemcpyDeviceToHost, m.st));
+    VB_CHECK(cudaStreamSynchronize(m.st));
+    if (device_ms && cudaEventElapsedTime(device_ms, m.evr0, m.evr1) != cudaSuccess) *device_ms = -1.0f;
+    const int done = m.h_in->dyn.frame;
+    const int end = m.h_in->dyn.done;
+    if (frames_done) *frames_done = done;
+    if (hit_end) *hit_end = (end == 2) ? 1 : 0;
+    if (codes_out && done > 0)
+        VB_CHECK(cudaMemcpy(codes_out, m.codes_all, sizeof(int) * (size_t)done * VB200_CODES, cudaMemcpyDeviceToHost));
+    m.h_in->dyn.done = 0;
+    m.h_in->dyn.frame = 0;
+    VB_CHECK(cudaMemcpy(&m.d_in->dyn, &m.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice));
+    return check_status();
 }
 
 /* y[M,N] = x[M,K] . W[N,K]^T for host or device x / y (cudaPointerGetAttributes

@@ -37,8 +37,8 @@ struct DevIn {
 struct DevOut {
     int status;
     int codes[VB200_CODES + 3];
-    float hidden[VB200_DIM];
-    float vel[2][VB200_ACOUSTIC_DIM];
+    alignas(16) float hidden[VB200_DIM];   /* read back with 128-bit loads by the acoustic ops */
+    alignas(16) float vel[2][VB200_ACOUSTIC_DIM];
 };
 
 struct Program {
@@ -79,9 +79,13 @@ struct Model {
     VbOp *d_op1 = nullptr;     /* slots for single-op programs */
 
     bool tap_on = false;
-    Program p_llm, p_ac, p_frame, p_chain, p_pv;
+    bool ignore_end = false;      /* timed runs: an END code does not stop a device-resident run */
+    Program p_llm, p_ac, p_frame, p_chain, p_pv, p_run_first, p_run_next;
+    float *noise_all = nullptr;   /* device-resident run: [frames, 36] */
+    int *codes_all = nullptr;     /* [frames, 37] */
+    int run_cap = 0, run_launched = 0;
 
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, evr0 = nullptr, evr1 = nullptr;
     double ms_sum = 0.0;
     int ms_n = 0;
     bool timing = false;
@@ -107,6 +111,9 @@ int predict_velocity(float *out_v, const float *x_t, const float *hidden, float 
 int linear(float *y, const float *x, const uint16_t *W_host, int M, int K, int N, const void *W_gpu);
 int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N);
 int prefill(const float *embeds, int seq_len, int start_pos);
+int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);
+int utterance_run(int n);
+int utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
 
 } // namespace vb
 

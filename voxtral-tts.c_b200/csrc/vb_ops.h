@@ -20,7 +20,8 @@ enum VbOpType {
     VB_OP_AC_TOKENS = 5,   /* Euler update + build the six acoustic input rows */
     VB_OP_ARGMAX = 6,      /* masked first-maximum over semantic logits */
     VB_OP_FSQ = 7,         /* last Euler update + quantise the latent to codes */
-    VB_OP_EMBED = 8        /* next decoder input from 37 codes (sum of BF16 rows) */
+    VB_OP_EMBED = 8,       /* next decoder input from 37 codes (sum of BF16 rows) */
+    VB_OP_ADVANCE = 9      /* end of a device-resident frame: pos++, frame++, END check */
 };
 
 enum VbEpilogue {
@@ -38,8 +39,8 @@ enum VbOpFlags {
 struct VbDyn {
     int pos;           /* cache row of the token being decoded */
     int kv_max;        /* rows per layer in the cache */
-    int n_keys_cap;    /* guard: pos must be < this */
-    int pad;
+    int frame;         /* frames completed in a device-resident run (indexes noise / code arrays) */
+    int done;          /* set once an END code was produced: later launches of the run return at once */
 };
 
 struct VbOp {
