@@ -36,7 +36,7 @@ def test_rows_are_partitioned_exactly_once(pkg, N, K, M, sw, n_cta):
         sizes.append(r1 - r0)
         assert passes * seg >= K and (passes - 1) * seg < K
         assert seg % 8 == 0 and seg <= 4096
-        assert rpc * seg * 2 <= 24576 and rpc * M <= 32
+        assert rpc * seg * 2 <= 49152 and rpc * M <= 32 and rpc <= 8
         assert blocks == -(-(r1 - r0) // rpc) and chunks == blocks * passes
         if sw:
             assert r0 % 2 == 0 and r1 % 2 == 0 and rpc % 2 == 0

@@ -228,6 +228,7 @@ int vb200_sm_count(void) { return model().sm_count; }
 
 double vb200_engine_ms(int reset, int *n) {
     Model &m = model();
+    flush_launch_time();
     const double avg = m.ms_n > 0 ? m.ms_sum / m.ms_n : 0.0;
     if (n) *n = m.ms_n;
     if (reset) {

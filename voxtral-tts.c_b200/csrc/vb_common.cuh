@@ -71,6 +71,12 @@ VB_DEVINL void vb_bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes,
         : "memory");
 }
 
+/* Pulls a global range into L2 without a destination (16-byte aligned, size a
+ * multiple of 16). */
+VB_DEVINL void vb_prefetch_l2(const void *gmem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 VB_DEVINL void vb_named_bar(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }

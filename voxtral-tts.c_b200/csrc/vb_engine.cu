@@ -13,11 +13,16 @@
  *                shift, as in voxtral_tts_kernels.c:49-53,177-182).
  *   warp 16      epilogue. Adds the 16 per-warp partials of a chunk in fixed
  *                order (deterministic), applies bias / residual / SwiGLU
- *                (voxtral_tts_llm.c:245-263) and stores to global memory.
+ *                (voxtral_tts_llm.c:245-263) and stores to global memory. The
+ *                partials travel through their own small ring, so a ring slot
+ *                goes back to the producer as soon as its weights are in
+ *                registers.
  *   warp 17      producer. Lane 0 walks the whole program ahead of everyone and
- *                keeps the ring full with 1-D bulk (TMA) copies of weight rows;
- *                it never waits at a grid barrier, so HBM keeps streaming the
- *                next op's weights while the other warps synchronise.
+ *                keeps the ring full with 1-D bulk (TMA) copies of weight rows,
+ *                and further ahead pulls the coming chunks into L2
+ *                (cp.async.bulk.prefetch.L2); it never waits at a grid barrier,
+ *                so HBM keeps streaming the next op's weights while the other
+ *                warps synchronise.
  *
  * Every wait (mbarrier, grid barrier) is bounded; on expiry a status code is
  * stored, the CTA's abort flag is raised and all roles fall through to the exit
@@ -68,34 +73,83 @@ __device__ void grid_sync(Ctx &c) {
 /* ------------------------------------------------------------------ */
 /* GEMV: producer side                                                 */
 /* ------------------------------------------------------------------ */
-__device__ void gemv_produce(Ctx &c, const VbOp &op) {
-    const GemvPlan p = gemv_plan(op.N, op.K, op.M, op.epi, blockIdx.x, gridDim.x);
-    const size_t K = (size_t)op.K;
-    for (int ci = 0; ci < p.n_chunks; ci++) {
-        const int pass = ci / p.row_blocks, rb = ci % p.row_blocks;
-        const int row = p.r0 + rb * p.rows_per_chunk;
-        const int rc = min(p.rows_per_chunk, p.r1 - row);
-        const int k0 = pass * p.seg_cols;
-        const int klen = min(p.seg_cols, op.K - k0);
-        const unsigned slot = c.chunk_counter % kSlots;
-        const unsigned use = c.chunk_counter / kSlots;
-        if (!vb_mbar_wait(&c.s->empty[slot], (use & 1u) ^ 1u, &c.s->abort_flag)) {
-            if (!aborted(c)) raise_abort(c, VB_ERR_EMPTY_WAIT);
-            return;
+/* One thread feeds the ring. Everything that can be hoisted out of the per-chunk
+ * path is: a chunk costs a bounded wait, one expect_tx and one bulk copy (or one
+ * per row when K is cut into column passes). `issued_bytes` in shared memory tells
+ * the prefetch warp how far the loads have got. */
+__device__ void produce_all(Ctx &c) {
+    SmemLayout *s = c.s;
+    unsigned long long issued = 0;
+    for (int oi = 0; oi < c.a.n_ops; oi++) {
+        const VbOp &op = c.a.ops[oi];
+        if (op.type != VB_OP_GEMV) continue;
+        const GemvPlan p = gemv_plan(op.N, op.K, op.M, op.epi, blockIdx.x, gridDim.x);
+        if (p.n_chunks == 0) continue;
+        const size_t K = (size_t)op.K;
+        const int rpc = p.rows_per_chunk;
+        for (int pass = 0; pass < p.passes; pass++) {
+            const int k0 = pass * p.seg_cols;
+            const uint32_t row_bytes = (uint32_t)min(p.seg_cols, op.K - k0) * 2u;
+            const uint16_t *src = op.W + (size_t)p.r0 * K + k0;
+            int rows_left = p.r1 - p.r0;
+            for (int rb = 0; rb < p.row_blocks; rb++, src += (size_t)rpc * K, rows_left -= rpc) {
+                const int rc = min(rpc, rows_left);
+                const unsigned slot = c.chunk_counter % kSlots;
+                const unsigned use = c.chunk_counter / kSlots;
+                c.chunk_counter++;
+                if (!vb_mbar_wait(&s->empty[slot], (use & 1u) ^ 1u, &s->abort_flag)) {
+                    if (!aborted(c)) raise_abort(c, VB_ERR_EMPTY_WAIT);
+                    return;
+                }
+                unsigned char *dst = s->ring[slot];
+                const uint32_t bytes = row_bytes * (uint32_t)rc;
+                vb_mbar_arrive_expect_tx(&s->full[slot], bytes);
+                if (p.passes == 1) {
+                    vb_bulk_g2s(dst, src, bytes, &s->full[slot]);
+                } else {
+                    for (int i = 0; i < rc; i++)
+                        vb_bulk_g2s(dst + (size_t)i * p.seg_cols * 2, src + (size_t)i * K, row_bytes, &s->full[slot]);
+                }
+                issued += bytes;
+                *(volatile unsigned long long *)&s->issued_bytes = issued;
+            }
         }
-        unsigned char *dst = c.s->ring[slot];
-        const uint16_t *src = op.W + (size_t)row * K + k0;
-        if (p.passes == 1) {
-            const uint32_t bytes = (uint32_t)(rc * klen * 2);
-            vb_mbar_arrive_expect_tx(&c.s->full[slot], bytes);
-            vb_bulk_g2s(dst, src, bytes, &c.s->full[slot]);
-        } else {
-            const uint32_t seg = (uint32_t)(klen * 2);
-            vb_mbar_arrive_expect_tx(&c.s->full[slot], seg * rc);
-            for (int i = 0; i < rc; i++)
-                vb_bulk_g2s(dst + (size_t)i * p.seg_cols * 2, src + (size_t)i * K, seg, &c.s->full[slot]);
+    }
+    *(volatile unsigned long long *)&s->issued_bytes = ~0ull; /* done: nothing left to run ahead of */
+}
+
+/* L2 warm-up ahead of the ring. A second thread walks the same weights in the same
+ * order, as plain byte ranges (a CTA's rows of one matrix are contiguous), and keeps
+ * `lead` bytes ahead of the loads with cp.async.bulk.prefetch.L2. The ring alone
+ * holds about 4 us of HBM traffic; the prefetched window keeps HBM streaming through
+ * the longer stalls at op boundaries (grid barrier, prologue, attention). */
+__device__ void prefetch_all(Ctx &c) {
+    SmemLayout *s = c.s;
+    const unsigned long long lead = (unsigned long long)c.a.prefetch_chunks * kSlotBytes;
+    if (lead == 0) return;
+    unsigned long long ahead = 0;
+    for (int oi = 0; oi < c.a.n_ops; oi++) {
+        const VbOp &op = c.a.ops[oi];
+        if (op.type != VB_OP_GEMV) continue;
+        const GemvPlan p = gemv_plan(op.N, op.K, op.M, op.epi, blockIdx.x, gridDim.x);
+        if (p.n_chunks == 0) continue;
+        const unsigned char *ptr = (const unsigned char *)(op.W + (size_t)p.r0 * op.K);
+        size_t left = (size_t)(p.r1 - p.r0) * op.K * 2;
+        while (left > 0) {
+            long long t0 = clock64();
+            while (true) {
+                const unsigned long long done = *(volatile unsigned long long *)&s->issued_bytes;
+                if (done == ~0ull || aborted(c)) return;
+                if (ahead < done + lead) break;
+                if (clock64() - t0 > VB_WAIT_CYCLES) return; /* only a hint: give up quietly */
+                __nanosleep(64);
+            }
+            const uint32_t n = (uint32_t)(left < (size_t)kSlotBytes ? left : (size_t)kSlotBytes);
+            vb_prefetch_l2(ptr, n);
+            ptr += n;
+            left -= n;
+            ahead += n;
         }
-        c.chunk_counter++;
     }
 }
 
@@ -103,14 +157,18 @@ __device__ void gemv_produce(Ctx &c, const VbOp &op) {
 /* GEMV: compute warps                                                 */
 /* ------------------------------------------------------------------ */
 template <int M>
-__device__ void gemv_compute(Ctx &c, const VbOp &op) {
+__device__ void gemv_compute(Ctx &c, const VbOp &op, int op_index) {
     SmemLayout *s = c.s;
     const GemvPlan p = gemv_plan(op.N, op.K, M, op.epi, blockIdx.x, gridDim.x);
     const int K = op.K;
+    float(*red)[kMaxM] = s->red[op_index & 1];
+    const bool norm_from_regs = op.norm_w && p.passes == 1;
 
-    /* RMSNorm prologue (voxtral_tts_kernels.c:333-349): 1/sqrt(mean(x^2)+eps) per row,
-     * recomputed by every CTA from the L2-resident activations. */
-    if (op.norm_w) {
+    /* RMSNorm prologue (voxtral_tts_kernels.c:333-349) when K needs several column
+     * passes: the sum of squares is taken over the whole row first. With a single
+     * pass the CTA's warps together hold the whole row in registers and the sum
+     * comes from there (below), saving one trip to L2. */
+    if (op.norm_w && !norm_from_regs) {
         float ss[M];
 #pragma unroll
         for (int m = 0; m < M; m++) ss[m] = 0.0f;
@@ -124,19 +182,10 @@ __device__ void gemv_compute(Ctx &c, const VbOp &op) {
 #pragma unroll
         for (int m = 0; m < M; m++) {
             float t = vb_warp_sum(ss[m]);
-            if (c.lane == 0) s->red[c.warp][m] = t;
-        }
-        vb_named_bar(2, kComputeThreads);
-        if (c.tid < M) {
-            float t = 0.0f;
-            for (int w = 0; w < kComputeWarps; w++) t += s->red[w][c.tid];
-            s->rinv[c.tid] = 1.0f / sqrtf(t / (float)K + op.eps);
+            if (c.lane == 0) red[c.warp][m] = t;
         }
         vb_named_bar(2, kComputeThreads);
     }
-
-    const int n_slices_full = (p.seg_cols + kSliceCols - 1) / kSliceCols;
-    (void)n_slices_full;
 
     for (int pass = 0; pass < p.passes; pass++) {
         const int k0 = pass * p.seg_cols;
@@ -145,6 +194,7 @@ __device__ void gemv_compute(Ctx &c, const VbOp &op) {
         const bool active = col < klen;
 
         float xr[M][8];
+        float g[8];
         if (active) {
 #pragma unroll
             for (int m = 0; m < M; m++) {
@@ -154,64 +204,93 @@ __device__ void gemv_compute(Ctx &c, const VbOp &op) {
                 xr[m][4] = b.x; xr[m][5] = b.y; xr[m][6] = b.z; xr[m][7] = b.w;
             }
             if (op.norm_w) {
-                float g[8];
                 const float4 ga = __ldg(reinterpret_cast<const float4 *>(op.norm_w + k0 + col));
                 const float4 gb = __ldg(reinterpret_cast<const float4 *>(op.norm_w + k0 + col + 4));
                 g[0] = ga.x; g[1] = ga.y; g[2] = ga.z; g[3] = ga.w;
                 g[4] = gb.x; g[5] = gb.y; g[6] = gb.z; g[7] = gb.w;
-#pragma unroll
-                for (int m = 0; m < M; m++) {
-                    const float ri = s->rinv[m];
-#pragma unroll
-                    for (int j = 0; j < 8; j++) xr[m][j] = xr[m][j] * ri * g[j];
-                }
             }
         } else {
 #pragma unroll
             for (int m = 0; m < M; m++)
 #pragma unroll
                 for (int j = 0; j < 8; j++) xr[m][j] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) g[j] = 0.0f;
+        }
+        if (norm_from_regs) {
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                float t = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) t = fmaf(xr[m][j], xr[m][j], t);
+                t = vb_warp_sum(t);
+                if (c.lane == 0) red[c.warp][m] = t;
+            }
+            vb_named_bar(2, kComputeThreads);
+        }
+        if (op.norm_w) {
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                float t = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kComputeWarps; w++) t += red[w][m];
+                const float ri = 1.0f / sqrtf(t / (float)K + op.eps);
+#pragma unroll
+                for (int j = 0; j < 8; j++) xr[m][j] = xr[m][j] * ri * g[j];
+            }
         }
 
         const int pitch = p.seg_cols * 2; /* bytes between rows inside a slot */
         for (int rb = 0; rb < p.row_blocks; rb++) {
             const int row = p.r0 + rb * p.rows_per_chunk;
             const int rc = min(p.rows_per_chunk, p.r1 - row);
-            const unsigned slot = c.chunk_counter % kSlots;
-            const unsigned use = c.chunk_counter / kSlots;
-            c.chunk_counter++;
+            const unsigned chunk = c.chunk_counter++;
+            const unsigned slot = chunk % kSlots, use = chunk / kSlots;
+            const unsigned pslot = chunk % kPartSlots, puse = chunk / kPartSlots;
             if (!vb_mbar_wait(&s->full[slot], use & 1u, &s->abort_flag)) {
                 if (!aborted(c)) raise_abort(c, VB_ERR_FULL_WAIT);
                 return;
             }
-            float acc[kMaxRowsPerChunk * M];
+            constexpr int RPC = rows_cap(M);
+            float acc[RPC * M];
 #pragma unroll
-            for (int v = 0; v < kMaxRowsPerChunk * M; v++) acc[v] = 0.0f;
+            for (int v = 0; v < RPC * M; v++) acc[v] = 0.0f;
             if (active) {
                 const unsigned char *base = s->ring[slot] + (size_t)col * 2;
+                /* rows past the end of a ragged last chunk re-read its last row; their
+                 * sums are ignored by the epilogue, and the loads stay unconditional */
+                uint4 wv[RPC];
 #pragma unroll
-                for (int i = 0; i < kMaxRowsPerChunk; i++) {
-                    if (i < rc) {
-                        const uint4 wv = *reinterpret_cast<const uint4 *>(base + (size_t)i * pitch);
-                        float wf[8];
-                        wf[0] = vb_bf16_lo(wv.x); wf[1] = vb_bf16_hi(wv.x);
-                        wf[2] = vb_bf16_lo(wv.y); wf[3] = vb_bf16_hi(wv.y);
-                        wf[4] = vb_bf16_lo(wv.z); wf[5] = vb_bf16_hi(wv.z);
-                        wf[6] = vb_bf16_lo(wv.w); wf[7] = vb_bf16_hi(wv.w);
+                for (int i = 0; i < RPC; i++)
+                    wv[i] = *reinterpret_cast<const uint4 *>(base + (size_t)min(i, rc - 1) * pitch);
 #pragma unroll
-                        for (int m = 0; m < M; m++) {
-                            float a = 0.0f;
+                for (int i = 0; i < RPC; i++) {
+                    float wf[8];
+                    wf[0] = vb_bf16_lo(wv[i].x); wf[1] = vb_bf16_hi(wv[i].x);
+                    wf[2] = vb_bf16_lo(wv[i].y); wf[3] = vb_bf16_hi(wv[i].y);
+                    wf[4] = vb_bf16_lo(wv[i].z); wf[5] = vb_bf16_hi(wv[i].z);
+                    wf[6] = vb_bf16_lo(wv[i].w); wf[7] = vb_bf16_hi(wv[i].w);
 #pragma unroll
-                            for (int j = 0; j < 8; j++) a = fmaf(wf[j], xr[m][j], a);
-                            acc[i * M + m] = a;
-                        }
+                    for (int m = 0; m < M; m++) {
+                        float a = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) a = fmaf(wf[j], xr[m][j], a);
+                        acc[i * M + m] = a;
                     }
                 }
             }
-            const int idx = vb_warp_multi_sum<kMaxRowsPerChunk * M>(acc, c.lane);
-            if (idx < kMaxRowsPerChunk * M) s->part[slot][c.warp][idx] = acc[0];
+            /* the weights are in registers: hand the ring slot back to the producer */
             __syncwarp();
-            if (c.lane == 0) vb_mbar_arrive(&s->done[slot]);
+            if (c.lane == 0) vb_mbar_arrive(&s->empty[slot]);
+
+            const int idx = vb_warp_multi_sum<RPC * M>(acc, c.lane);
+            if (!vb_mbar_wait(&s->pfree[pslot], (puse & 1u) ^ 1u, &s->abort_flag)) {
+                if (!aborted(c)) raise_abort(c, VB_ERR_DONE_WAIT);
+                return;
+            }
+            if (idx < RPC * M) s->part[pslot][c.warp][idx] = acc[0];
+            __syncwarp();
+            if (c.lane == 0) vb_mbar_arrive(&s->pdone[pslot]);
         }
     }
 }
@@ -225,29 +304,45 @@ __device__ void gemv_epilogue(Ctx &c, const VbOp &op) {
     const GemvPlan p = gemv_plan(op.N, op.K, M, op.epi, blockIdx.x, gridDim.x);
     const int v = c.lane;
     const int i = v / M, m = v % M;
+    /* op fields in registers: the waits below are compiler barriers for memory */
+    const int epi = op.epi, ldy = op.ldy, K = op.K;
+    float *const y = op.y;
+    float *const tap = op.tap;
+    const float *const bias = op.bias;
+    const float *const res = op.res;
+
+    /* Residual values of this CTA's rows, fetched once up front instead of one L2
+     * round trip per chunk on the epilogue's critical path. */
+    const int n_rows = p.r1 - p.r0;
+    const bool res_cached = epi == VB_EPI_ADD && n_rows * M <= kResFloats;
+    if (res_cached) {
+        for (int e = c.lane; e < n_rows * M; e += 32)
+            s->resv[e] = vb_ldcg(res + (size_t)(e % M) * ldy + p.r0 + e / M);
+        __syncwarp();
+    }
+
     for (int pass = 0; pass < p.passes; pass++) {
-        const int klen = min(p.seg_cols, op.K - pass * p.seg_cols);
+        const int klen = min(p.seg_cols, K - pass * p.seg_cols);
         const int n_slices = min(kComputeWarps, (klen + kSliceCols - 1) / kSliceCols);
         for (int rb = 0; rb < p.row_blocks; rb++) {
             const int row0 = p.r0 + rb * p.rows_per_chunk;
             const int rc = min(p.rows_per_chunk, p.r1 - row0);
-            const unsigned slot = c.chunk_counter % kSlots;
-            const unsigned use = c.chunk_counter / kSlots;
-            c.chunk_counter++;
-            if (!vb_mbar_wait(&s->done[slot], use & 1u, &s->abort_flag)) {
+            const unsigned chunk = c.chunk_counter++;
+            const unsigned pslot = chunk % kPartSlots, puse = chunk / kPartSlots;
+            if (!vb_mbar_wait(&s->pdone[pslot], puse & 1u, &s->abort_flag)) {
                 if (!aborted(c)) raise_abort(c, VB_ERR_DONE_WAIT);
                 return;
             }
-            const bool mine = (v < kMaxRowsPerChunk * M) && (i < rc);
+            const bool mine = (v < rows_cap(M) * M) && (i < rc);
             float val = 0.0f;
             if (mine) {
-                for (int w = 0; w < n_slices; w++) val += s->part[slot][w][v];
+                for (int w = 0; w < n_slices; w++) val += s->part[pslot][w][v];
             }
             __syncwarp();
-            if (c.lane == 0) vb_mbar_arrive(&s->empty[slot]);
+            if (c.lane == 0) vb_mbar_arrive(&s->pfree[pslot]);
 
+            const int yi = (rb * p.rows_per_chunk + i) * M + m;
             if (p.passes > 1) {
-                const int yi = (rb * p.rows_per_chunk + i) * M + m;
                 if (mine) {
                     if (pass > 0) val += s->yacc[yi];
                     if (pass < p.passes - 1) s->yacc[yi] = val;
@@ -256,31 +351,31 @@ __device__ void gemv_epilogue(Ctx &c, const VbOp &op) {
             }
 
             const int row = row0 + i;
-            if (op.epi == VB_EPI_SWIGLU) {
+            if (epi == VB_EPI_SWIGLU) {
                 /* gate rows are even, up rows odd; the up value sits M lanes higher */
                 const float upv = __shfl_down_sync(0xffffffffu, val, M);
                 if (mine && (i & 1) == 0) {
                     const float g = val / (1.0f + expf(-val));
                     const float r = g * upv;
-                    const size_t o = (size_t)m * op.ldy + (row >> 1);
-                    op.y[o] = r;
-                    if (op.tap) op.tap[o] = r;
+                    const size_t o = (size_t)m * ldy + (row >> 1);
+                    y[o] = r;
+                    if (tap) tap[o] = r;
                 }
             } else if (mine) {
-                const size_t o = (size_t)m * op.ldy + row;
+                const size_t o = (size_t)m * ldy + row;
                 float r = val;
-                if (op.bias) r += __ldg(op.bias + row);
-                if (op.epi == VB_EPI_ADD) r = vb_ldcg(op.res + o) + r;
-                op.y[o] = r;
-                if (op.tap) op.tap[o] = r;
+                if (bias) r += __ldg(bias + row);
+                if (epi == VB_EPI_ADD) r = (res_cached ? s->resv[yi] : vb_ldcg(res + o)) + r;
+                y[o] = r;
+                if (tap) tap[o] = r;
             }
         }
     }
 }
 
 template <int M>
-__device__ void gemv_work(Ctx &c, const VbOp &op) {
-    if (c.warp < kComputeWarps) gemv_compute<M>(c, op);
+__device__ void gemv_work(Ctx &c, const VbOp &op, int op_index) {
+    if (c.warp < kComputeWarps) gemv_compute<M>(c, op, op_index);
     else gemv_epilogue<M>(c, op);
 }
 
@@ -478,10 +573,10 @@ __device__ void op_norm(Ctx &c, const VbOp &op) {
         float ss = 0.0f;
         for (int i = c.tid; i < op.K; i += kComputeThreads) { const float v = vb_ldcg(x + i); ss += v * v; }
         ss = vb_warp_sum(ss);
-        if (c.lane == 0) s->red[c.warp][0] = ss;
+        if (c.lane == 0) s->red[0][c.warp][0] = ss;
         vb_named_bar(2, kComputeThreads);
         float t = 0.0f;
-        for (int w = 0; w < kComputeWarps; w++) t += s->red[w][0];
+        for (int w = 0; w < kComputeWarps; w++) t += s->red[0][w][0];
         const float inv = 1.0f / sqrtf(t / (float)op.K + op.eps);
         for (int i = c.tid; i < op.K; i += kComputeThreads)
             op.y[(size_t)m * op.ldy + i] = vb_ldcg(x + i) * inv * __ldg(op.norm_w + i);
@@ -566,12 +661,12 @@ __device__ void op_argmax(Ctx &c, const VbOp &op) {
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (c.lane == 0) { s->red[c.warp][0] = best; s->red[c.warp][1] = __int_as_float(bi); }
+    if (c.lane == 0) { s->red[0][c.warp][0] = best; s->red[0][c.warp][1] = __int_as_float(bi); }
     vb_named_bar(2, kComputeThreads);
     if (c.tid == 0) {
         for (int w = 0; w < kComputeWarps; w++) {
-            const float ov = s->red[w][0];
-            const int oi = __float_as_int(s->red[w][1]);
+            const float ov = s->red[0][w][0];
+            const int oi = __float_as_int(s->red[0][w][1]);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
         ((int *)op.p2)[0] = bi;
@@ -664,36 +759,37 @@ __global__ void __launch_bounds__(kThreads, 1) vb_engine_kernel(EngineArgs a) {
     if (c.tid == 0) {
         for (int i = 0; i < kSlots; i++) {
             vb_mbar_init(&s->full[i], 1);
-            vb_mbar_init(&s->empty[i], 1);
-            vb_mbar_init(&s->done[i], kComputeWarps);
+            vb_mbar_init(&s->empty[i], kComputeWarps);
+        }
+        for (int i = 0; i < kPartSlots; i++) {
+            vb_mbar_init(&s->pdone[i], kComputeWarps);
+            vb_mbar_init(&s->pfree[i], 1);
         }
         s->abort_flag = 0;
+        s->issued_bytes = 0;
         s->last_flag = 0;
         vb_mbar_init_fence();
     }
     __syncthreads();
 
     if (c.warp == kProducerWarp) {
-        if (c.lane == 0) {
-            for (int oi = 0; oi < a.n_ops && !aborted(c); oi++) {
-                const VbOp &op = a.ops[oi];
-                if (op.type == VB_OP_GEMV) gemv_produce(c, op);
-            }
-        }
+        if (c.lane == 0) produce_all(c);
+    } else if (c.warp == kPrefetchWarp) {
+        if (c.lane == 0) prefetch_all(c);
     } else {
         for (int oi = 0; oi < a.n_ops && !aborted(c); oi++) {
             const VbOp &op = a.ops[oi];
             switch (op.type) {
             case VB_OP_GEMV:
                 switch (op.M) {
-                case 1: gemv_work<1>(c, op); break;
-                case 2: gemv_work<2>(c, op); break;
-                case 3: gemv_work<3>(c, op); break;
-                case 4: gemv_work<4>(c, op); break;
-                case 5: gemv_work<5>(c, op); break;
-                case 6: gemv_work<6>(c, op); break;
-                case 7: gemv_work<7>(c, op); break;
-                case 8: gemv_work<8>(c, op); break;
+                case 1: gemv_work<1>(c, op, oi); break;
+                case 2: gemv_work<2>(c, op, oi); break;
+                case 3: gemv_work<3>(c, op, oi); break;
+                case 4: gemv_work<4>(c, op, oi); break;
+                case 5: gemv_work<5>(c, op, oi); break;
+                case 6: gemv_work<6>(c, op, oi); break;
+                case 7: gemv_work<7>(c, op, oi); break;
+                case 8: gemv_work<8>(c, op, oi); break;
                 default: if (c.tid == 0) raise_abort(c, VB_ERR_BAD_OP); break;
                 }
                 break;

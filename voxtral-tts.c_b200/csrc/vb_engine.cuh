@@ -15,35 +15,44 @@ namespace vb {
 constexpr int kComputeWarps = 16;                 /* FMA warps; each owns 256-column slices */
 constexpr int kEpilogueWarp = kComputeWarps;      /* cross-warp sum, epilogue, global store */
 constexpr int kProducerWarp = kComputeWarps + 1;  /* lane 0 issues the bulk copies */
-constexpr int kThreads = (kComputeWarps + 2) * 32;
+constexpr int kPrefetchWarp = kComputeWarps + 2;  /* lane 0 warms L2 ahead of the ring */
+constexpr int kThreads = (kComputeWarps + 3) * 32;
 constexpr int kComputeThreads = kComputeWarps * 32;
 constexpr int kWorkThreads = kComputeThreads + 32; /* compute + epilogue: named barrier 1 */
 
-constexpr int kSlots = 7;                  /* ring depth */
-constexpr int kSlotBytes = 24576;          /* 4 rows of K=3072, 3 of K=4096 */
-constexpr int kMaxRowsPerChunk = 4;
+constexpr int kSlots = 4;                  /* ring depth */
+constexpr int kSlotBytes = 49152;          /* 8 rows of K=3072, 6 of K=4096 */
+constexpr int kPartSlots = 6;              /* ring of per-chunk partial sums (warps -> epilogue) */
+constexpr int kPrefetchChunks = 0;         /* L2 warm-up distance in chunks; 0 = off (measured: no gain, see profiles) */
+constexpr int kResFloats = 256;            /* residual values cached per op by the epilogue */
+constexpr int kMaxRowsPerChunk = 8;        /* rows a warp reduces together: more rows per barrier round trip */
 constexpr int kMaxM = 8;
-constexpr int kMaxV = kMaxRowsPerChunk * kMaxM; /* partial sums per warp per chunk */
+constexpr int kMaxV = 32;                  /* partial sums per warp per chunk: one per epilogue lane */
+/* Rows per chunk for M activation rows: rows x M partial sums must fit the 32 epilogue lanes. */
+__host__ __device__ constexpr int rows_cap(int M) { return kMaxV / M < kMaxRowsPerChunk ? kMaxV / M : kMaxRowsPerChunk; }
 constexpr int kSliceCols = 256;            /* columns one warp covers: 32 lanes x 8 bf16 */
 constexpr int kMaxSegCols = kComputeWarps * kSliceCols; /* 4096: widest K handled in one pass */
-constexpr int kYaccFloats = 2048;          /* cross-pass accumulators (rows x M) */
+constexpr int kYaccFloats = 1024;          /* cross-pass accumulators (rows x M) */
 constexpr int kAttnSubsets = 4;            /* key subsets per head inside a CTA */
 constexpr int kHeadDim = 128;
 
 struct SmemLayout {
     alignas(128) unsigned char ring[kSlots][kSlotBytes];
-    float part[kSlots][kComputeWarps][kMaxV];
+    float part[kPartSlots][kComputeWarps][kMaxV];
     float yacc[kYaccFloats];
     float attn_o[kAttnSubsets][4][kHeadDim];
     float attn_ml[kAttnSubsets][4][2];
     float qs[4][kHeadDim];
     float cs[kHeadDim];          /* (cos, sin) pairs for the current position */
-    float red[kComputeWarps][kMaxM];
+    float red[2][kComputeWarps][kMaxM];   /* double-buffered by op parity */
+    float resv[kResFloats];
     float rinv[kMaxM];
     float xs[64];                /* small per-op vector (latent, 36 wide) */
     uint64_t full[kSlots];
     uint64_t empty[kSlots];
-    uint64_t done[kSlots];
+    uint64_t pdone[kPartSlots];
+    uint64_t pfree[kPartSlots];
+    unsigned long long issued_bytes;   /* weight bytes the producer has requested so far */
     int abort_flag;
     int last_flag;
 };
@@ -55,6 +64,7 @@ struct EngineArgs {
     unsigned *bar_counter;   /* grid barrier arrivals, zero between launches */
     unsigned *exit_counter;  /* CTAs that finished; the last one re-zeroes both */
     int *status;             /* VbStatus, sticky until the host clears it */
+    int prefetch_chunks;     /* L2 prefetch distance of the producer, in chunks (0 = off) */
 };
 
 /* Row/column decomposition of one GEMV op for one CTA. Host code uses the same
@@ -71,9 +81,11 @@ struct GemvPlan {
 __host__ __device__ inline GemvPlan gemv_plan(int N, int K, int M, int epi, int cta, int n_cta) {
     GemvPlan p;
     int unit = (epi == VB_EPI_SWIGLU) ? 2 : 1;
-    long long U = N / unit;
-    p.r0 = (int)(U * cta / n_cta) * unit;
-    p.r1 = (int)(U * (cta + 1) / n_cta) * unit;
+    /* balanced split without 64-bit division: the first `rem` CTAs take one unit more */
+    const unsigned U = (unsigned)(N / unit), nc = (unsigned)n_cta, q = U / nc, rem = U - q * nc;
+    const unsigned c0 = (unsigned)cta, u0 = c0 * q + (c0 < rem ? c0 : rem);
+    p.r0 = (int)u0 * unit;
+    p.r1 = (int)(u0 + q + (c0 < rem ? 1u : 0u)) * unit;
     p.passes = (K + kMaxSegCols - 1) / kMaxSegCols;
     if (p.passes <= 1) {
         p.passes = 1;
@@ -84,8 +96,7 @@ __host__ __device__ inline GemvPlan gemv_plan(int N, int K, int M, int epi, int 
         p.passes = (K + p.seg_cols - 1) / p.seg_cols;
     }
     int rc = kSlotBytes / (p.seg_cols * 2);
-    if (rc > kMaxRowsPerChunk) rc = kMaxRowsPerChunk;
-    if (rc * M > kMaxV) rc = kMaxV / M;
+    if (rc > rows_cap(M)) rc = rows_cap(M);
     if (unit == 2) rc &= ~1;
     if (rc < 1) rc = 1;
     p.rows_per_chunk = rc;

@@ -90,6 +90,7 @@ int model_init(int kv_cache_max) {
         fprintf(stderr, "voxtral_b200: frame kernel does not fit on this device\n");
         return -1;
     }
+    if (getenv("VB200_PREFETCH")) m.prefetch_chunks = atoi(getenv("VB200_PREFETCH"));
     const char *cta_env = getenv("VB200_CTAS");
     if (cta_env && atoi(cta_env) > 0 && atoi(cta_env) < m.n_cta) m.n_cta = atoi(cta_env);
 
@@ -521,23 +522,38 @@ int model_rebuild_programs() {
 /* ------------------------------------------------------------------ */
 /* running                                                             */
 /* ------------------------------------------------------------------ */
+/* Per-launch device time (only while vb200_engine_ms has switched timing on): the
+ * event pair of the previous launch is read before the next one reuses it. */
+void flush_launch_time() {
+    Model &m = g_model;
+    if (!m.time_pending) return;
+    m.time_pending = false;
+    float ms = 0.0f;
+    if (cudaEventSynchronize(m.ev1) == cudaSuccess && cudaEventElapsedTime(&ms, m.ev0, m.ev1) == cudaSuccess) {
+        m.ms_sum += ms;
+        m.ms_n++;
+    }
+}
+
 static int launch(const VbOp *d_ops, int n) {
     Model &m = g_model;
     EngineArgs a;
     a.ops = d_ops; a.n_ops = n; a.dyn = &m.d_in->dyn;
     a.bar_counter = m.bar; a.exit_counter = m.exitc; a.status = &m.d_out->status;
-    if (m.timing) cudaEventRecord(m.ev0, m.st);
+    a.prefetch_chunks = m.prefetch_chunks;
+    if (m.timing) {
+        flush_launch_time();
+        cudaEventRecord(m.ev0, m.st);
+    }
     VB_CHECK(engine_launch(a, m.n_cta, m.st));
-    if (m.timing) cudaEventRecord(m.ev1, m.st);
+    if (m.timing) {
+        cudaEventRecord(m.ev1, m.st);
+        m.time_pending = true;
+    }
     return 0;
 }
 
-static void account_time() {
-    Model &m = g_model;
-    if (!m.timing) return;
-    float ms = 0.0f;
-    if (cudaEventElapsedTime(&ms, m.ev0, m.ev1) == cudaSuccess) { m.ms_sum += ms; m.ms_n++; }
-}
+static void account_time() { flush_launch_time(); }
 
 /* Reads back the status word after a synchronised launch; a non-zero status
  * means a bounded wait ran out inside the kernel. The counters are re-zeroed so

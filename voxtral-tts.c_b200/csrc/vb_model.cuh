@@ -79,6 +79,7 @@ struct Model {
     VbOp *d_op1 = nullptr;     /* slots for single-op programs */
 
     bool tap_on = false;
+    int prefetch_chunks = kPrefetchChunks;   /* VB200_PREFETCH overrides */
     bool ignore_end = false;      /* timed runs: an END code does not stop a device-resident run */
     Program p_llm, p_ac, p_frame, p_chain, p_pv, p_run_first, p_run_next;
     float *noise_all = nullptr;   /* device-resident run: [frames, 36] */
@@ -88,7 +89,7 @@ struct Model {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, evr0 = nullptr, evr1 = nullptr;
     double ms_sum = 0.0;
     int ms_n = 0;
-    bool timing = false;
+    bool timing = false, time_pending = false;
     int last_status = 0;
 };
 
@@ -101,6 +102,7 @@ int model_upload_acoustic(const vb200_acoustic_weights_t *w);
 int model_upload_audio_embed(const uint16_t *table, int rows);
 int model_rebuild_programs();
 
+void flush_launch_time();
 int run_program(const Program &p);   /* launch + status */
 int run_ops(const std::vector<VbOp> &ops);
 
