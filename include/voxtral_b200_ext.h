@@ -66,6 +66,29 @@ int vb200_kv_read(int layer, int pos0, int n, float *k_rows, float *v_rows);
 int vb200_tap_enable(int on);
 int vb200_tap_read(float *out);
 
+/* y[seq,out] = x[seq,in] . W[out,in]^T like tts_cuda_linear_bf16, for callers that may
+ * not allocate device memory at the time of the call: plugins inside a host that owns
+ * the whole GPU heap, real-time audio threads that cannot afford cudaMalloc's implicit
+ * synchronisation, code that must leave a tracked allocator untouched. No counterpart
+ * in the reference. It calls no cudaMalloc / cudaFree (nor anything that does) and
+ * does not need tts_cuda_init. All three pointers are device memory supplied by the
+ * caller. The few hundred bytes per row block that the kernel needs besides its
+ * operands (op descriptors, barrier counters, status) live in a fixed 10 KB device
+ * array inside the library, present on every GPU that loads it until exit.
+ *  - Limit: seq_len <= 512 per call (64 descriptors of 8 rows); more returns -2 and
+ *    does nothing. Other failures return -1; 0 means the work was queued.
+ *  - Asynchronous on the default stream; tts_cuda_sync() (or any device
+ *    synchronisation) before reading y. vb200_linear_bf16_static_status() then gives
+ *    the kernel's status word (0 = fine).
+ *  - The first call on each device looks up the array's address and zeroes it with
+ *    synchronous runtime calls: make that first call before starting a stream capture.
+ *  - One array per device is shared by all calls and keeps what the last call left
+ *    (the counters are re-zeroed by every launch); two calls in flight on the same
+ *    GPU at once would race on it, so issue them from one thread / one stream. */
+int vb200_linear_bf16_static(float *d_y, const float *d_x, const uint16_t *d_W, int seq_len,
+                             int in_dim, int out_dim);
+int vb200_linear_bf16_static_status(void);
+
 /* How the frame kernel splits a [N,K] matrix product with M activation rows
  * over `n_cta` CTAs (host logic, usable without a GPU). out[0..6] = first row,
  * end row, column passes, columns per pass, rows per chunk, row blocks, chunks of

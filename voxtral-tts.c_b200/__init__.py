@@ -95,6 +95,8 @@ def lib():
         "vb200_tap_enable": (C.c_int, [C.c_int]),
         "vb200_tap_read": (C.c_int, [C.c_void_p]),
         "vb200_debug_gemv_plan": (C.c_int, [C.c_int] * 6 + [i32p]),
+        "vb200_linear_bf16_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+        "vb200_linear_bf16_static_status": (C.c_int, []),
         "vb200_last_status": (C.c_int, []),
         "vb200_sm_count": (C.c_int, []),
         "vb200_engine_ms": (C.c_double, [C.c_int, i32p]),
