@@ -213,6 +213,32 @@ def cpu_reference(pkg, model, kv_prefix, first_embed, noise, n_frames, budget_s)
             "ms_per_frame": 1000.0 / fps}
 
 
+def micro(args):
+    """One GEMV op of the frame kernel through tts_cuda_linear_bf16 on device buffers:
+    y[m,n] = x[m,k] . W[n,k]^T. Not the headline metric: a small, self-contained case for profiling."""
+    pkg = load_package()
+    eng = pkg.Engine(kv_cache_max=64)
+    L = eng.L
+    M, K, N = args.m, args.k, args.n
+    x = pkg.synth_f32((M, K), 1, "micro.x")
+    W = pkg.synth_bf16((N, K), 2, "micro.W")
+    dx, dW, dy = pkg.DeviceBuffer(x), pkg.DeviceBuffer(W), pkg.DeviceBuffer(nbytes=M * N * 4)
+    for _ in range(3):
+        L.tts_cuda_linear_bf16(dy.ptr, dx.ptr, None, M, K, N, dW.ptr)
+    L.tts_cuda_sync()
+    eng.engine_ms(reset=True)
+    for _ in range(args.reps):
+        L.tts_cuda_linear_bf16(dy.ptr, dx.ptr, None, M, K, N, dW.ptr)
+    L.tts_cuda_sync()
+    ms, n = eng.engine_ms()
+    peak, src = measured_hbm_peak()
+    gbs = 2.0 * N * K / (ms / 1000.0) / 1e9
+    print(json.dumps({"micro": "gemv", "m": M, "k": K, "n": N, "launches": n, "us_per_launch": ms * 1000.0,
+                      "weight_bytes": 2 * N * K, "achieved_gbs": gbs, "frac_of_peak": gbs / peak, "peak_source": src,
+                      "status": L.vb200_last_status()}))
+    eng.close()
+
+
 # ----------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -223,7 +249,15 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="frames of the host-ABI measurement (default: min(steps, 64))")
     ap.add_argument("--cpu-budget", type=float, default=25.0, help="seconds of CPU-baseline frames")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default="", choices=["", "gemv"],
+                    help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--n", type=int, default=32768)
+    ap.add_argument("--reps", type=int, default=8)
     args = ap.parse_args()
+    if args.micro:
+        return micro(args)
     K, W = max(args.steps, 1), max(args.warmup, 0)
 
     rank = int(os.environ.get("RANK", "0"))
