@@ -68,7 +68,8 @@ def test_linear_device_pointers(pkg, eng, oracle, M, K, N):
     y = dy.get((M, N))
     ref = oracle.linear(x, W)
     assert eng.L.vb200_last_status() == 0
-    assert rel_l2(y, ref) < 2e-6, rel_l2(y, ref)
+    # M >= 2 runs on the tensor cores: fp32 rows as three BF16 terms, TMEM accumulation order
+    assert rel_l2(y, ref) < (2e-6 if M == 1 else 2e-5), rel_l2(y, ref)
     assert close_like_reference_harness(ref, y, 1e-3, 1e-4)   # test_kernels.c:416
     for d in (dx, dW, dy):
         d.free()
@@ -82,7 +83,7 @@ def test_linear_host_pointers_and_weight_upload(pkg, eng, oracle):
     from ctypes import c_void_p
     eng.L.tts_cuda_linear_bf16(y.ctypes.data_as(c_void_p), x.ctypes.data_as(c_void_p),
                                W.ctypes.data_as(c_void_p), 2, 512, 96, None)
-    assert rel_l2(y, oracle.linear(x, W)) < 2e-6
+    assert rel_l2(y, oracle.linear(x, W)) < 2e-5
 
 
 def test_linear_empty(pkg, eng):

@@ -33,7 +33,8 @@ def test_static_scratch_linear_matches_regular_entry_point(pkg, M, K, N):
         assert L.vb200_linear_bf16_static(d_new.ptr, dx.ptr, dW.ptr, M, K, N) == 0
         got = d_new.get((M, N))                # synchronises
         assert L.vb200_linear_bf16_static_status() == 0
-        assert rel_l2(got, ref) < 2e-6, (call, rel_l2(got, ref))
+        # the regular entry point runs M >= 2 on the tensor cores, this one on the streaming kernel
+        assert rel_l2(got, ref) < 2e-5, (call, rel_l2(got, ref))
     for d in (dx, dW, d_ref, d_new):
         d.free()
 

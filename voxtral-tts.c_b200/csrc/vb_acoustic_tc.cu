@@ -1,0 +1,327 @@
+/*
+ * vb_acoustic_tc.cu - the acoustic frame on the tensor-core path.
+ *
+ * tts_acoustic_forward (voxtral_tts_acoustic.c:268-373): semantic head + argmax, then 7
+ * Euler steps; both guidance branches of a step run together as six token rows
+ * (voxtral_tts_acoustic.c:198-212, :345-348), so every layer matrix is streamed once per
+ * step by the tcgen05 GEMM (vb_tc.cu). Around the GEMMs sit small kernels: token
+ * build + Euler update, 3-token attention, split-K reduction + residual + RMSNorm +
+ * BF16 term split ("prepare"), velocity head, FSQ. The sequence (about 200 launches) is
+ * captured once as a CUDA graph and replayed per frame.
+ */
+#include "vb_model.cuh"
+#include "vb_tc.cuh"
+#include "vb_common.cuh"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace vb {
+
+static const int D = VB200_DIM, QD = VB200_Q_DIM, KVD = VB200_KV_DIM, HID = VB200_HIDDEN;
+static const int QKV = QD + 2 * KVD;
+static const int A = VB200_ACOUSTIC_DIM;
+static const int ROWS = 6;     /* 2 guidance branches x 3 tokens */
+
+struct AcTc {
+    bool ready = false;
+    TcWeight wqkv[VB200_AC_LAYERS], wo[VB200_AC_LAYERS], w13[VB200_AC_LAYERS], w2[VB200_AC_LAYERS];
+    TcActs aD, aQ, aH;
+    uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
+    float *part = nullptr;      /* split-K partials [splits][6][N] */
+    int s_qkv = 1, s_wo = 1, s_w2 = 1;
+};
+static AcTc g_ac;
+void acoustic_tc_drop_graphs();
+
+/* ---- small kernels ---- */
+
+__device__ __forceinline__ float euler_step(float x, float vc, float vu, float alpha, float dt) {
+    /* v = alpha*vc + (1-alpha)*vu; x += v*dt  without fused multiply-adds
+     * (voxtral_tts_acoustic.c:350-354) */
+    const float v = __fadd_rn(__fmul_rn(alpha, vc), __fmul_rn(__fsub_rn(1.0f, alpha), vu));
+    return __fadd_rn(x, __fmul_rn(v, dt));
+}
+
+/* Euler update of the latent (step > 0) and the six input rows of a pass
+ * (voxtral_tts_acoustic.c:198-212): rows 0,3 input_proj(x_t); 1,4 the precomputed time token;
+ * 2 llm_proj(h); 5 zero. */
+__global__ void ac_tokens_kernel(float *X6, float *lat, const float *vel, const uint16_t *Wip, const float *ttok,
+                                 const float *ltok, int step, float alpha, float dt_prev, const float *noise_all,
+                                 const VbDyn *dyn) {
+    __shared__ float xs[64];
+    if (noise_all && dyn->done) return;   /* device-resident run already ended */
+    if (threadIdx.x < A) {
+        float xv;
+        if (step == 0) {
+            if (noise_all) {
+                xv = noise_all[(size_t)dyn->frame * A + threadIdx.x];
+                if (blockIdx.x == 0) lat[threadIdx.x] = xv;
+            } else {
+                xv = lat[threadIdx.x];
+            }
+        } else {
+            xv = euler_step(lat[(step - 1) * A + threadIdx.x], vel[threadIdx.x], vel[A + threadIdx.x], alpha, dt_prev);
+            if (blockIdx.x == 0) lat[step * A + threadIdx.x] = xv;
+        }
+        xs[threadIdx.x] = xv;
+    }
+    __syncthreads();
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= D) return;
+    const uint16_t *wr = Wip + (size_t)n * A;
+    float acc = 0.0f;
+    for (int k = 0; k < A; k++) acc = __fadd_rn(acc, __fmul_rn(__uint_as_float((uint32_t)wr[k] << 16), xs[k]));
+    const float tt = ttok[(size_t)step * D + n];
+    X6[n] = acc;
+    X6[3 * D + n] = acc;
+    X6[1 * D + n] = tt;
+    X6[4 * D + n] = tt;
+    X6[2 * D + n] = ltok[n];
+    X6[5 * D + n] = 0.0f;
+}
+
+/* Unmasked attention inside each 3-token sequence (tts_bidirectional_attention,
+ * voxtral_tts_kernels.c:467-525) on q/k/v given as split-K partials [n_part][6][6144].
+ * One warp per (row, head). */
+__global__ void ac_attention_kernel(float *out, const float *part, int n_part, float scale) {
+    const int task = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (task >= ROWS * VB200_HEADS) return;
+    const int row = task / VB200_HEADS, h = task % VB200_HEADS, kvh = h / (VB200_HEADS / VB200_KV_HEADS);
+    const int seq0 = (row / 3) * 3;
+    const size_t ps = (size_t)ROWS * QKV;
+    float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n_part; p++) {
+        const float4 t = *reinterpret_cast<const float4 *>(part + p * ps + (size_t)row * QKV + h * 128 + 4 * lane);
+        q.x += t.x; q.y += t.y; q.z += t.z; q.w += t.w;
+    }
+    float mx = -1e30f, den = 0.0f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < 3; j++) {
+        float4 k = make_float4(0.f, 0.f, 0.f, 0.f), v = k;
+        for (int p = 0; p < n_part; p++) {
+            const float *b = part + p * ps + (size_t)(seq0 + j) * QKV + QD + kvh * 128 + 4 * lane;
+            const float4 tk = *reinterpret_cast<const float4 *>(b);
+            const float4 tv = *reinterpret_cast<const float4 *>(b + KVD);
+            k.x += tk.x; k.y += tk.y; k.z += tk.z; k.w += tk.w;
+            v.x += tv.x; v.y += tv.y; v.z += tv.z; v.w += tv.w;
+        }
+        float d = q.x * k.x + q.y * k.y + q.z * k.z + q.w * k.w;
+        d = vb_warp_sum(d) * scale;
+        if (d > mx) {
+            const float corr = expf(mx - d);
+            den = den * corr + 1.0f;
+            o.x = o.x * corr + v.x; o.y = o.y * corr + v.y; o.z = o.z * corr + v.z; o.w = o.w * corr + v.w;
+            mx = d;
+        } else {
+            const float w = expf(d - mx);
+            den += w;
+            o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
+        }
+    }
+    const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    *reinterpret_cast<float4 *>(out + (size_t)row * QD + h * 128 + 4 * lane) =
+        make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+}
+
+/* Last residual add, final RMSNorm of token 0 of each branch (rows 0 and 3) and the 36-wide
+ * velocity head (voxtral_tts_acoustic.c:255-261). One CTA per branch. */
+__global__ void ac_velocity_kernel(float *vel, const float *X6, const float *part, int n_part, const float *gain,
+                                   float eps, const uint16_t *Wout) {
+    __shared__ float xn[VB200_DIM];
+    __shared__ float red[32];
+    const int row = blockIdx.x * 3;
+    const size_t ps = (size_t)ROWS * D;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float s = 0.0f;
+        for (int p = 0; p < n_part; p++) s += part[p * ps + (size_t)row * D + c];
+        const float v = X6[(size_t)row * D + c] + s;
+        xn[c] = v;
+        ss += v * v;
+    }
+    ss = vb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += red[w];
+    const float inv = 1.0f / sqrtf(t / (float)D + eps);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) xn[c] = xn[c] * inv * gain[c];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int n = warp; n < A; n += nw) {
+        const uint16_t *wr = Wout + (size_t)n * D;
+        float acc = 0.0f;
+        for (int c = lane; c < D; c += 32) acc = fmaf(__uint_as_float((uint32_t)wr[c] << 16), xn[c], acc);
+        acc = vb_warp_sum(acc);
+        if (lane == 0) vel[blockIdx.x * A + n] = acc;
+    }
+}
+
+/* Last Euler update and FSQ (voxtral_tts_acoustic.c:358-372); END forces code 2 (:312-320).
+ * In a device-resident run it also logs the frame's codes and advances position and frame
+ * counter (the loop of voxtral_tts.c:301-321). */
+__global__ void ac_fsq_kernel(int *codes, float *lat, const float *vel, int steps, int levels, float alpha, float dt,
+                              int *codes_all, VbDyn *dyn, int frame_cap, int advance, int ignore_end) {
+    const int i = threadIdx.x;
+    if (advance && dyn->done) return;
+    const int sem = codes[0];
+    const int frame = advance ? dyn->frame : 0;
+    __syncthreads();
+    if (advance && i == 0) {
+        if (codes_all) codes_all[(size_t)frame * (A + 1)] = sem;
+        const int nf = frame + 1, np = dyn->pos + 1;
+        dyn->frame = nf;
+        dyn->pos = np;
+        if (sem == 1 && !ignore_end) dyn->done = 2;
+        else if (nf >= frame_cap || np >= dyn->kv_max) dyn->done = 1;
+    }
+    if (i >= A) return;
+    float xv = euler_step(lat[(steps - 1) * A + i], vel[i], vel[A + i], alpha, dt);
+    lat[steps * A + i] = xv;
+    if (xv > 1.0f) xv = 1.0f;
+    if (xv < -1.0f) xv = -1.0f;
+    const float scaled = __fmul_rn(__fdiv_rn(__fadd_rn(xv, 1.0f), 2.0f), (float)(levels - 1));
+    int code = (int)__fadd_rn(scaled, 0.5f);
+    if (code < 0) code = 0;
+    if (code >= levels) code = levels - 1;
+    const int out = (sem == 1) ? 2 : code + 2;
+    codes[1 + i] = out;
+    if (advance && codes_all) codes_all[(size_t)frame * (A + 1) + 1 + i] = out;
+}
+
+/* ---- set-up ---- */
+static int alloc_zero(void **p, size_t bytes) {
+    if (cudaMalloc(p, bytes) != cudaSuccess) return -1;
+    model().allocs.push_back(*p);
+    return cudaMemset(*p, 0, bytes) == cudaSuccess ? 0 : -1;
+}
+
+int acoustic_tc_setup() {
+    Model &m = model();
+    AcTc &t = g_ac;
+    t.ready = false;
+    acoustic_tc_drop_graphs();   /* captured launches hold the old weight pointers */
+    if (getenv("VB200_NO_TC")) return 0;
+    if (tc_init()) {
+        fprintf(stderr, "voxtral_b200: cuTensorMapEncodeTiled unavailable; acoustic frame stays on the streaming kernel\n");
+        return 0;
+    }
+    for (int l = 0; l < VB200_AC_LAYERS; l++) {
+        const LayerDev &L = m.ac[l];
+        if (tc_weight(&t.wqkv[l], L.wqkv, QKV, D) || tc_weight(&t.wo[l], L.wo, D, QD) ||
+            tc_weight(&t.w13[l], L.w13, 2 * HID, D) || tc_weight(&t.w2[l], L.w2, D, HID))
+            return -1;
+    }
+    if (!t.bD) {
+        if (alloc_zero((void **)&t.bD, tc_acts_bytes(16, D)) || alloc_zero((void **)&t.bQ, tc_acts_bytes(16, QD)) ||
+            alloc_zero((void **)&t.bH, tc_acts_bytes(16, HID)) ||
+            alloc_zero((void **)&t.part, sizeof(float) * kTcMaxSplits * ROWS * QKV))
+            return -1;
+    }
+    if (tc_acts(&t.aD, t.bD, 16, D) || tc_acts(&t.aQ, t.bQ, 16, QD) || tc_acts(&t.aH, t.bH, 16, HID)) return -1;
+    t.s_qkv = tc_pick_splits(QKV, D, m.sm_count);
+    t.s_wo = tc_pick_splits(D, QD, m.sm_count);
+    t.s_w2 = tc_pick_splits(D, HID, m.sm_count);
+    t.ready = true;
+    return 0;
+}
+
+bool acoustic_tc_ready() { return g_ac.ready; }
+
+/* Enqueues the 7 Euler steps + FSQ on the library's stream. The semantic head, llm token
+ * and argmax have already run (engine program); `hidden`-dependent inputs are in m.ltok. */
+static int enqueue_direct(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end) {
+    Model &m = model();
+    AcTc &t = g_ac;
+    cudaStream_t st = m.st;
+    const float scale = 1.0f / sqrtf((float)VB200_HEAD_DIM);
+    const int steps = VB200_FLOW_STEPS - 1;
+    float *lat = &m.d_in->lat[0][0];
+    float *vel = &m.d_out->vel[0][0];
+    int *status = &m.d_out->status;
+    const size_t psD = (size_t)ROWS * D;
+    for (int s = 0; s < steps; s++) {
+        ac_tokens_kernel<<<(D + 127) / 128, 128, 0, st>>>(m.X6, lat, vel, m.ac_input_proj, m.ttok, m.ltok, s,
+                                                          VB200_CFG_ALPHA, s > 0 ? m.dt[s - 1] : 0.0f, noise_all,
+                                                          &m.d_in->dyn);
+        for (int l = 0; l < VB200_AC_LAYERS; l++) {
+            const LayerDev &L = m.ac[l];
+            if (l == 0)
+                tc_prepare(t.aD, m.X6, D, ROWS, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, VB200_NORM_EPS, st);
+            else
+                tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_w2, psD, m.X6, m.X6, L.attn_norm, VB200_NORM_EPS, st);
+            if (tc_gemm(t.wqkv[l], t.aD, ROWS, t.part, QKV, t.s_qkv, TC_EPI_PARTIAL, nullptr, status, st)) return -1;
+            ac_attention_kernel<<<(ROWS * VB200_HEADS * 32 + 255) / 256, 256, 0, st>>>(m.attn6, t.part, t.s_qkv, scale);
+            tc_prepare(t.aQ, m.attn6, QD, ROWS, nullptr, 0, 0, nullptr, nullptr, nullptr, 0.0f, st);
+            if (tc_gemm(t.wo[l], t.aQ, ROWS, t.part, D, t.s_wo, TC_EPI_PARTIAL, nullptr, status, st)) return -1;
+            tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_wo, psD, m.X6, m.X6, L.ffn_norm, VB200_NORM_EPS, st);
+            if (tc_gemm(t.w13[l], t.aD, ROWS, m.h6, HID, 1, TC_EPI_SWIGLU, nullptr, status, st)) return -1;
+            tc_prepare(t.aH, m.h6, HID, ROWS, nullptr, 0, 0, nullptr, nullptr, nullptr, 0.0f, st);
+            if (tc_gemm(t.w2[l], t.aH, ROWS, t.part, D, t.s_w2, TC_EPI_PARTIAL, nullptr, status, st)) return -1;
+        }
+        ac_velocity_kernel<<<2, 512, 0, st>>>(vel, m.X6, t.part, t.s_w2, m.ac_norm, VB200_NORM_EPS, m.ac_out);
+    }
+    ac_fsq_kernel<<<1, 64, 0, st>>>(m.d_out->codes, lat, vel, steps, VB200_FSQ_LEVELS, VB200_CFG_ALPHA, m.dt[steps - 1],
+                                    codes_all, &m.d_in->dyn, frame_cap, advance ? 1 : 0, ignore_end ? 1 : 0);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+/* The ~200 launches of a frame are captured once per argument set as a CUDA graph and
+ * replayed; the first call with a new argument set runs directly (it also sets the
+ * kernels' shared-memory attributes, which must not happen inside a capture). */
+struct GraphSlot {
+    const float *noise_all = nullptr;
+    int *codes_all = nullptr;
+    int cap = 0;
+    bool advance = false, ignore_end = false, used = false;
+    int calls = 0;
+    cudaGraphExec_t exec = nullptr;
+};
+static GraphSlot g_slots[2];
+
+void acoustic_tc_drop_graphs() {
+    for (GraphSlot &s : g_slots) {
+        if (s.exec) cudaGraphExecDestroy(s.exec);
+        s = GraphSlot();
+    }
+}
+
+int acoustic_tc_enqueue(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end) {
+    Model &m = model();
+    if (getenv("VB200_NO_GRAPH")) return enqueue_direct(noise_all, codes_all, frame_cap, advance, ignore_end);
+    GraphSlot &s = g_slots[advance ? 1 : 0];
+    const bool same = s.used && s.noise_all == noise_all && s.codes_all == codes_all && s.cap == frame_cap &&
+                      s.advance == advance && s.ignore_end == ignore_end;
+    if (!same) {
+        if (s.exec) cudaGraphExecDestroy(s.exec);
+        s = GraphSlot();
+        s.noise_all = noise_all; s.codes_all = codes_all; s.cap = frame_cap;
+        s.advance = advance; s.ignore_end = ignore_end; s.used = true;
+    }
+    if (s.exec) return cudaGraphLaunch(s.exec, m.st) == cudaSuccess ? 0 : -1;
+    if (s.calls++ == 0) return enqueue_direct(noise_all, codes_all, frame_cap, advance, ignore_end);
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(m.st, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+        cudaGetLastError();
+        return enqueue_direct(noise_all, codes_all, frame_cap, advance, ignore_end);
+    }
+    const int rc = enqueue_direct(noise_all, codes_all, frame_cap, advance, ignore_end);
+    const cudaError_t ee = cudaStreamEndCapture(m.st, &graph);
+    if (rc || ee != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return -1;
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&s.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        s.exec = nullptr;
+        cudaGetLastError();
+        return -1;
+    }
+    return cudaGraphLaunch(s.exec, m.st) == cudaSuccess ? 0 : -1;
+}
+
+} // namespace vb

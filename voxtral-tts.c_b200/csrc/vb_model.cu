@@ -7,6 +7,7 @@
  */
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
+#include "vb_tc.cuh"
 
 #include <math.h>
 #include <stddef.h>
@@ -301,6 +302,7 @@ int model_upload_acoustic(const vb200_acoustic_weights_t *w) {
     if (!rc && cudaStreamSynchronize(m.st) != cudaSuccess) rc = -1;
     dev_release(temb_d);
     if (rc) { upload_failed(); return -1; }
+    if (acoustic_tc_setup()) { upload_failed(); return -1; }
     m.ac_ready = true;
     return model_rebuild_programs();
 }
@@ -416,6 +418,9 @@ static void build_acoustic(std::vector<VbOp> &ops, const float *hidden, const fl
     o.type = VB_OP_ARGMAX; o.N = VB200_SEM_PADDED; o.x = m.logits; o.i0 = VB200_SEM_VALID_END;
     o.p2 = m.d_out->codes; o.flags = VB_F_NOSYNC;
     ops.push_back(o);
+    /* With the tensor-core path up, the Euler steps run as their own kernels after this
+     * program (vb_acoustic_tc.cu); the program ends with the semantic head. */
+    if (acoustic_tc_ready()) return;
 
     const int steps = VB200_FLOW_STEPS - 1;
     float *lat = &m.d_in->lat[0][0];
@@ -622,11 +627,13 @@ int frame(const float *embed, const float *noise, int pos, float *hidden_out, in
         VB_CHECK(cudaMemcpyAsync(&m.d_in->dyn, &m.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice, m.st));
         VB_CHECK(cudaMemcpyAsync(m.d_in->lat[0], m.h_in->lat[0], sizeof(float) * A, cudaMemcpyHostToDevice, m.st));
         if (run_program(m.p_chain)) return -1;
+        if (acoustic_tc_ready() && acoustic_tc_enqueue(nullptr, nullptr, 0, false, false)) return -1;
     } else {
         memcpy(m.h_in->embed, embed, sizeof(float) * D);
         VB_CHECK(cudaMemcpyAsync(m.d_in, m.h_in, offsetof(DevIn, lat) + sizeof(float) * A, cudaMemcpyHostToDevice,
                                  m.st));
         if (run_program(m.p_frame)) return -1;
+        if (acoustic_tc_ready() && acoustic_tc_enqueue(nullptr, nullptr, 0, false, false)) return -1;
     }
     if (finish(offsetof(DevOut, vel))) return -1;
     memcpy(codes, m.h_out->codes, sizeof(int) * VB200_CODES);
@@ -641,6 +648,7 @@ int acoustic_frame(const float *hidden, const float *noise, int *codes, float *l
     memcpy(m.h_in->hidden_in, hidden, sizeof(float) * D);
     VB_CHECK(cudaMemcpyAsync(m.d_in, m.h_in, offsetof(DevIn, temb), cudaMemcpyHostToDevice, m.st));
     if (run_program(m.p_ac)) return -1;
+    if (acoustic_tc_ready() && acoustic_tc_enqueue(nullptr, nullptr, 0, false, false)) return -1;
     if (latent_out)
         VB_CHECK(cudaMemcpyAsync(m.h_in->lat[VB200_FLOW_STEPS - 1], m.d_in->lat[VB200_FLOW_STEPS - 1],
                                  sizeof(float) * A, cudaMemcpyDeviceToHost, m.st));
@@ -693,7 +701,7 @@ int utterance_begin(const float *first_embed, int start_pos, const float *noise_
     adv.type = VB_OP_ADVANCE; adv.p0 = m.d_out->codes; adv.i0 = n_frames; adv.i1 = m.ignore_end ? 1 : 0;
     build_llm(ops, m.d_in->embed, m.d_out->hidden);
     build_acoustic(ops, m.d_out->hidden, m.noise_all, m.codes_all);
-    ops.push_back(adv);
+    if (!acoustic_tc_ready()) ops.push_back(adv);
     if (upload_program(m.p_run_first, ops)) return -1;
     ops.clear();
     VbOp e = op_zero();
@@ -702,7 +710,7 @@ int utterance_begin(const float *first_embed, int start_pos, const float *noise_
     ops.push_back(e);
     build_llm(ops, m.d_in->embed, m.d_out->hidden);
     build_acoustic(ops, m.d_out->hidden, m.noise_all, m.codes_all);
-    ops.push_back(adv);
+    if (!acoustic_tc_ready()) ops.push_back(adv);
     if (upload_program(m.p_run_next, ops)) return -1;
 
     m.h_in->dyn.pos = start_pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.frame = 0; m.h_in->dyn.done = 0;
@@ -722,6 +730,8 @@ int utterance_run(int n) {
     for (int i = 0; i < n; i++) {
         if (m.run_launched >= m.run_cap) break;
         if (run_program(m.run_launched == 0 ? m.p_run_first : m.p_run_next)) return -1;
+        if (acoustic_tc_ready() && acoustic_tc_enqueue(m.noise_all, m.codes_all, m.run_cap, true, m.ignore_end))
+            return -1;
         m.run_launched++;
     }
     cudaEventRecord(m.evr1, m.st);
@@ -766,6 +776,37 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
     if (!aligned || gemv_validate(N, K, 1, VB_EPI_STORE, m.n_cta) != 0) {
         linear_generic(d_y, d_x, d_W, nullptr, M, K, N, m.st);
         return 0;
+    }
+    /* Two or more rows: the tensor-core GEMM (fp32 rows as three BF16 terms, vb_tc.cu). */
+    if (M >= 2 && (K % kTcBlockK) == 0 && !getenv("VB200_NO_TC") && tc_init() == 0) {
+        TcWeight w;
+        if (tc_weight(&w, d_W, N, K) == 0) {
+            int rc = 0;
+            for (int r = 0; r < M && !rc; r += 256) {
+                const int rows = (M - r < 256) ? M - r : 256;
+                const int rp = tc_rows_pad(rows);
+                const int splits = tc_pick_splits(N, K, m.sm_count);
+                void *buf = nullptr, *part = nullptr;
+                TcActs a;
+                if (cudaMalloc(&buf, tc_acts_bytes(rp, K)) != cudaSuccess) return -1;
+                cudaMemsetAsync(buf, 0, tc_acts_bytes(rp, K), m.st);
+                if (tc_acts(&a, (uint16_t *)buf, rp, K)) rc = -1;
+                if (!rc) tc_prepare(a, d_x + (size_t)r * K, K, rows, nullptr, 0, 0, nullptr, nullptr, nullptr, 0.0f, m.st);
+                if (!rc && splits == 1) {
+                    rc = tc_gemm(w, a, rows, d_y + (size_t)r * N, N, 1, TC_EPI_STORE, nullptr, &m.d_out->status, m.st);
+                } else if (!rc) {
+                    if (cudaMalloc(&part, sizeof(float) * (size_t)splits * rows * N) != cudaSuccess) rc = -1;
+                    if (!rc) rc = tc_gemm(w, a, rows, (float *)part, N, splits, TC_EPI_PARTIAL, nullptr,
+                                          &m.d_out->status, m.st);
+                    if (!rc) tc_reduce(d_y + (size_t)r * N, (const float *)part, splits, (size_t)rows * N,
+                                       (size_t)rows * N, nullptr, N, m.st);
+                }
+                cudaStreamSynchronize(m.st);
+                cudaFree(buf);
+                cudaFree(part);
+            }
+            return rc;
+        }
     }
     for (int r = 0; r < M; r += kMaxM) {
         const int rows = (M - r < kMaxM) ? M - r : kMaxM;

@@ -113,6 +113,11 @@ int predict_velocity(float *out_v, const float *x_t, const float *hidden, float 
 int linear(float *y, const float *x, const uint16_t *W_host, int M, int K, int N, const void *W_gpu);
 int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N);
 int prefill(const float *embeds, int seq_len, int start_pos);
+/* tensor-core acoustic path (vb_acoustic_tc.cu) */
+int acoustic_tc_setup();
+bool acoustic_tc_ready();
+int acoustic_tc_enqueue(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end);
+
 int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);
 int utterance_run(int n);
 int utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
