@@ -30,6 +30,8 @@ struct AcTc {
     TcActs aD, aQ, aH;
     uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
     float *part = nullptr;      /* split-K partials [splits][6][N] */
+    uint16_t *tiled[VB200_AC_LAYERS][4] = {};   /* tile-contiguous weight copies */
+    float *ssq = nullptr;       /* per-row, per-chunk sums of squares for the deferred RMSNorm scale */
     int s_qkv = 1, s_wo = 1, s_w2 = 1;
 };
 static AcTc g_ac;
@@ -51,6 +53,8 @@ __global__ void ac_tokens_kernel(float *X6, float *lat, const float *vel, const 
                                  const float *ltok, int step, float alpha, float dt_prev, const float *noise_all,
                                  const VbDyn *dyn) {
     __shared__ float xs[64];
+    pdl_launch_dependents();
+    pdl_wait();
     if (noise_all && dyn->done) return;   /* device-resident run already ended */
     if (threadIdx.x < A) {
         float xv;
@@ -84,8 +88,11 @@ __global__ void ac_tokens_kernel(float *X6, float *lat, const float *vel, const 
 
 /* Unmasked attention inside each 3-token sequence (tts_bidirectional_attention,
  * voxtral_tts_kernels.c:467-525) on q/k/v given as split-K partials [n_part][6][6144].
- * One warp per (row, head). */
-__global__ void ac_attention_kernel(float *out, const float *part, int n_part, float scale) {
+ * One warp per (row, head). The result goes out as the three BF16 terms the O projection's
+ * GEMM consumes ([3][16][4096]). */
+__global__ void ac_attention_kernel(uint16_t *terms, const float *part, int n_part, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int task = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (task >= ROWS * VB200_HEADS) return;
     const int row = task / VB200_HEADS, h = task % VB200_HEADS, kvh = h / (VB200_HEADS / VB200_KV_HEADS);
@@ -121,17 +128,26 @@ __global__ void ac_attention_kernel(float *out, const float *part, int n_part, f
         }
     }
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
-    *reinterpret_cast<float4 *>(out + (size_t)row * QD + h * 128 + 4 * lane) =
-        make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    const float e[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
+    uint16_t t0[4], t1[4], t2[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) vb_split3(e[i], t0[i], t1[i], t2[i]);
+    const size_t off = (size_t)row * QD + h * 128 + 4 * lane, term = (size_t)16 * QD;
+    *reinterpret_cast<uint2 *>(terms + off) = make_uint2(t0[0] | ((uint32_t)t0[1] << 16), t0[2] | ((uint32_t)t0[3] << 16));
+    *reinterpret_cast<uint2 *>(terms + term + off) = make_uint2(t1[0] | ((uint32_t)t1[1] << 16), t1[2] | ((uint32_t)t1[3] << 16));
+    *reinterpret_cast<uint2 *>(terms + 2 * term + off) = make_uint2(t2[0] | ((uint32_t)t2[1] << 16), t2[2] | ((uint32_t)t2[3] << 16));
 }
 
 /* Last residual add, final RMSNorm of token 0 of each branch (rows 0 and 3) and the 36-wide
- * velocity head (voxtral_tts_acoustic.c:255-261). One CTA per branch. */
+ * velocity head (voxtral_tts_acoustic.c:255-261). grid = (9, 2): branch blockIdx.y, four of
+ * the 36 outputs per CTA (every CTA re-derives the normalised row; it is 12 KB). */
 __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *part, int n_part, const float *gain,
                                    float eps, const uint16_t *Wout) {
     __shared__ float xn[VB200_DIM];
     __shared__ float red[32];
-    const int row = blockIdx.x * 3;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y * 3;
     const size_t ps = (size_t)ROWS * D;
     float ss = 0.0f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
@@ -149,13 +165,20 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
     const float inv = 1.0f / sqrtf(t / (float)D + eps);
     for (int c = threadIdx.x; c < D; c += blockDim.x) xn[c] = xn[c] * inv * gain[c];
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int n = warp; n < A; n += nw) {
-        const uint16_t *wr = Wout + (size_t)n * D;
-        float acc = 0.0f;
-        for (int c = lane; c < D; c += 32) acc = fmaf(__uint_as_float((uint32_t)wr[c] << 16), xn[c], acc);
-        acc = vb_warp_sum(acc);
-        if (lane == 0) vel[blockIdx.x * A + n] = acc;
+    /* 4 outputs per CTA, 4 warps per output, then a fixed-order sum of the 4 warp partials */
+    __shared__ float wsum[16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 4 + (warp >> 2), q = warp & 3;
+    const uint16_t *wr = Wout + (size_t)n * D;
+    float acc = 0.0f;
+    for (int c = q * (D / 4) + lane; c < (q + 1) * (D / 4); c += 32)
+        acc = fmaf(__uint_as_float((uint32_t)wr[c] << 16), xn[c], acc);
+    acc = vb_warp_sum(acc);
+    if (lane == 0) wsum[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x < 4) {
+        const int o = threadIdx.x;
+        vel[blockIdx.y * A + blockIdx.x * 4 + o] = ((wsum[4 * o] + wsum[4 * o + 1]) + wsum[4 * o + 2]) + wsum[4 * o + 3];
     }
 }
 
@@ -165,6 +188,8 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
 __global__ void ac_fsq_kernel(int *codes, float *lat, const float *vel, int steps, int levels, float alpha, float dt,
                               int *codes_all, VbDyn *dyn, int frame_cap, int advance, int ignore_end) {
     const int i = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (advance && dyn->done) return;
     const int sem = codes[0];
     const int frame = advance ? dyn->frame : 0;
@@ -210,14 +235,28 @@ int acoustic_tc_setup() {
     }
     for (int l = 0; l < VB200_AC_LAYERS; l++) {
         const LayerDev &L = m.ac[l];
-        if (tc_weight(&t.wqkv[l], L.wqkv, QKV, D) || tc_weight(&t.wo[l], L.wo, D, QD) ||
-            tc_weight(&t.w13[l], L.w13, 2 * HID, D) || tc_weight(&t.w2[l], L.w2, D, HID))
-            return -1;
+        if (getenv("VB200_TC_UNTILED")) {
+            if (tc_weight(&t.wqkv[l], L.wqkv, QKV, D) || tc_weight(&t.wo[l], L.wo, D, QD) ||
+                tc_weight(&t.w13[l], L.w13, 2 * HID, D) || tc_weight(&t.w2[l], L.w2, D, HID))
+                return -1;
+            continue;
+        }
+        /* tile-contiguous copies for the tensor-core path (the row-major originals stay for the
+         * streaming kernel's single-pass entry point) */
+        const struct { TcWeight *w; const uint16_t *src; int N, K; uint16_t **dst; } jobs[4] = {
+            {&t.wqkv[l], L.wqkv, QKV, D, &t.tiled[l][0]}, {&t.wo[l], L.wo, D, QD, &t.tiled[l][1]},
+            {&t.w13[l], L.w13, 2 * HID, D, &t.tiled[l][2]}, {&t.w2[l], L.w2, D, HID, &t.tiled[l][3]}};
+        for (int j = 0; j < 4; j++) {
+            if (!*jobs[j].dst && alloc_zero((void **)jobs[j].dst, tc_tiled_bytes(jobs[j].N, jobs[j].K))) return -1;
+            if (tc_weight_tiled(jobs[j].w, jobs[j].src, jobs[j].N, jobs[j].K, *jobs[j].dst, m.st)) return -1;
+        }
+        if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
     }
     if (!t.bD) {
         if (alloc_zero((void **)&t.bD, tc_acts_bytes(16, D)) || alloc_zero((void **)&t.bQ, tc_acts_bytes(16, QD)) ||
             alloc_zero((void **)&t.bH, tc_acts_bytes(16, HID)) ||
-            alloc_zero((void **)&t.part, sizeof(float) * kTcMaxSplits * ROWS * QKV))
+            alloc_zero((void **)&t.part, sizeof(float) * kTcMaxSplits * ROWS * QKV) ||
+            alloc_zero((void **)&t.ssq, sizeof(float) * 16 * 16))
             return -1;
     }
     if (tc_acts(&t.aD, t.bD, 16, D) || tc_acts(&t.aQ, t.bQ, 16, QD) || tc_acts(&t.aH, t.bH, 16, HID)) return -1;
@@ -242,29 +281,40 @@ static int enqueue_direct(const float *noise_all, int *codes_all, int frame_cap,
     float *vel = &m.d_out->vel[0][0];
     int *status = &m.d_out->status;
     const size_t psD = (size_t)ROWS * D;
+    const int chunksD = tc_prepare_chunks(D);
+    TcGemm g;
+    g.M = ROWS; g.status = status;
     for (int s = 0; s < steps; s++) {
-        ac_tokens_kernel<<<(D + 127) / 128, 128, 0, st>>>(m.X6, lat, vel, m.ac_input_proj, m.ttok, m.ltok, s,
-                                                          VB200_CFG_ALPHA, s > 0 ? m.dt[s - 1] : 0.0f, noise_all,
-                                                          &m.d_in->dyn);
+        launch_pdl(ac_tokens_kernel, dim3((D + 127) / 128), dim3(128), 0, st, m.X6, lat, (const float *)vel,
+                   (const uint16_t *)m.ac_input_proj, (const float *)m.ttok, (const float *)m.ltok, s,
+                   VB200_CFG_ALPHA, s > 0 ? m.dt[s - 1] : 0.0f, noise_all, (const VbDyn *)&m.d_in->dyn);
         for (int l = 0; l < VB200_AC_LAYERS; l++) {
             const LayerDev &L = m.ac[l];
-            if (l == 0)
-                tc_prepare(t.aD, m.X6, D, ROWS, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, VB200_NORM_EPS, st);
-            else
-                tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_w2, psD, m.X6, m.X6, L.attn_norm, VB200_NORM_EPS, st);
-            if (tc_gemm(t.wqkv[l], t.aD, ROWS, t.part, QKV, t.s_qkv, TC_EPI_PARTIAL, nullptr, status, st)) return -1;
-            ac_attention_kernel<<<(ROWS * VB200_HEADS * 32 + 255) / 256, 256, 0, st>>>(m.attn6, t.part, t.s_qkv, scale);
-            tc_prepare(t.aQ, m.attn6, QD, ROWS, nullptr, 0, 0, nullptr, nullptr, nullptr, 0.0f, st);
-            if (tc_gemm(t.wo[l], t.aQ, ROWS, t.part, D, t.s_wo, TC_EPI_PARTIAL, nullptr, status, st)) return -1;
-            tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_wo, psD, m.X6, m.X6, L.ffn_norm, VB200_NORM_EPS, st);
-            if (tc_gemm(t.w13[l], t.aD, ROWS, m.h6, HID, 1, TC_EPI_SWIGLU, nullptr, status, st)) return -1;
-            tc_prepare(t.aH, m.h6, HID, ROWS, nullptr, 0, 0, nullptr, nullptr, nullptr, 0.0f, st);
-            if (tc_gemm(t.w2[l], t.aH, ROWS, t.part, D, t.s_w2, TC_EPI_PARTIAL, nullptr, status, st)) return -1;
+            /* attention half: (reduce + residual +) gain -> QKV -> attention -> O */
+            if (l == 0) tc_prepare(t.aD, m.X6, D, ROWS, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
+            else tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_w2, psD, m.X6, m.X6, L.attn_norm, t.ssq, st);
+            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+            g.splits = t.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+            if (tc_gemm(t.wqkv[l], t.aD, g, st)) return -1;
+            launch_pdl(ac_attention_kernel, dim3((ROWS * VB200_HEADS * 32 + 255) / 256), dim3(256), 0, st, t.bQ,
+                       (const float *)t.part, t.s_qkv, scale);
+            g.splits = t.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+            if (tc_gemm(t.wo[l], t.aQ, g, st)) return -1;
+            /* FFN half: reduce + residual + gain -> gate/up with SwiGLU (terms out) -> down */
+            tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_wo, psD, m.X6, m.X6, L.ffn_norm, t.ssq, st);
+            g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
+            g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
+            if (tc_gemm(t.w13[l], t.aD, g, st)) return -1;
+            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+            g.splits = t.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+            if (tc_gemm(t.w2[l], t.aH, g, st)) return -1;
         }
-        ac_velocity_kernel<<<2, 512, 0, st>>>(vel, m.X6, t.part, t.s_w2, m.ac_norm, VB200_NORM_EPS, m.ac_out);
+        launch_pdl(ac_velocity_kernel, dim3(9, 2), dim3(512), 0, st, vel, (const float *)m.X6, (const float *)t.part,
+                   t.s_w2, (const float *)m.ac_norm, VB200_NORM_EPS, (const uint16_t *)m.ac_out);
     }
-    ac_fsq_kernel<<<1, 64, 0, st>>>(m.d_out->codes, lat, vel, steps, VB200_FSQ_LEVELS, VB200_CFG_ALPHA, m.dt[steps - 1],
-                                    codes_all, &m.d_in->dyn, frame_cap, advance ? 1 : 0, ignore_end ? 1 : 0);
+    launch_pdl(ac_fsq_kernel, dim3(1), dim3(64), 0, st, m.d_out->codes, lat, (const float *)vel, steps,
+               VB200_FSQ_LEVELS, VB200_CFG_ALPHA, m.dt[steps - 1], codes_all, &m.d_in->dyn, frame_cap,
+               advance ? 1 : 0, ignore_end ? 1 : 0);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

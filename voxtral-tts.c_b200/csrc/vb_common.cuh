@@ -7,6 +7,7 @@
 #ifndef VB_COMMON_CUH
 #define VB_COMMON_CUH
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -146,6 +147,25 @@ VB_DEVINL int vb_warp_multi_sum(float (&v)[V], int lane) {
     }
     /* a lane that ended on a padding slot (odd counts on the way) owns no value */
     return real > 0 ? base : V;
+}
+
+/* Programmatic dependent launch: launch_dependents lets the next kernel of the stream begin
+ * its prologue; wait blocks until the previous kernel has completed and its writes are visible
+ * (a no-op for kernels launched without the attribute). */
+VB_DEVINL void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+VB_DEVINL void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+/* v = t0 + t1 + t2 with three BF16 terms (8 + 8 + 8 mantissa bits): what the tensor-core
+ * path feeds instead of an fp32 activation. */
+VB_DEVINL void vb_split3(float v, uint16_t &t0, uint16_t &t1, uint16_t &t2) {
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h0);
+    const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(h1);
+    const __nv_bfloat16 h2 = __float2bfloat16_rn(r2);
+    t0 = __bfloat16_as_ushort(h0);
+    t1 = __bfloat16_as_ushort(h1);
+    t2 = __bfloat16_as_ushort(h2);
 }
 
 #endif

@@ -791,13 +791,16 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
                 if (cudaMalloc(&buf, tc_acts_bytes(rp, K)) != cudaSuccess) return -1;
                 cudaMemsetAsync(buf, 0, tc_acts_bytes(rp, K), m.st);
                 if (tc_acts(&a, (uint16_t *)buf, rp, K)) rc = -1;
-                if (!rc) tc_prepare(a, d_x + (size_t)r * K, K, rows, nullptr, 0, 0, nullptr, nullptr, nullptr, 0.0f, m.st);
+                if (!rc) tc_prepare(a, d_x + (size_t)r * K, K, rows, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, m.st);
+                TcGemm g;
+                g.M = rows; g.status = &m.d_out->status; g.ld_out = N; g.splits = splits;
                 if (!rc && splits == 1) {
-                    rc = tc_gemm(w, a, rows, d_y + (size_t)r * N, N, 1, TC_EPI_STORE, nullptr, &m.d_out->status, m.st);
+                    g.epi = TC_EPI_STORE; g.out = d_y + (size_t)r * N;
+                    rc = tc_gemm(w, a, g, m.st);
                 } else if (!rc) {
                     if (cudaMalloc(&part, sizeof(float) * (size_t)splits * rows * N) != cudaSuccess) rc = -1;
-                    if (!rc) rc = tc_gemm(w, a, rows, (float *)part, N, splits, TC_EPI_PARTIAL, nullptr,
-                                          &m.d_out->status, m.st);
+                    g.epi = TC_EPI_PARTIAL; g.out = (float *)part;
+                    if (!rc) rc = tc_gemm(w, a, g, m.st);
                     if (!rc) tc_reduce(d_y + (size_t)r * N, (const float *)part, splits, (size_t)rows * N,
                                        (size_t)rows * N, nullptr, N, m.st);
                 }

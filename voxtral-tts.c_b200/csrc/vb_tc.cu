@@ -27,6 +27,8 @@
 
 #include <cuda_bf16.h>
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 
 namespace vb {
 
@@ -66,9 +68,44 @@ static int make_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t co
 
 int tc_weight(TcWeight *w, const uint16_t *d_W, int N, int K) {
     w->ok = false;
-    w->W = d_W; w->N = N; w->K = K;
+    w->W = d_W; w->N = N; w->K = K; w->tiled = false;
     if (N <= 0 || K <= 0 || (K % kTcBlockK) != 0) return -1;
     if (make_map(&w->map, d_W, (uint64_t)N, (uint64_t)K, kTcTileN)) return -1;
+    w->ok = true;
+    return 0;
+}
+
+/* Weights re-laid out so that every [128 rows x 64 columns] tile the kernel fetches is one
+ * contiguous 16 KB block (tile-major, then k-block), instead of 128 pieces of 128 bytes that
+ * sit a whole weight row apart: the TMA request becomes a single DRAM-friendly burst. */
+__global__ void vb_tc_tile_weights_kernel(uint4 *dst, const uint4 *src, int N, int K) {
+    const int kblocks = K / kTcBlockK;
+    const size_t n_vec = (size_t)((N + kTcTileN - 1) / kTcTileN) * kblocks * kTcTileN * (kTcBlockK / 8);
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const int v = (int)(i % (kTcBlockK / 8));                 /* 16-byte vector inside the 128-byte row */
+    const int r = (int)((i / (kTcBlockK / 8)) % kTcTileN);    /* row inside the tile */
+    const size_t blk = i / ((kTcBlockK / 8) * kTcTileN);
+    const int kb = (int)(blk % kblocks), t = (int)(blk / kblocks);
+    const int row = t * kTcTileN + r;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (row < N) val = src[((size_t)row * K + (size_t)kb * kTcBlockK) / 8 + v];
+    dst[i] = val;
+}
+
+size_t tc_tiled_bytes(int N, int K) {
+    return (size_t)((N + kTcTileN - 1) / kTcTileN) * kTcTileN * K * 2;
+}
+
+int tc_weight_tiled(TcWeight *w, const uint16_t *d_W, int N, int K, uint16_t *d_tiled, cudaStream_t st) {
+    w->ok = false;
+    w->W = d_tiled; w->N = N; w->K = K; w->tiled = true;
+    if (N <= 0 || K <= 0 || (K % kTcBlockK) != 0 || ((uintptr_t)d_W & 15) || ((uintptr_t)d_tiled & 15)) return -1;
+    const size_t n_vec = tc_tiled_bytes(N, K) / 16;
+    vb_tc_tile_weights_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, st>>>((uint4 *)d_tiled, (const uint4 *)d_W, N, K);
+    if (cudaGetLastError() != cudaSuccess) return -1;
+    const uint64_t rows = (uint64_t)((N + kTcTileN - 1) / kTcTileN) * (K / kTcBlockK) * kTcTileN;
+    if (make_map(&w->map, d_tiled, rows, (uint64_t)kTcBlockK, kTcTileN)) return -1;
     w->ok = true;
     return 0;
 }
@@ -156,19 +193,47 @@ struct TcCfg {
     static constexpr int kStageA = kTcTileN * kTcBlockK * 2;        /* 16 KB */
     static constexpr int kTermB = NB * kTcBlockK * 2;               /* one BF16 term of the activations */
     static constexpr int kStage = kStageA + kTcTerms * kTermB;
-    static constexpr int kStages = NB == 16 ? 8 : NB == 64 ? 5 : 2;
-    static constexpr int kTmemCols = NB < 32 ? 32 : NB;
-    static constexpr int kSmemBytes = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int kStages = NB == 16 ? 5 : NB == 64 ? 5 : 2;   /* NB=16: 110 KB, two CTAs fit one SM so that a GEMM can start under the tail of the previous one */
+    /* The three BF16 terms of the activations lie one after another in a stage, so for
+     * NB <= 64 they form ONE B operand of 3*NB rows: a single MMA per 16-wide K step writes the
+     * three partial products to separate TMEM column groups (summed in the epilogue) instead of
+     * three narrow MMAs - the narrow ones are issue-latency bound, not throughput bound. */
+    static constexpr bool kFusedTerms = (kTcTerms * NB) <= 256;
+    static constexpr int kMmaN = kFusedTerms ? kTcTerms * NB : NB;
+    static constexpr int kAccCols = kFusedTerms ? kTcTerms * NB : NB;
+    static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : 256;
+    static constexpr int kSmemBytes = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */ + 4 * NB;
 };
 
 constexpr int kTcThreads = 192;
 
+/* Kernel-side scalars and pointers (everything but the two tensor maps). */
+struct TcKernelArgs {
+    int N, K, M, rows_pad, ld_out, splits, epi;
+    int a_tiled;             /* weights in the tile-contiguous layout */
+    float *out;
+    const float *bias;
+    const float *ssq;        /* optional [M][ssq_chunks] sums of squares: deferred RMSNorm row scale */
+    int ssq_chunks;
+    float eps;
+    uint16_t *out_terms;     /* TC_EPI_SWIGLU_TERMS: BF16 terms of the result, [3][out_rows_pad][N/2] */
+    int out_rows_pad;
+    int *status;
+};
+
 template <int NB>
 __global__ void __launch_bounds__(kTcThreads, 1)
-vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, int N, int K,
-                  int M, int rows_pad, float *out, int ld_out, int splits, int epi, const float *bias,
-                  int *status) {
+vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                  const TcKernelArgs ka) {
     using Cfg = TcCfg<NB>;
+    const int N = ka.N, K = ka.K, M = ka.M, rows_pad = ka.rows_pad, ld_out = ka.ld_out, splits = ka.splits,
+              epi = ka.epi;
+    float *const out = ka.out;
+    const float *const bias = ka.bias;
+    int *const status = ka.status;
+    /* Programmatic dependent launch: the next kernel in the stream may start its own
+     * prologue now; it waits (griddepcontrol.wait) before touching what this one writes. */
+    pdl_launch_dependents();
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char *base = (unsigned char *)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *stages = base;
@@ -177,6 +242,7 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     uint64_t *accum = empty + Cfg::kStages;
     uint32_t *tmem_slot = (uint32_t *)(accum + 1);
     int *abort_flag = (int *)(tmem_slot + 1);
+    float *rscale = (float *)(abort_flag + 1);   /* [NB] per-row scales */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / splits, sp = blockIdx.x % splits;
@@ -202,8 +268,25 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     const uint32_t tmem = *(volatile uint32_t *)tmem_slot;
 
     if (warp == 4 && lane == 0) {
-        /* ---- TMA producer ---- */
-        for (int it = 0; it < n_it; it++) {
+        /* ---- TMA producer ----
+         * Weights do not depend on the previous kernel: the first ring-full of weight
+         * tiles is requested at once, then the kernel waits for its predecessor
+         * (griddepcontrol.wait) and only then fetches the activation terms. */
+        const int first = n_it < Cfg::kStages ? n_it : Cfg::kStages;
+        for (int it = 0; it < first; it++) {
+            unsigned char *sa = stages + (size_t)it * Cfg::kStage;
+            vb_mbar_arrive_expect_tx(&full[it], (uint32_t)Cfg::kStage);
+            if (ka.a_tiled) tma_load_2d(sa, &mapA, 0, (tile * kblocks + kb0 + it) * kTcTileN, &full[it]);
+            else tma_load_2d(sa, &mapA, (kb0 + it) * kTcBlockK, tile * kTcTileN, &full[it]);
+        }
+        pdl_wait();
+        for (int it = 0; it < first; it++) {
+            unsigned char *sa = stages + (size_t)it * Cfg::kStage;
+#pragma unroll
+            for (int j = 0; j < kTcTerms; j++)
+                tma_load_2d(sa + Cfg::kStageA + j * Cfg::kTermB, &mapB, (kb0 + it) * kTcBlockK, j * rows_pad, &full[it]);
+        }
+        for (int it = first; it < n_it; it++) {
             const int s = it % Cfg::kStages, use = it / Cfg::kStages;
             if (!vb_mbar_wait(&empty[s], (use & 1u) ^ 1u, abort_flag)) {
                 atomicCAS(status, 0, 11);
@@ -213,14 +296,15 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             unsigned char *sa = stages + (size_t)s * Cfg::kStage;
             vb_mbar_arrive_expect_tx(&full[s], (uint32_t)Cfg::kStage);
             const int kx = (kb0 + it) * kTcBlockK;
-            tma_load_2d(sa, &mapA, kx, tile * kTcTileN, &full[s]);
+            if (ka.a_tiled) tma_load_2d(sa, &mapA, 0, (tile * kblocks + kb0 + it) * kTcTileN, &full[s]);
+            else tma_load_2d(sa, &mapA, kx, tile * kTcTileN, &full[s]);
 #pragma unroll
             for (int j = 0; j < kTcTerms; j++)
                 tma_load_2d(sa + Cfg::kStageA + j * Cfg::kTermB, &mapB, kx, j * rows_pad, &full[s]);
         }
     } else if (warp == 5 && lane == 0) {
         /* ---- MMA issuer ---- */
-        const uint32_t idesc = umma_idesc_bf16(NB);
+        const uint32_t idesc = umma_idesc_bf16(Cfg::kMmaN);
         bool ok = true;
         for (int it = 0; it < n_it && ok; it++) {
             const int s = it % Cfg::kStages, use = it / Cfg::kStages;
@@ -233,13 +317,19 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             tc_fence_after();
             const unsigned char *sa = stages + (size_t)s * Cfg::kStage;
             const uint64_t adesc = umma_desc_k_sw128(sa);
+            /* 16 BF16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units */
+            if (Cfg::kFusedTerms) {
+                const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::kStageA);
 #pragma unroll
-            for (int j = 0; j < kTcTerms; j++) {
-                const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::kStageA + j * Cfg::kTermB);
+                for (int k = 0; k < kTcBlockK / 16; k++)
+                    umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (it | k) != 0 ? 1u : 0u);
+            } else {
 #pragma unroll
-                for (int k = 0; k < kTcBlockK / 16; k++) {
-                    /* 16 BF16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units */
-                    umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (it | j | k) != 0 ? 1u : 0u);
+                for (int j = 0; j < kTcTerms; j++) {
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::kStageA + j * Cfg::kTermB);
+#pragma unroll
+                    for (int k = 0; k < kTcBlockK / 16; k++)
+                        umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (it | j | k) != 0 ? 1u : 0u);
                 }
             }
             umma_commit(&empty[s]);   /* stage reusable once these MMAs have read it */
@@ -247,6 +337,18 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         umma_commit(accum);           /* accumulator complete (arrives at once when nothing was issued) */
     } else if (warp < 4) {
         /* ---- epilogue: TMEM -> registers -> global ---- */
+        /* Everything below reads or writes what earlier kernels of the stream own. While the main
+         * loop runs, fetch the per-row RMSNorm scale: the activations went in as x*gain and
+         * 1/sqrt(mean(x^2)+eps) is applied to the accumulators (voxtral_tts_kernels.c:333-349). */
+        pdl_wait();
+        if (ka.ssq) {
+            for (int m = threadIdx.x; m < M; m += 128) {
+                float t = 0.0f;
+                for (int c = 0; c < ka.ssq_chunks; c++) t += __ldcg(ka.ssq + m * ka.ssq_chunks + c);
+                rscale[m] = 1.0f / sqrtf(t / (float)K + ka.eps);
+            }
+            vb_named_bar(1, 128);
+        }
         bool ok = vb_mbar_wait(accum, 0u, abort_flag);
         if (!ok) {
             atomicCAS(status, 0, 13);
@@ -259,14 +361,35 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             for (int c0 = 0; c0 < NB && c0 < M; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                if (Cfg::kFusedTerms) {
+                    /* column groups NB and 2*NB hold the lo and lo2 products: add them in */
+                    uint32_t r1[16], r2[16];
+                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(NB + c0), r1);
+                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(2 * NB + c0), r2);
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        r[i] = __float_as_uint((__uint_as_float(r[i]) + __uint_as_float(r1[i])) + __uint_as_float(r2[i]));
+                }
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const int m = c0 + i;
-                    const float v = __uint_as_float(r[i]);
-                    if (epi == TC_EPI_SWIGLU) {
+                    float v = __uint_as_float(r[i]);
+                    if (ka.ssq && m < M) v *= rscale[m];
+                    if (epi == TC_EPI_SWIGLU || epi == TC_EPI_SWIGLU_TERMS) {
                         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-                        if (m < M && row < N && (lane & 1) == 0)
-                            out[(size_t)m * ld_out + (row >> 1)] = (v / (1.0f + expf(-v))) * other;
+                        if (m < M && row < N && (lane & 1) == 0) {
+                            const float res = (v / (1.0f + expf(-v))) * other;
+                            if (epi == TC_EPI_SWIGLU) {
+                                out[(size_t)m * ld_out + (row >> 1)] = res;
+                            } else {
+                                uint16_t t0, t1, t2;
+                                vb_split3(res, t0, t1, t2);
+                                const size_t ko = (size_t)(N >> 1), o = (size_t)m * ko + (row >> 1);
+                                ka.out_terms[o] = t0;
+                                ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = t1;
+                                ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
+                            }
+                        }
                     } else if (m < M && row < N) {
                         if (epi == TC_EPI_STORE) out[(size_t)m * ld_out + row] = v + (bias ? __ldg(bias + row) : 0.0f);
                         else out[((size_t)sp * M + m) * ld_out + row] = v;
@@ -295,8 +418,7 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 }
 
 template <int NB>
-static int launch_tc(const TcWeight &w, const TcActs &a, int M, float *out, int ld_out, int splits, int epi,
-                     const float *bias, int *d_status, cudaStream_t st) {
+static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, cudaStream_t st) {
     using Cfg = TcCfg<NB>;
     static bool attr = false;
     if (!attr) {
@@ -306,84 +428,97 @@ static int launch_tc(const TcWeight &w, const TcActs &a, int M, float *out, int 
         attr = true;
     }
     const int tiles = (w.N + kTcTileN - 1) / kTcTileN;
-    vb_tc_gemm_kernel<NB><<<tiles * splits, kTcThreads, Cfg::kSmemBytes, st>>>(
-        w.map, a.map, w.N, w.K, M, a.rows_pad, out, ld_out, splits, epi, bias, d_status);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return launch_pdl(vb_tc_gemm_kernel<NB>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
+                      w.map, a.map, ka) == cudaSuccess
+               ? 0
+               : -1;
 }
 
-int tc_gemm(const TcWeight &w, const TcActs &a, int M, float *out, int ld_out, int splits, int epi,
-            const float *bias, int *d_status, cudaStream_t st) {
-    if (!w.ok || !a.ok || w.K != a.K || M < 1 || M > a.rows_pad) return -1;
-    if (splits < 1 || splits > kTcMaxSplits || splits > w.K / kTcBlockK) return -1;
-    if (epi != TC_EPI_PARTIAL && splits != 1) return -1;
-    if (epi == TC_EPI_SWIGLU && (w.N & 1)) return -1;
+int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st) {
+    if (!w.ok || !a.ok || w.K != a.K || g.M < 1 || g.M > a.rows_pad) return -1;
+    if (g.splits < 1 || g.splits > kTcMaxSplits || g.splits > w.K / kTcBlockK) return -1;
+    if (g.epi != TC_EPI_PARTIAL && g.splits != 1) return -1;
+    if ((g.epi == TC_EPI_SWIGLU || g.epi == TC_EPI_SWIGLU_TERMS) && (w.N & 1)) return -1;
+    if (g.epi == TC_EPI_SWIGLU_TERMS && (!g.out_terms || g.out_rows_pad < g.M)) return -1;
+    TcKernelArgs ka;
+    ka.a_tiled = w.tiled ? 1 : 0;
+    ka.N = w.N; ka.K = w.K; ka.M = g.M; ka.rows_pad = a.rows_pad; ka.ld_out = g.ld_out; ka.splits = g.splits;
+    ka.epi = g.epi; ka.out = g.out; ka.bias = g.bias; ka.ssq = g.ssq; ka.ssq_chunks = g.ssq_chunks; ka.eps = g.eps;
+    ka.out_terms = g.out_terms; ka.out_rows_pad = g.out_rows_pad; ka.status = g.status;
     switch (a.rows_pad) {
-    case 16: return launch_tc<16>(w, a, M, out, ld_out, splits, epi, bias, d_status, st);
-    case 64: return launch_tc<64>(w, a, M, out, ld_out, splits, epi, bias, d_status, st);
-    case 256: return launch_tc<256>(w, a, M, out, ld_out, splits, epi, bias, d_status, st);
+    case 16: return launch_tc<16>(w, a, ka, st);
+    case 64: return launch_tc<64>(w, a, ka, st);
+    case 256: return launch_tc<256>(w, a, ka, st);
     default: return -1;
     }
 }
 
 /* ---------------------------------------------------------------- prepare */
-/* One CTA per activation row: v = x (or residual + sum of split-K partials), optional
- * RMSNorm (voxtral_tts_kernels.c:333-349), then the three BF16 terms. */
+/* Activation rows -> three BF16 terms. grid = (K / 1024, M), 256 threads x 4 columns.
+ *   v = x                                   (plain)
+ *   v = residual + sum_p partials[p]        (split-K reduction in fixed order + residual add)
+ * optional: x_out = v (the new residual stream); with a gain, the terms hold v*gain and the
+ * CTA's sum of v^2 goes to ssq[m][chunk] - the consumer GEMM applies 1/sqrt(mean+eps), so no
+ * CTA has to see a whole row and the kernel is a few microseconds instead of a serial pass. */
 __global__ void vb_tc_prepare_kernel(uint16_t *buf, int rows_pad, int K, const float *x, int ldx,
-                                     const float *partials, int n_part, size_t part_stride, int M,
-                                     const float *residual, float *x_out, const float *gain, float eps) {
-    extern __shared__ float row_smem[];
-    __shared__ float red[32];
-    const int m = blockIdx.x;
+                                     const float *partials, int n_part, size_t part_stride,
+                                     const float *residual, float *x_out, const float *gain, float *ssq) {
+    __shared__ float red[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < K; c += blockDim.x) {
-        float v;
+    if (c < K) {
+        float4 v;
         if (partials) {
-            v = 0.0f;
-            for (int p = 0; p < n_part; p++) v += partials[(size_t)p * part_stride + (size_t)m * K + c];
-            if (residual) v = residual[(size_t)m * ldx + c] + v;
+            v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 0; p < n_part; p++) {
+                const float4 t = *reinterpret_cast<const float4 *>(partials + (size_t)p * part_stride + (size_t)m * K + c);
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            if (residual) {
+                const float4 r = *reinterpret_cast<const float4 *>(residual + (size_t)m * ldx + c);
+                v.x = r.x + v.x; v.y = r.y + v.y; v.z = r.z + v.z; v.w = r.w + v.w;
+            }
         } else {
-            v = x[(size_t)m * ldx + c];
+            v = *reinterpret_cast<const float4 *>(x + (size_t)m * ldx + c);
         }
-        if (x_out) x_out[(size_t)m * ldx + c] = v;
-        row_smem[c] = v;
-        ss += v * v;
+        if (x_out) *reinterpret_cast<float4 *>(x_out + (size_t)m * ldx + c) = v;
+        ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (gain) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(gain + c));
+            v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
+        }
+        const float e[4] = {v.x, v.y, v.z, v.w};
+        uint16_t t0[4], t1[4], t2[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) vb_split3(e[i], t0[i], t1[i], t2[i]);
+        const size_t o = (size_t)m * K + c, term = (size_t)rows_pad * K;
+        *reinterpret_cast<uint2 *>(buf + o) = make_uint2(t0[0] | ((uint32_t)t0[1] << 16), t0[2] | ((uint32_t)t0[3] << 16));
+        *reinterpret_cast<uint2 *>(buf + term + o) = make_uint2(t1[0] | ((uint32_t)t1[1] << 16), t1[2] | ((uint32_t)t1[3] << 16));
+        *reinterpret_cast<uint2 *>(buf + 2 * term + o) = make_uint2(t2[0] | ((uint32_t)t2[1] << 16), t2[2] | ((uint32_t)t2[3] << 16));
     }
-    float inv = 1.0f;
-    if (gain) {
+    if (ssq) {
         ss = vb_warp_sum(ss);
         if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
         __syncthreads();
-        float t = 0.0f;
-        for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += red[w];
-        inv = 1.0f / sqrtf(t / (float)K + eps);
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < K; c += blockDim.x) {
-        float v = row_smem[c];
-        if (gain) v = v * inv * gain[c];
-        const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
-        const float r1 = v - __bfloat162float(h0);
-        const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
-        const float r2 = r1 - __bfloat162float(h1);
-        const __nv_bfloat16 h2 = __float2bfloat16_rn(r2);
-        buf[((size_t)0 * rows_pad + m) * K + c] = __bfloat16_as_ushort(h0);
-        buf[((size_t)1 * rows_pad + m) * K + c] = __bfloat16_as_ushort(h1);
-        buf[((size_t)2 * rows_pad + m) * K + c] = __bfloat16_as_ushort(h2);
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += red[w];
+            ssq[m * gridDim.x + blockIdx.x] = t;
+        }
     }
 }
 
+int tc_prepare_chunks(int K) { return (K + 1023) / 1024; }
+
 void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float *partials, int n_part,
-                size_t part_stride, const float *residual, float *x_out, const float *gain, float eps,
+                size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
                 cudaStream_t st) {
     if (M <= 0) return;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(vb_tc_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        attr = true;
-    }
-    vb_tc_prepare_kernel<<<M, 512, (size_t)acts.K * sizeof(float), st>>>(acts.buf, acts.rows_pad, acts.K, x, ldx,
-                                                                        partials, n_part, part_stride, M, residual,
-                                                                        x_out, gain, eps);
+    launch_pdl(vb_tc_prepare_kernel, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf, acts.rows_pad,
+               acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq);
 }
 
 /* y[i] = sum over the split-K partials in fixed order (+ bias[i % N]). */

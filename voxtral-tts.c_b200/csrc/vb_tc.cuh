@@ -16,6 +16,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 namespace vb {
 
@@ -25,9 +27,10 @@ constexpr int kTcTerms = 3;       /* BF16 terms per fp32 activation */
 constexpr int kTcMaxSplits = 8;   /* split-K factor limit (partials are summed in fixed order) */
 
 enum TcEpilogue {
-    TC_EPI_PARTIAL = 0,  /* out[split][m][n] = partial sum (fp32) */
-    TC_EPI_STORE = 1,    /* splits == 1: out[m][n] = sum (+ bias[n]) */
-    TC_EPI_SWIGLU = 2    /* splits == 1, rows interleaved (gate, up): out[m][n/2] = silu(gate) * up */
+    TC_EPI_PARTIAL = 0,       /* out[split][m][n] = partial sum (fp32) */
+    TC_EPI_STORE = 1,         /* splits == 1: out[m][n] = sum (+ bias[n]) */
+    TC_EPI_SWIGLU = 2,        /* splits == 1, rows interleaved (gate, up): out[m][n/2] = silu(gate) * up */
+    TC_EPI_SWIGLU_TERMS = 3   /* same value, written as three BF16 terms for the next GEMM */
 };
 
 /* One weight matrix prepared for the tensor-core path. */
@@ -36,6 +39,7 @@ struct TcWeight {
     const uint16_t *W;
     int N, K;
     bool ok;
+    bool tiled;          /* W points at the tile-contiguous copy (tc_weight_tiled) */
 };
 
 /* Activation rows split into BF16 terms: [terms][rows_pad][K], rows_pad = 16, 64 or 256. */
@@ -46,26 +50,61 @@ struct TcActs {
     bool ok;
 };
 
+/* One GEMM launch. */
+struct TcGemm {
+    int M = 0, splits = 1, epi = TC_EPI_STORE;
+    float *out = nullptr;
+    int ld_out = 0;
+    const float *bias = nullptr;
+    const float *ssq = nullptr;       /* [M][ssq_chunks] sums of squares of the un-normalised rows:  */
+    int ssq_chunks = 0;               /* the result is scaled by 1/sqrt(sum/K + eps) per row          */
+    float eps = 0.0f;
+    uint16_t *out_terms = nullptr;    /* TC_EPI_SWIGLU_TERMS destination [3][out_rows_pad][N/2] */
+    int out_rows_pad = 0;
+    int *status = nullptr;            /* device int, set non-zero when a bounded wait runs out */
+};
+
 int tc_init();                                     /* resolves cuTensorMapEncodeTiled; 0 when usable */
 int tc_weight(TcWeight *w, const uint16_t *d_W, int N, int K);
+/* Same, on a tile-contiguous copy of W written to d_tiled (tc_tiled_bytes(N, K) bytes). */
+int tc_weight_tiled(TcWeight *w, const uint16_t *d_W, int N, int K, uint16_t *d_tiled, cudaStream_t st);
+size_t tc_tiled_bytes(int N, int K);
 int tc_acts(TcActs *a, uint16_t *d_buf, int rows_pad, int K);
 size_t tc_acts_bytes(int rows_pad, int K);
 int tc_rows_pad(int M);                            /* 16, 64, 256; 0 when M is too large */
 int tc_pick_splits(int N, int K, int n_sm);
+int tc_prepare_chunks(int K);                      /* column chunks (and ssq entries) per row */
 
-/* x[M,K] fp32 (optionally: sum of `n_part` partial buffers + residual, optionally RMS-normalised
- * with `gain`) -> BF16 terms in `acts`; optionally also stores the summed fp32 rows to x_out. */
+/* Rows -> BF16 terms in `acts`. Source: x[M, ldx], or residual[M, ldx] + the sum of n_part
+ * split-K partial buffers ([M, K] each, part_stride floats apart). x_out (optional) receives the
+ * fp32 rows. With `gain` the terms hold row*gain and ssq[m][chunk] the chunk's sum of squares
+ * (RMSNorm's scalar is applied by the consuming GEMM). */
 void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float *partials, int n_part,
-                size_t part_stride, const float *residual, float *x_out, const float *gain, float eps,
+                size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
                 cudaStream_t st);
 
-/* Launches the GEMM. out layout by epilogue (see TcEpilogue). status: device int, set non-zero
- * when a bounded wait runs out. */
-int tc_gemm(const TcWeight &w, const TcActs &acts, int M, float *out, int ld_out, int splits, int epi,
-            const float *bias, int *d_status, cudaStream_t st);
+int tc_gemm(const TcWeight &w, const TcActs &acts, const TcGemm &g, cudaStream_t st);
 
 void tc_reduce(float *y, const float *partials, int n_part, size_t stride, size_t count, const float *bias, int N,
                cudaStream_t st);
+
+/* Launch with the programmatic-stream-serialization attribute: the kernel may begin (weight
+ * prefetch, barrier set-up, TMEM allocation) while its predecessor in the stream is still
+ * running; whatever depends on the predecessor sits behind griddepcontrol.wait in the kernel.
+ * VB200_NO_PDL=1 turns the attribute off. */
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    static const bool no_pdl = getenv("VB200_NO_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 } // namespace vb
 
