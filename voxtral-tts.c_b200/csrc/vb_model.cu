@@ -246,6 +246,7 @@ int model_upload_llm(const vb200_decoder_weights_t *w) {
     g_cuda.tok_embeddings_gpu = m.tok_emb;
     g_cuda.dec_norm_gpu = m.dec_norm;
     m.llm_ready = true;
+    prefill_tc_setup();
     return model_rebuild_programs();
 }
 

@@ -10,6 +10,7 @@
  */
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
+#include "vb_tc.cuh"
 
 #include <math.h>
 #include <stdio.h>
@@ -43,6 +44,115 @@ static int run_row_blocks(VbOp proto, int M, int x_ld, int y_ld, bool res_is_y) 
     return 0;
 }
 
+/* ---- tensor-core prefill ---- */
+struct PrefillTc {
+    bool ready = false;
+    TcWeight wqkv[VB200_DEC_LAYERS], wo[VB200_DEC_LAYERS], w13[VB200_DEC_LAYERS], w2[VB200_DEC_LAYERS];
+    uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
+    float *part = nullptr, *ssq = nullptr;
+    TcActs aD[3], aQ[3], aH[3];   /* for 16, 64 and 256 padded rows, over the same buffers */
+};
+static PrefillTc g_pf;
+static const int kPfRows = 256;
+
+static int pf_slot(int rows_pad) { return rows_pad == 16 ? 0 : rows_pad == 64 ? 1 : 2; }
+
+/* Tensor maps of the decoder weights and the activation-term buffers; called after the
+ * decoder upload. Failing here is not fatal: prefill() then uses the streaming kernel. */
+int prefill_tc_setup() {
+    Model &m = model();
+    PrefillTc &t = g_pf;
+    t.ready = false;
+    if (getenv("VB200_NO_TC") || tc_init()) return 0;
+    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+        const LayerDev &L = m.dec[l];
+        if (tc_weight(&t.wqkv[l], L.wqkv, QKV, D) || tc_weight(&t.wo[l], L.wo, D, QD) ||
+            tc_weight(&t.w13[l], L.w13, 2 * HID, D) || tc_weight(&t.w2[l], L.w2, D, HID))
+            return 0;
+    }
+    if (!t.bD) {
+        void *p[5] = {};
+        const size_t sz[5] = {tc_acts_bytes(kPfRows, D), tc_acts_bytes(kPfRows, QD), tc_acts_bytes(kPfRows, HID),
+                              sizeof(float) * (size_t)kTcMaxSplits * kPfRows * QKV, sizeof(float) * kPfRows * 16};
+        for (int i = 0; i < 5; i++) {
+            if (cudaMalloc(&p[i], sz[i]) != cudaSuccess) return 0;
+            m.allocs.push_back(p[i]);
+            cudaMemset(p[i], 0, sz[i]);
+        }
+        t.bD = (uint16_t *)p[0]; t.bQ = (uint16_t *)p[1]; t.bH = (uint16_t *)p[2];
+        t.part = (float *)p[3]; t.ssq = (float *)p[4];
+    }
+    const int pads[3] = {16, 64, 256};
+    for (int i = 0; i < 3; i++)
+        if (tc_acts(&t.aD[i], t.bD, pads[i], D) || tc_acts(&t.aQ[i], t.bQ, pads[i], QD) ||
+            tc_acts(&t.aH[i], t.bH, pads[i], HID))
+            return 0;
+    t.ready = true;
+    return 0;
+}
+
+/* Prefill with the tcgen05 GEMM (vb_tc.cu): per layer and per block of up to 256 rows
+ * gain+terms -> QKV -> RoPE -> cache rows; causal attention over the whole cache prefix;
+ * terms -> O -> residual+gain+terms -> gate/up with SwiGLU -> down -> residual. */
+static int prefill_tc(float *x, float *qkv, float *attn, const float *cs, int M, int start_pos) {
+    Model &m = model();
+    PrefillTc &t = g_pf;
+    cudaStream_t st = m.st;
+    const float scale = 1.0f / sqrtf((float)VB200_HEAD_DIM);
+    const int s_qkv = tc_pick_splits(QKV, D, m.sm_count), s_wo = tc_pick_splits(D, QD, m.sm_count),
+              s_w2 = tc_pick_splits(D, HID, m.sm_count);
+    const int chunksD = tc_prepare_chunks(D);
+    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+        const LayerDev &L = m.dec[l];
+        for (int r0 = 0; r0 < M; r0 += kPfRows) {
+            const int rows = M - r0 < kPfRows ? M - r0 : kPfRows;
+            const int slot = pf_slot(tc_rows_pad(rows));
+            float *xr = x + (size_t)r0 * D, *qr = qkv + (size_t)r0 * QKV;
+            tc_prepare(t.aD[slot], xr, D, rows, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
+            TcGemm g;
+            g.M = rows; g.status = &m.d_out->status; g.epi = TC_EPI_PARTIAL; g.out = t.part; g.ld_out = QKV;
+            g.splits = s_qkv; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+            if (tc_gemm(t.wqkv[l], t.aD[slot], g, st)) return -1;
+            tc_reduce(qr, t.part, s_qkv, (size_t)rows * QKV, (size_t)rows * QKV, nullptr, QKV, st);
+            rope_apply(qr, cs + (size_t)r0 * VB200_HEAD_DIM, rows, VB200_HEADS, VB200_HEAD_DIM, QKV, st);
+            rope_apply(qr + QD, cs + (size_t)r0 * VB200_HEAD_DIM, rows, VB200_KV_HEADS, VB200_HEAD_DIM, QKV, st);
+            float *ck = m.kv_k + ((size_t)l * m.kv_max + start_pos + r0) * KVD;
+            float *cv = m.kv_v + ((size_t)l * m.kv_max + start_pos + r0) * KVD;
+            if (cudaMemcpy2DAsync(ck, (size_t)KVD * 4, qr + QD, (size_t)QKV * 4, (size_t)KVD * 4, rows,
+                                  cudaMemcpyDeviceToDevice, st) != cudaSuccess ||
+                cudaMemcpy2DAsync(cv, (size_t)KVD * 4, qr + QD + KVD, (size_t)QKV * 4, (size_t)KVD * 4, rows,
+                                  cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+                return -1;
+        }
+        const float *k0 = m.kv_k + (size_t)l * m.kv_max * KVD, *v0 = m.kv_v + (size_t)l * m.kv_max * KVD;
+        if (attention_rows(attn, qkv, k0, v0, M, start_pos + M, VB200_HEADS, VB200_KV_HEADS, VB200_HEAD_DIM, scale,
+                           start_pos, 1, QKV, KVD, QD, st))
+            return -1;
+        if (l == VB200_DEC_LAYERS - 1) break;   /* only the cache is kept (voxtral_tts_llm.c:281) */
+        for (int r0 = 0; r0 < M; r0 += kPfRows) {
+            const int rows = M - r0 < kPfRows ? M - r0 : kPfRows;
+            const int rp = tc_rows_pad(rows), slot = pf_slot(rp);
+            float *xr = x + (size_t)r0 * D;
+            const size_t psD = (size_t)rows * D;
+            tc_prepare(t.aQ[slot], attn + (size_t)r0 * QD, QD, rows, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, st);
+            TcGemm g;
+            g.M = rows; g.status = &m.d_out->status; g.epi = TC_EPI_PARTIAL; g.out = t.part; g.ld_out = D;
+            g.splits = s_wo;
+            if (tc_gemm(t.wo[l], t.aQ[slot], g, st)) return -1;
+            tc_prepare(t.aD[slot], nullptr, D, rows, t.part, s_wo, psD, xr, xr, L.ffn_norm, t.ssq, st);
+            g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = rp; g.splits = 1;
+            g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+            if (tc_gemm(t.w13[l], t.aD[slot], g, st)) return -1;
+            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr; g.splits = s_w2; g.ld_out = D;
+            g.ssq = nullptr; g.ssq_chunks = 0;
+            if (tc_gemm(t.w2[l], t.aH[slot], g, st)) return -1;
+            /* residual add (the terms it also writes are overwritten by the next layer's prepare) */
+            tc_prepare(t.aD[slot], nullptr, D, rows, t.part, s_w2, psD, xr, xr, nullptr, nullptr, st);
+        }
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
 int prefill(const float *embeds, int seq_len, int start_pos) {
     Model &m = model();
     if (!m.inited || !m.llm_ready) return -1;
@@ -64,6 +174,18 @@ int prefill(const float *embeds, int seq_len, int start_pos) {
     if (!rc && cudaMemcpyAsync(x, embeds, (size_t)M * D * 4, cudaMemcpyDefault, m.st) != cudaSuccess) rc = -1;
     if (!rc) rope_table(cs, start_pos, M, VB200_HEAD_DIM, VB200_ROPE_THETA, m.st);
 
+    if (!rc && g_pf.ready) {
+        rc = prefill_tc(x, qkv, attn, cs, M, start_pos);
+        if (cudaStreamSynchronize(m.st) != cudaSuccess) rc = -1;
+        cudaFree(x); cudaFree(qkv); cudaFree(attn); cudaFree(h); cudaFree(cs);
+        if (!rc) {
+            int status = 0;
+            cudaMemcpy(&status, &m.d_out->status, sizeof(int), cudaMemcpyDeviceToHost);
+            m.last_status = status;
+            if (status) rc = -1;
+        }
+        return rc;
+    }
     for (int l = 0; l < VB200_DEC_LAYERS && !rc; l++) {
         const LayerDev &L = m.dec[l];
         float *ck = m.kv_k + ((size_t)l * m.kv_max + start_pos) * KVD;
