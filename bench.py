@@ -370,20 +370,49 @@ def main():
         dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
     e2e_value = world * Ke / float(t_e.item())
 
-    # ---- roofline of the frame kernel -----------------------------------------------------------
+    # ---- roofline of the dominant kernel --------------------------------------------------------
+    # Per frame the work is one launch of vb_engine_kernel (re-embedding, the 26-layer decoder
+    # step, semantic head + llm token: the streaming GEMV path) followed, when the tensor-core
+    # path is up, by 84 vb_tc_gemm_kernel launches (the acoustic layers, 7 steps x 3 layers x 4
+    # matrices) and small glue kernels. The frame kernel has the largest share of the frame; its
+    # launches are timed one by one with CUDA events inside the timed region.
     peak, peak_src = measured_hbm_peak()
-    mean_bytes = float(np.mean([frame_bytes(PROMPT_ROWS + W + f) for f in range(K)]))
-    launch_ms = total_ms / K
-    achieved = mean_bytes / (launch_ms / 1000.0) / 1e9
+    n_eng = C.c_int(0)
+    eng_ms_total = float(Lb.vb200_utterance_engine_ms(C.byref(n_eng)))
+    tc_path = os.environ.get("VB200_NO_TC") is None
+    head_bytes = 51_118_080 + 18_874_368                      # semantic head + llm_proj
+    dec_bytes = lambda pos: LLM_WEIGHT_BYTES + LLM_NORM_BYTES + 26 * (pos + 1) * 8192 + KV_WRITE_BYTES
+    mean_frame_bytes = float(np.mean([frame_bytes(PROMPT_ROWS + W + f) for f in range(K)]))
+    if tc_path and n_eng.value == K:
+        eng_bytes = float(np.mean([dec_bytes(PROMPT_ROWS + W + f) for f in range(K)])) + head_bytes + REEMBED_BYTES
+        launch_ms = eng_ms_total / n_eng.value
+        kernel_desc = "vb_engine_kernel (one launch per frame: re-embedding + decoder step + semantic head)"
+    else:                                                     # whole frame inside the frame kernel
+        eng_bytes = mean_frame_bytes
+        launch_ms = (eng_ms_total / n_eng.value) if n_eng.value == K else total_ms / K
+        kernel_desc = "vb_engine_kernel (one launch = one whole frame)"
+    achieved = eng_bytes / (launch_ms / 1000.0) / 1e9
     traffic = None
     try:
         with open(os.path.join(ROOT, "profiles", "frame_kernel_traffic.json")) as f:
-            traffic = json.load(f).get("dram_bytes_per_launch")
+            ratio = json.load(f).get("dram_read_over_algorithmic")
+            traffic = eng_bytes * ratio if ratio else None
     except Exception:
         pass
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "kernel": "vb_engine_kernel (one launch = one frame)",
-                "algorithmic_bytes_per_launch": mean_bytes, "launch_ms": launch_ms, "peak_source": peak_src}
+                "traffic": traffic, "kernel": kernel_desc, "algorithmic_bytes_per_launch": eng_bytes,
+                "launch_ms": launch_ms, "share_of_frame_time": launch_ms / (total_ms / K), "peak_source": peak_src,
+                "whole_frame": {"algorithmic_bytes": mean_frame_bytes, "ms": total_ms / K,
+                                "achieved": mean_frame_bytes / (total_ms / K / 1000.0) / 1e9,
+                                "frac": mean_frame_bytes / (total_ms / K / 1000.0) / 1e9 / peak}}
+    if tc_path and n_eng.value == K:
+        rest_ms = total_ms / K - launch_ms
+        ac_bytes = ACOUSTIC_BYTES - head_bytes
+        roofline["acoustic_tensor_core_path"] = {
+            "kernels": "84 x vb_tc_gemm_kernel<16> + prepare / attention / velocity / FSQ glue, one CUDA graph",
+            "algorithmic_bytes": ac_bytes, "ms": rest_ms, "achieved": ac_bytes / (rest_ms / 1000.0) / 1e9,
+            "frac": ac_bytes / (rest_ms / 1000.0) / 1e9 / peak}
+    launches_per_frame = 1 + (84 + 42 + 21 + 14 + 1 if tc_path else 0)
 
     if rank != 0:
         eng.close()
@@ -403,7 +432,7 @@ def main():
             "data": "synthetic", "config": config, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "frames/s", "steps": Ke,
                     "h2d_bytes_per_step": 16 + 3072 * 4 + 36 * 4, "d2h_bytes_per_step": 176 + 3072 * 4},
-            "gpu_launches": K, "roofline": roofline, "cpu_baseline": cpu}
+            "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line))
 
 

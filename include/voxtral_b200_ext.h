@@ -50,6 +50,9 @@ int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows);
 int vb200_utterance_begin(const float *first_embed, int start_pos, const float *noise, int n_frames);
 int vb200_utterance_run(int n_frames);
 int vb200_utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
+/* Device time (ms, CUDA events) spent inside the frame-kernel launches of the last
+ * vb200_utterance_run batch, and how many launches that was. */
+double vb200_utterance_engine_ms(int *launches);
 /* Options by name. "ignore_end" (0/1): a device-resident run started after this call
  * treats END as an ordinary code, for fixed-length timing runs. Returns -1 for an
  * unknown name. */

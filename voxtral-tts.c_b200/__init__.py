@@ -89,6 +89,7 @@ def lib():
         "vb200_utterance_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
         "vb200_utterance_run": (C.c_int, [C.c_int]),
         "vb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
+        "vb200_utterance_engine_ms": (C.c_double, [i32p]),
         "vb200_utterance_end": (C.c_int, [C.c_void_p, i32p, i32p, f32p]),
         "vb200_kv_write": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
         "vb200_kv_read": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

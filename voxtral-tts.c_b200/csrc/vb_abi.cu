@@ -159,6 +159,11 @@ int vb200_utterance_begin(const float *first_embed, int start_pos, const float *
 
 int vb200_utterance_run(int n_frames) { return utterance_run(n_frames); }
 
+double vb200_utterance_engine_ms(int *launches) {
+    if (launches) *launches = model().run_engine_n;
+    return model().run_engine_ms;
+}
+
 int vb200_set_option(const char *name, int value) {
     if (!name) return -1;
     if (!strcmp(name, "ignore_end")) { model().ignore_end = value != 0; return 0; }

@@ -727,10 +727,22 @@ int utterance_run(int n) {
     if (!m.noise_all || n < 0) return -1;
     const bool timing = m.timing;
     m.timing = false;                      /* one event pair around the whole batch instead */
+    m.run_ev_used = 0;
     cudaEventRecord(m.evr0, m.st);
     for (int i = 0; i < n; i++) {
         if (m.run_launched >= m.run_cap) break;
+        /* the frame kernel's own device time: one event pair per launch */
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        if (m.run_ev.size() < 2 * (size_t)(m.run_ev_used + 1)) {
+            if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
+                m.run_ev.push_back(e0);
+                m.run_ev.push_back(e1);
+            }
+        }
+        const bool timed = m.run_ev.size() >= 2 * (size_t)(m.run_ev_used + 1);
+        if (timed) cudaEventRecord(m.run_ev[2 * m.run_ev_used], m.st);
         if (run_program(m.run_launched == 0 ? m.p_run_first : m.p_run_next)) return -1;
+        if (timed) cudaEventRecord(m.run_ev[2 * m.run_ev_used++ + 1], m.st);
         if (acoustic_tc_ready() && acoustic_tc_enqueue(m.noise_all, m.codes_all, m.run_cap, true, m.ignore_end))
             return -1;
         m.run_launched++;
@@ -749,6 +761,15 @@ int utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_
     VB_CHECK(cudaMemcpyAsync(&m.h_in->dyn, &m.d_in->dyn, sizeof(VbDyn), cudaMemcpyDeviceToHost, m.st));
     VB_CHECK(cudaStreamSynchronize(m.st));
     if (device_ms && cudaEventElapsedTime(device_ms, m.evr0, m.evr1) != cudaSuccess) *device_ms = -1.0f;
+    m.run_engine_ms = 0.0;
+    m.run_engine_n = 0;
+    for (int i = 0; i < m.run_ev_used; i++) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, m.run_ev[2 * i], m.run_ev[2 * i + 1]) == cudaSuccess) {
+            m.run_engine_ms += ms;
+            m.run_engine_n++;
+        }
+    }
     const int done = m.h_in->dyn.frame;
     const int end = m.h_in->dyn.done;
     if (frames_done) *frames_done = done;

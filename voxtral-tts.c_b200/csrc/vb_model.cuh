@@ -85,6 +85,9 @@ struct Model {
     float *noise_all = nullptr;   /* device-resident run: [frames, 36] */
     int *codes_all = nullptr;     /* [frames, 37] */
     int run_cap = 0, run_launched = 0;
+    std::vector<cudaEvent_t> run_ev;   /* event pairs around the frame-kernel launches of a run */
+    int run_ev_used = 0, run_engine_n = 0;
+    double run_engine_ms = 0.0;
 
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, evr0 = nullptr, evr1 = nullptr;
     double ms_sum = 0.0;
