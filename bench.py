@@ -57,6 +57,25 @@ def load_package():
     return mod
 
 
+def utterance_seeds(rank):
+    """Each rank generates its own utterance (prompt and noise seeds): independent units, no
+    data-path collective."""
+    return {"prompt": 100 + rank, "noise": 1000 + rank}
+
+
+def aggregate(local_ms, frames_per_rank, dist=None, device="cuda"):
+    """Whole-job frames/s: every rank ran frames_per_rank frames in local_ms of device time; the
+    job took the slowest rank's time. Returns (frames_per_s, max_ms)."""
+    import torch
+    t = torch.tensor([float(local_ms)], dtype=torch.float64, device=device)
+    world = 1
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        world = dist.get_world_size()
+    max_ms = float(t.item())
+    return world * frames_per_rank / (max_ms / 1000.0), max_ms
+
+
 def frame_bytes(pos):
     """Algorithmic HBM bytes of one frame decoded at cache row `pos` (keys = pos + 1)."""
     return (LLM_WEIGHT_BYTES + LLM_NORM_BYTES + 26 * (pos + 1) * 8192 + KV_WRITE_BYTES + ACOUSTIC_BYTES
@@ -317,10 +336,11 @@ def main():
     eng.upload(model, decoder=True, acoustic=True, audio_table=True)
     eng.L.vb200_set_option(b"ignore_end", 1)
 
-    rows = prompt_rows(pkg, model, 100 + rank)
+    seeds = utterance_seeds(rank)
+    rows = prompt_rows(pkg, model, seeds["prompt"])
     eng.prefill(rows, 0)
     first = model.token_rows([24])[0]                      # embed(AUDIO), voxtral_tts.c:295
-    noise = noise_rows(1000 + rank, W + K)
+    noise = noise_rows(seeds["noise"], W + K)
 
     # ---- value: device-resident loop -------------------------------------------------------
     sampler = ClockSampler(local_rank)
@@ -340,11 +360,7 @@ def main():
     assert Lb.vb200_utterance_end(codes.ctypes.data, C.byref(done), C.byref(end), C.byref(ms)) == 0
     if done.value != W + K:
         raise SystemExit(f"device loop ran {done.value} of {W + K} frames (status {Lb.vb200_last_status()})")
-    t_ms = torch.tensor([ms.value], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    total_ms = float(t_ms.item())
-    value = world * K / (total_ms / 1000.0)
+    value, total_ms = aggregate(ms.value, K, dist)
 
     # ---- e2e: one host-facing call per frame, re-embedding on the host ------------------------
     Ke = args.e2e_steps or min(K, 64)
@@ -365,10 +381,7 @@ def main():
         e = (table[offs + c].astype(np.uint32) << 16).view(np.float32).sum(axis=0, dtype=np.float32)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
-    t_e = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
-    e2e_value = world * Ke / float(t_e.item())
+    e2e_value, _ = aggregate(e2e_s * 1000.0, Ke, dist)
 
     # ---- roofline of the dominant kernel --------------------------------------------------------
     # Per frame the work is one launch of vb_engine_kernel (re-embedding, the 26-layer decoder
@@ -416,6 +429,8 @@ def main():
 
     if rank != 0:
         eng.close()
+        if dist is not None:
+            dist.destroy_process_group()
         return
 
     cpu = None
@@ -434,6 +449,8 @@ def main():
                     "h2d_bytes_per_step": 16 + 3072 * 4 + 36 * 4, "d2h_bytes_per_step": 176 + 3072 * 4},
             "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
