@@ -53,6 +53,28 @@ int vb200_utterance_end(int *codes_out, int *frames_done, int *hit_end, float *d
 /* Device time (ms, CUDA events) spent inside the frame-kernel launches of the last
  * vb200_utterance_run batch, and how many launches that was. */
 double vb200_utterance_engine_ms(int *launches);
+/* Several independent utterances decoded in lock step on this GPU (no counterpart in the
+ * reference, which synthesises one utterance per process: voxtral_tts.c:301-321 run once
+ * per utterance). Every weight matrix is read once per frame for all utterances: the decoder
+ * step runs as an n-row and the acoustic passes as a 6n-row tensor-core GEMM. Each utterance
+ * has its own cache slab, position, noise and END state.
+ *   open:    1..8 utterances, cache rows per utterance, frames the code/noise arrays hold
+ *   prefill: prompt rows [n_rows, 3072] of one utterance into its cache rows 0..n_rows-1
+ *   begin:   first decoder input rows [n, 3072], first cache row per utterance [n], noise
+ *            [n, max_frames, 36]
+ *   run:     queue up to n_frames more frames for every utterance still running
+ *   end:     wait; codes [n, max_frames, 37] (zero past frames_done[u]), frames_done [n],
+ *            hit_end [n], device time of the last run call
+ *   hidden:  decoder output rows of the last frame [n, 3072] */
+int vb200_batch_open(int n_utterances, int kv_max, int max_frames);
+int vb200_batch_prefill(int utterance, const float *embeds, int n_rows);
+int vb200_batch_begin(const float *first_embeds, const int *start_pos, const float *noise);
+int vb200_batch_run(int n_frames);
+int vb200_batch_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
+int vb200_batch_hidden(float *out);
+int vb200_batch_launches_per_frame(void);
+void vb200_batch_close(void);
+
 /* Options by name. "ignore_end" (0/1): a device-resident run started after this call
  * treats END as an ordinary code, for fixed-length timing runs. Returns -1 for an
  * unknown name. */

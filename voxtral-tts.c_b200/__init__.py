@@ -88,6 +88,14 @@ def lib():
         "vb200_upload_audio_embed": (C.c_int, [C.c_void_p, C.c_int]),
         "vb200_utterance_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
         "vb200_utterance_run": (C.c_int, [C.c_int]),
+        "vb200_batch_open": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+        "vb200_batch_prefill": (C.c_int, [C.c_int, C.c_void_p, C.c_int]),
+        "vb200_batch_begin": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+        "vb200_batch_run": (C.c_int, [C.c_int]),
+        "vb200_batch_end": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, f32p]),
+        "vb200_batch_hidden": (C.c_int, [C.c_void_p]),
+        "vb200_batch_launches_per_frame": (C.c_int, []),
+        "vb200_batch_close": (None, []),
         "vb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
         "vb200_utterance_engine_ms": (C.c_double, [i32p]),
         "vb200_utterance_end": (C.c_int, [C.c_void_p, i32p, i32p, f32p]),
@@ -341,6 +349,36 @@ class Engine:
         self._ok("vb200_utterance_end",
                  self.L.vb200_utterance_end(_ptr(codes), C.byref(done), C.byref(end), C.byref(ms)))
         return codes[:done.value], bool(end.value), ms.value
+
+    def batch(self, prompts, first_embeds, noise, kv_max=None):
+        """Decodes len(prompts) utterances in lock step. prompts: list of [rows, 3072] prompt
+        embeddings; first_embeds [n, 3072]; noise [n, frames, 36]. Returns (codes list of
+        [frames_done, 37], hit_end list, hidden [n, 3072], device_ms)."""
+        n = len(prompts)
+        noise = np.ascontiguousarray(noise, dtype=np.float32).reshape(n, -1, ACOUSTIC_DIM)
+        frames = noise.shape[1]
+        first_embeds = np.ascontiguousarray(first_embeds, dtype=np.float32).reshape(n, DIM)
+        if kv_max is None:
+            kv_max = max(p.shape[0] for p in prompts) + frames + 1
+        self._ok("vb200_batch_open", self.L.vb200_batch_open(n, int(kv_max), frames))
+        try:
+            start = np.zeros(n, dtype=np.int32)
+            for u, p in enumerate(prompts):
+                p = np.ascontiguousarray(p, dtype=np.float32).reshape(-1, DIM)
+                self._ok("vb200_batch_prefill", self.L.vb200_batch_prefill(u, _ptr(p), p.shape[0]))
+                start[u] = p.shape[0]
+            self._ok("vb200_batch_begin", self.L.vb200_batch_begin(_ptr(first_embeds), _ptr(start), _ptr(noise)))
+            self._ok("vb200_batch_run", self.L.vb200_batch_run(frames))
+            codes = np.zeros((n, frames, CODES), dtype=np.int32)
+            done = np.zeros(n, dtype=np.int32)
+            end = np.zeros(n, dtype=np.int32)
+            ms = C.c_float(0.0)
+            self._ok("vb200_batch_end", self.L.vb200_batch_end(_ptr(codes), _ptr(done), _ptr(end), C.byref(ms)))
+            hidden = np.zeros((n, DIM), dtype=np.float32)
+            self._ok("vb200_batch_hidden", self.L.vb200_batch_hidden(_ptr(hidden)))
+        finally:
+            self.L.vb200_batch_close()
+        return [codes[u, :done[u]] for u in range(n)], [bool(e) for e in end], hidden, ms.value
 
     def kv_write(self, layer, pos0, k_rows, v_rows):
         k_rows = np.ascontiguousarray(k_rows, dtype=np.float32)

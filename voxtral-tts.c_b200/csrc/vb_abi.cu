@@ -159,6 +159,19 @@ int vb200_utterance_begin(const float *first_embed, int start_pos, const float *
 
 int vb200_utterance_run(int n_frames) { return utterance_run(n_frames); }
 
+int vb200_batch_open(int n_utterances, int kv_max, int max_frames) { return batch_open(n_utterances, kv_max, max_frames); }
+int vb200_batch_prefill(int utterance, const float *embeds, int n_rows) { return batch_prefill(utterance, embeds, n_rows); }
+int vb200_batch_begin(const float *first_embeds, const int *start_pos, const float *noise) {
+    return batch_begin(first_embeds, start_pos, noise);
+}
+int vb200_batch_run(int n_frames) { return batch_run(n_frames); }
+int vb200_batch_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms) {
+    return batch_end(codes_out, frames_done, hit_end, device_ms);
+}
+int vb200_batch_hidden(float *out) { return batch_hidden(out); }
+int vb200_batch_launches_per_frame(void) { return batch_launches_per_frame(); }
+void vb200_batch_close(void) { batch_close(); }
+
 double vb200_utterance_engine_ms(int *launches) {
     if (launches) *launches = model().run_engine_n;
     return model().run_engine_ms;

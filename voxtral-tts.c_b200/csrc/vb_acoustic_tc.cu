@@ -9,8 +9,7 @@
  * BF16 term split ("prepare"), velocity head, FSQ. The sequence (about 200 launches) is
  * captured once as a CUDA graph and replayed per frame.
  */
-#include "vb_model.cuh"
-#include "vb_tc.cuh"
+#include "vb_acoustic_tc.cuh"
 #include "vb_common.cuh"
 
 #include <math.h>
@@ -22,17 +21,14 @@ namespace vb {
 static const int D = VB200_DIM, QD = VB200_Q_DIM, KVD = VB200_KV_DIM, HID = VB200_HIDDEN;
 static const int QKV = QD + 2 * KVD;
 static const int A = VB200_ACOUSTIC_DIM;
-static const int ROWS = 6;     /* 2 guidance branches x 3 tokens */
+static const int ROWS1 = 6;    /* rows per utterance: 2 guidance branches x 3 tokens */
 
 struct AcTc {
     bool ready = false;
     TcWeight wqkv[VB200_AC_LAYERS], wo[VB200_AC_LAYERS], w13[VB200_AC_LAYERS], w2[VB200_AC_LAYERS];
-    TcActs aD, aQ, aH;
-    uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
-    float *part = nullptr;      /* split-K partials [splits][6][N] */
     uint16_t *tiled[VB200_AC_LAYERS][4] = {};   /* tile-contiguous weight copies */
-    float *ssq = nullptr;       /* per-row, per-chunk sums of squares for the deferred RMSNorm scale */
     int s_qkv = 1, s_wo = 1, s_w2 = 1;
+    AcBuffers one;              /* the single-utterance buffers */
 };
 static AcTc g_ac;
 void acoustic_tc_drop_graphs();
@@ -51,10 +47,18 @@ __device__ __forceinline__ float euler_step(float x, float vc, float vu, float a
  * 2 llm_proj(h); 5 zero. */
 __global__ void ac_tokens_kernel(float *X6, float *lat, const float *vel, const uint16_t *Wip, const float *ttok,
                                  const float *ltok, int step, float alpha, float dt_prev, const float *noise_all,
-                                 const VbDyn *dyn) {
+                                 const VbDyn *dyn, AcStrides sd) {
     __shared__ float xs[64];
     pdl_launch_dependents();
     pdl_wait();
+    /* utterance blockIdx.y of the batch */
+    const int b = blockIdx.y;
+    X6 += (size_t)b * ROWS1 * D;
+    lat += (size_t)b * sd.lat;
+    vel += (size_t)b * sd.vel;
+    ltok += (size_t)b * D;
+    dyn += b;
+    if (noise_all) noise_all += (size_t)b * sd.noise;
     if (noise_all && dyn->done) return;   /* device-resident run already ended */
     if (threadIdx.x < A) {
         float xv;
@@ -89,8 +93,9 @@ __global__ void ac_tokens_kernel(float *X6, float *lat, const float *vel, const 
 /* Unmasked attention inside each 3-token sequence (tts_bidirectional_attention,
  * voxtral_tts_kernels.c:467-525) on q/k/v given as split-K partials [n_part][6][6144].
  * One warp per (row, head). The result goes out as the three BF16 terms the O projection's
- * GEMM consumes ([3][16][4096]). */
-__global__ void ac_attention_kernel(uint16_t *terms, const float *part, int n_part, float scale) {
+ * GEMM consumes ([3][rows_pad][4096]). */
+__global__ void ac_attention_kernel(uint16_t *terms, const float *part, int n_part, float scale, int ROWS,
+                                    int rows_pad) {
     pdl_launch_dependents();
     pdl_wait();
     const int task = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -132,17 +137,18 @@ __global__ void ac_attention_kernel(uint16_t *terms, const float *part, int n_pa
     uint16_t t0[4], t1[4], t2[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) vb_split3(e[i], t0[i], t1[i], t2[i]);
-    const size_t off = (size_t)row * QD + h * 128 + 4 * lane, term = (size_t)16 * QD;
+    const size_t off = (size_t)row * QD + h * 128 + 4 * lane, term = (size_t)rows_pad * QD;
     *reinterpret_cast<uint2 *>(terms + off) = make_uint2(t0[0] | ((uint32_t)t0[1] << 16), t0[2] | ((uint32_t)t0[3] << 16));
     *reinterpret_cast<uint2 *>(terms + term + off) = make_uint2(t1[0] | ((uint32_t)t1[1] << 16), t1[2] | ((uint32_t)t1[3] << 16));
     *reinterpret_cast<uint2 *>(terms + 2 * term + off) = make_uint2(t2[0] | ((uint32_t)t2[1] << 16), t2[2] | ((uint32_t)t2[3] << 16));
 }
 
 /* Last residual add, final RMSNorm of token 0 of each branch (rows 0 and 3) and the 36-wide
- * velocity head (voxtral_tts_acoustic.c:255-261). grid = (9, 2): branch blockIdx.y, four of
- * the 36 outputs per CTA (every CTA re-derives the normalised row; it is 12 KB). */
+ * velocity head (voxtral_tts_acoustic.c:255-261). grid = (9, 2 * utterances): blockIdx.y =
+ * 2 * utterance + branch, four of the 36 outputs per CTA (every CTA re-derives the normalised
+ * row; it is 12 KB). */
 __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *part, int n_part, const float *gain,
-                                   float eps, const uint16_t *Wout) {
+                                   float eps, const uint16_t *Wout, int ROWS, int vel_stride) {
     __shared__ float xn[VB200_DIM];
     __shared__ float red[32];
     pdl_launch_dependents();
@@ -178,7 +184,8 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
     __syncthreads();
     if (threadIdx.x < 4) {
         const int o = threadIdx.x;
-        vel[blockIdx.y * A + blockIdx.x * 4 + o] = ((wsum[4 * o] + wsum[4 * o + 1]) + wsum[4 * o + 2]) + wsum[4 * o + 3];
+        vel[(size_t)(blockIdx.y >> 1) * vel_stride + (blockIdx.y & 1) * A + blockIdx.x * 4 + o] =
+            ((wsum[4 * o] + wsum[4 * o + 1]) + wsum[4 * o + 2]) + wsum[4 * o + 3];
     }
 }
 
@@ -186,10 +193,16 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
  * In a device-resident run it also logs the frame's codes and advances position and frame
  * counter (the loop of voxtral_tts.c:301-321). */
 __global__ void ac_fsq_kernel(int *codes, float *lat, const float *vel, int steps, int levels, float alpha, float dt,
-                              int *codes_all, VbDyn *dyn, int frame_cap, int advance, int ignore_end) {
+                              int *codes_all, VbDyn *dyn, int frame_cap, int advance, int ignore_end, AcStrides sd) {
     const int i = threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
+    const int b = blockIdx.x;   /* utterance */
+    codes += (size_t)b * sd.codes;
+    lat += (size_t)b * sd.lat;
+    vel += (size_t)b * sd.vel;
+    dyn += b;
+    if (codes_all) codes_all += (size_t)b * sd.codes_all;
     if (advance && dyn->done) return;
     const int sem = codes[0];
     const int frame = advance ? dyn->frame : 0;
@@ -217,10 +230,24 @@ __global__ void ac_fsq_kernel(int *codes, float *lat, const float *vel, int step
 }
 
 /* ---- set-up ---- */
-static int alloc_zero(void **p, size_t bytes) {
+static int alloc_zero(void **p, size_t bytes, std::vector<void *> *owner) {
     if (cudaMalloc(p, bytes) != cudaSuccess) return -1;
-    model().allocs.push_back(*p);
+    owner->push_back(*p);
     return cudaMemset(*p, 0, bytes) == cudaSuccess ? 0 : -1;
+}
+
+int acoustic_buffers_alloc(AcBuffers *b, int B, std::vector<void *> *owner) {
+    const int rows = ROWS1 * B, rp = tc_rows_pad(rows);
+    if (B < 1 || rp == 0) return -1;
+    b->B = B; b->rows = rows; b->rows_pad = rp;
+    if (alloc_zero((void **)&b->bD, tc_acts_bytes(rp, D), owner) || alloc_zero((void **)&b->bQ, tc_acts_bytes(rp, QD), owner) ||
+        alloc_zero((void **)&b->bH, tc_acts_bytes(rp, HID), owner) ||
+        alloc_zero((void **)&b->part, sizeof(float) * kTcMaxSplits * rows * QKV, owner) ||
+        alloc_zero((void **)&b->ssq, sizeof(float) * rows * 16, owner))
+        return -1;
+    if (!b->X6 && alloc_zero((void **)&b->X6, sizeof(float) * rows * D, owner)) return -1;
+    if (tc_acts(&b->aD, b->bD, rp, D) || tc_acts(&b->aQ, b->bQ, rp, QD) || tc_acts(&b->aH, b->bH, rp, HID)) return -1;
+    return 0;
 }
 
 int acoustic_tc_setup() {
@@ -247,19 +274,22 @@ int acoustic_tc_setup() {
             {&t.wqkv[l], L.wqkv, QKV, D, &t.tiled[l][0]}, {&t.wo[l], L.wo, D, QD, &t.tiled[l][1]},
             {&t.w13[l], L.w13, 2 * HID, D, &t.tiled[l][2]}, {&t.w2[l], L.w2, D, HID, &t.tiled[l][3]}};
         for (int j = 0; j < 4; j++) {
-            if (!*jobs[j].dst && alloc_zero((void **)jobs[j].dst, tc_tiled_bytes(jobs[j].N, jobs[j].K))) return -1;
+            if (!*jobs[j].dst && alloc_zero((void **)jobs[j].dst, tc_tiled_bytes(jobs[j].N, jobs[j].K), &m.allocs)) return -1;
             if (tc_weight_tiled(jobs[j].w, jobs[j].src, jobs[j].N, jobs[j].K, *jobs[j].dst, m.st)) return -1;
         }
         if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
     }
-    if (!t.bD) {
-        if (alloc_zero((void **)&t.bD, tc_acts_bytes(16, D)) || alloc_zero((void **)&t.bQ, tc_acts_bytes(16, QD)) ||
-            alloc_zero((void **)&t.bH, tc_acts_bytes(16, HID)) ||
-            alloc_zero((void **)&t.part, sizeof(float) * kTcMaxSplits * ROWS * QKV) ||
-            alloc_zero((void **)&t.ssq, sizeof(float) * 16 * 16))
-            return -1;
+    AcBuffers &o = t.one;
+    if (!o.bD) {
+        o.X6 = m.X6;
+        if (acoustic_buffers_alloc(&o, 1, &m.allocs)) return -1;
     }
-    if (tc_acts(&t.aD, t.bD, 16, D) || tc_acts(&t.aQ, t.bQ, 16, QD) || tc_acts(&t.aH, t.bH, 16, HID)) return -1;
+    o.lat = &m.d_in->lat[0][0];
+    o.vel = &m.d_out->vel[0][0];
+    o.ltok = m.ltok;
+    o.codes = m.d_out->codes;
+    o.dyn = &m.d_in->dyn;
+    o.status = &m.d_out->status;
     t.s_qkv = tc_pick_splits(QKV, D, m.sm_count);
     t.s_wo = tc_pick_splits(D, QD, m.sm_count);
     t.s_w2 = tc_pick_splits(D, HID, m.sm_count);
@@ -270,52 +300,57 @@ int acoustic_tc_setup() {
 bool acoustic_tc_ready() { return g_ac.ready; }
 
 /* Enqueues the 7 Euler steps + FSQ on the library's stream. The semantic head, llm token
- * and argmax have already run (engine program); `hidden`-dependent inputs are in m.ltok. */
-static int enqueue_direct(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end) {
+ * and argmax have already run; the llm token rows are in b.ltok. */
+int acoustic_tc_enqueue_on(const AcBuffers &b, const float *noise_all, int *codes_all, int frame_cap, bool advance,
+                           bool ignore_end) {
     Model &m = model();
     AcTc &t = g_ac;
+    if (!t.ready) return -1;
     cudaStream_t st = m.st;
     const float scale = 1.0f / sqrtf((float)VB200_HEAD_DIM);
     const int steps = VB200_FLOW_STEPS - 1;
-    float *lat = &m.d_in->lat[0][0];
-    float *vel = &m.d_out->vel[0][0];
-    int *status = &m.d_out->status;
+    const int ROWS = b.rows;
     const size_t psD = (size_t)ROWS * D;
     const int chunksD = tc_prepare_chunks(D);
     TcGemm g;
-    g.M = ROWS; g.status = status;
+    g.M = ROWS; g.status = b.status;
     for (int s = 0; s < steps; s++) {
-        launch_pdl(ac_tokens_kernel, dim3((D + 127) / 128), dim3(128), 0, st, m.X6, lat, (const float *)vel,
-                   (const uint16_t *)m.ac_input_proj, (const float *)m.ttok, (const float *)m.ltok, s,
-                   VB200_CFG_ALPHA, s > 0 ? m.dt[s - 1] : 0.0f, noise_all, (const VbDyn *)&m.d_in->dyn);
+        launch_pdl(ac_tokens_kernel, dim3((D + 127) / 128, b.B), dim3(128), 0, st, b.X6, b.lat, (const float *)b.vel,
+                   (const uint16_t *)m.ac_input_proj, (const float *)m.ttok, (const float *)b.ltok, s,
+                   VB200_CFG_ALPHA, s > 0 ? m.dt[s - 1] : 0.0f, noise_all, (const VbDyn *)b.dyn, b.sd);
         for (int l = 0; l < VB200_AC_LAYERS; l++) {
             const LayerDev &L = m.ac[l];
             /* attention half: (reduce + residual +) gain -> QKV -> attention -> O */
-            if (l == 0) tc_prepare(t.aD, m.X6, D, ROWS, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
-            else tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_w2, psD, m.X6, m.X6, L.attn_norm, t.ssq, st);
-            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
-            g.splits = t.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
-            if (tc_gemm(t.wqkv[l], t.aD, g, st)) return -1;
-            launch_pdl(ac_attention_kernel, dim3((ROWS * VB200_HEADS * 32 + 255) / 256), dim3(256), 0, st, t.bQ,
-                       (const float *)t.part, t.s_qkv, scale);
+            if (l == 0) tc_prepare(b.aD, b.X6, D, ROWS, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, b.ssq, st);
+            else tc_prepare(b.aD, nullptr, D, ROWS, b.part, t.s_w2, psD, b.X6, b.X6, L.attn_norm, b.ssq, st);
+            g.epi = TC_EPI_PARTIAL; g.out = b.part; g.out_terms = nullptr;
+            g.splits = t.s_qkv; g.ld_out = QKV; g.ssq = b.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+            if (tc_gemm(t.wqkv[l], b.aD, g, st)) return -1;
+            launch_pdl(ac_attention_kernel, dim3((ROWS * VB200_HEADS * 32 + 255) / 256), dim3(256), 0, st, b.bQ,
+                       (const float *)b.part, t.s_qkv, scale, ROWS, b.rows_pad);
             g.splits = t.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
-            if (tc_gemm(t.wo[l], t.aQ, g, st)) return -1;
+            if (tc_gemm(t.wo[l], b.aQ, g, st)) return -1;
             /* FFN half: reduce + residual + gain -> gate/up with SwiGLU (terms out) -> down */
-            tc_prepare(t.aD, nullptr, D, ROWS, t.part, t.s_wo, psD, m.X6, m.X6, L.ffn_norm, t.ssq, st);
-            g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
-            g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
-            if (tc_gemm(t.w13[l], t.aD, g, st)) return -1;
-            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+            tc_prepare(b.aD, nullptr, D, ROWS, b.part, t.s_wo, psD, b.X6, b.X6, L.ffn_norm, b.ssq, st);
+            g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = b.bH; g.out_rows_pad = b.rows_pad;
+            g.splits = 1; g.ld_out = HID; g.ssq = b.ssq; g.ssq_chunks = chunksD;
+            if (tc_gemm(t.w13[l], b.aD, g, st)) return -1;
+            g.epi = TC_EPI_PARTIAL; g.out = b.part; g.out_terms = nullptr;
             g.splits = t.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
-            if (tc_gemm(t.w2[l], t.aH, g, st)) return -1;
+            if (tc_gemm(t.w2[l], b.aH, g, st)) return -1;
         }
-        launch_pdl(ac_velocity_kernel, dim3(9, 2), dim3(512), 0, st, vel, (const float *)m.X6, (const float *)t.part,
-                   t.s_w2, (const float *)m.ac_norm, VB200_NORM_EPS, (const uint16_t *)m.ac_out);
+        launch_pdl(ac_velocity_kernel, dim3(9, 2 * b.B), dim3(512), 0, st, b.vel, (const float *)b.X6,
+                   (const float *)b.part, t.s_w2, (const float *)m.ac_norm, VB200_NORM_EPS, (const uint16_t *)m.ac_out,
+                   ROWS, b.sd.vel);
     }
-    launch_pdl(ac_fsq_kernel, dim3(1), dim3(64), 0, st, m.d_out->codes, lat, (const float *)vel, steps,
-               VB200_FSQ_LEVELS, VB200_CFG_ALPHA, m.dt[steps - 1], codes_all, &m.d_in->dyn, frame_cap,
-               advance ? 1 : 0, ignore_end ? 1 : 0);
+    launch_pdl(ac_fsq_kernel, dim3(b.B), dim3(64), 0, st, b.codes, b.lat, (const float *)b.vel, steps,
+               VB200_FSQ_LEVELS, VB200_CFG_ALPHA, m.dt[steps - 1], codes_all, b.dyn, frame_cap,
+               advance ? 1 : 0, ignore_end ? 1 : 0, b.sd);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+static int enqueue_direct(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end) {
+    return acoustic_tc_enqueue_on(g_ac.one, noise_all, codes_all, frame_cap, advance, ignore_end);
 }
 
 /* The ~200 launches of a frame are captured once per argument set as a CUDA graph and

@@ -1,0 +1,622 @@
+/*
+ * vb_batch.cu - several independent utterances decoded in lock step on one GPU.
+ *
+ * The reference synthesises one utterance at a time (voxtral_tts.c:301-321: decoder step,
+ * acoustic frame, re-embedding, per frame). Frames of different utterances do not depend on
+ * one another, so B of them share every weight read: the decoder step becomes a B-row GEMM
+ * and the acoustic passes a 6B-row GEMM on the tcgen05 kernel (vb_tc.cu); weights cross HBM
+ * once per frame for all B utterances. Each utterance has its own KV cache slab, position,
+ * noise rows and END state.
+ *
+ * One frame of the batch is a fixed sequence of launches (captured as a CUDA graph):
+ *   embed (from the previous frame's codes)
+ *   26 x [prepare, QKV GEMM, decode attention, O GEMM, prepare, gate/up GEMM, down GEMM]
+ *   final norm, semantic-head GEMM + argmax, llm_proj GEMM
+ *   7 Euler steps + FSQ (vb_acoustic_tc.cu), which also advances every utterance.
+ */
+#include "vb_acoustic_tc.cuh"
+#include "vb_common.cuh"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace vb {
+
+static const int D = VB200_DIM, QD = VB200_Q_DIM, KVD = VB200_KV_DIM, HID = VB200_HIDDEN;
+static const int QKV = QD + 2 * KVD;
+static const int A = VB200_ACOUSTIC_DIM;
+static const int NSEM = VB200_SEM_PADDED;
+constexpr int kHD = VB200_HEAD_DIM;        /* 128 */
+constexpr int kGroup = VB200_HEADS / VB200_KV_HEADS;   /* 4 query heads per KV head */
+constexpr int kBtMaxUtt = 8;
+constexpr int kBtKeySplits = 16;           /* CTAs sharing one (utterance, KV head) */
+constexpr int kBtSubsets = 4;              /* warp subsets of a CTA's key range */
+constexpr int kBtAttnThreads = 512;
+constexpr int kCodeStride = 40;            /* ints per utterance in the codes block */
+
+struct Batch {
+    bool open = false, begun = false;
+    int B = 0, kv_max = 0, cap = 0, launched = 0;
+    std::vector<void *> allocs;
+    /* decoder weights on the tensor-core path (tile-contiguous copies) */
+    bool weights_ready = false;
+    TcWeight wqkv[VB200_DEC_LAYERS], wo[VB200_DEC_LAYERS], w13[VB200_DEC_LAYERS], w2[VB200_DEC_LAYERS];
+    TcWeight wsem, wllm;
+    std::vector<void *> weight_allocs;
+    int s_qkv = 1, s_wo = 1, s_w2 = 1, s_sem = 1, s_llm = 1;
+    /* per-utterance state */
+    float *kv_k = nullptr, *kv_v = nullptr;     /* [B][layers][kv_max][1024] */
+    size_t slab = 0;                            /* floats per utterance */
+    VbDyn *dyn = nullptr;                       /* [B] */
+    float *X = nullptr, *hidden = nullptr;      /* [B][3072] */
+    float *lat = nullptr, *vel = nullptr, *ltok = nullptr;
+    int *codes = nullptr, *status = nullptr;
+    float *noise_all = nullptr;                 /* [B][cap][36] */
+    int *codes_all = nullptr;                   /* [B][cap][37] */
+    /* decoder-step activations */
+    TcActs aD, aQ, aH;
+    uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
+    float *part = nullptr, *ssq = nullptr, *logit_part = nullptr;
+    float *attn_scratch = nullptr;
+    unsigned *tickets = nullptr;
+    AcBuffers ac;
+    cudaGraphExec_t exec = nullptr;
+    int direct_calls = 0;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+};
+static Batch g_bt;
+
+/* ------------------------------------------------------------------ kernels */
+
+/* Next decoder input of every utterance: the sum of the 37 code rows of the audio table in
+ * codebook order (voxtral_tts_voice.c:292-315, offsets :275-283). Frame 0 keeps the row the
+ * host supplied. grid = (dim / 256, B). */
+__global__ void bt_embed_kernel(float *X, const uint16_t *table, const int *codes, const VbDyn *dyn, int n_codes,
+                                int rows0, int rows_other) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    if (dyn[b].done || dyn[b].frame == 0) return;
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= D) return;
+    const int *cb = codes + (size_t)b * kCodeStride;
+    float acc = 0.0f;
+    int base = 0;
+    for (int c = 0; c < n_codes; c++) {
+        const int row = base + __ldcg(cb + c);
+        acc += __uint_as_float((uint32_t)__ldg(table + (size_t)row * D + n) << 16);
+        base += (c == 0) ? rows0 : rows_other;
+    }
+    X[(size_t)b * D + n] = acc;
+}
+
+/* Decode attention for one new token per utterance: split-K reduction of the QKV GEMM's
+ * partials, RoPE on q and k, cache append, GQA attention over the utterance's own cache
+ * (voxtral_tts_llm.c:221-238; tts_apply_rope / tts_causal_attention,
+ * voxtral_tts_kernels.c:403-465, 602-634). grid = (key splits, KV heads, B); a CTA serves the
+ * four query heads of its KV head on one slice of the keys; the last CTA of a (utterance,
+ * KV head) to finish merges the slices in fixed order and writes the result as the three
+ * BF16 terms the O projection's GEMM consumes. */
+__global__ void __launch_bounds__(kBtAttnThreads)
+bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, size_t part_stride, float *kv_k,
+               float *kv_v, size_t slab, int layer, const VbDyn *dyn, float scale, float theta, float *scratch,
+               unsigned *tickets, int *status) {
+    __shared__ float cs[kHD];
+    __shared__ __align__(16) float qraw[kGroup * kHD];
+    __shared__ float kraw[kHD], vraw[kHD];
+    __shared__ __align__(16) float qs[kGroup][kHD];
+    __shared__ __align__(16) float attn_o[kBtSubsets][kGroup][kHD];
+    __shared__ float attn_ml[kBtSubsets][kGroup][2];
+    __shared__ int last_flag;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int max_s = gridDim.x, G = gridDim.y;
+    if (dyn[b].done) return;
+    const int pos = dyn[b].pos, kv_max = dyn[b].kv_max;
+    if (pos < 0 || pos >= kv_max) {
+        if (tid == 0) atomicCAS(status, 0, (int)VB_ERR_POS_RANGE);
+        return;
+    }
+    const int nk = pos + 1;
+    int S = (nk + 31) / 32;
+    if (S > max_s) S = max_s;
+    if (S < 1) S = 1;
+    if (sp >= S) return;
+    const int j0 = (int)((long long)nk * sp / S), j1 = (int)((long long)nk * (sp + 1) / S);
+    float *Kc = kv_k + (size_t)b * slab + (size_t)layer * kv_max * KVD;
+    float *Vc = kv_v + (size_t)b * slab + (size_t)layer * kv_max * KVD;
+    const float *row = part + (size_t)b * QKV;
+    const bool writer = sp == S - 1;   /* its key range ends with the new token */
+
+    {
+        float v = 0.0f;
+        for (int p = 0; p < n_part; p++) v += __ldcg(row + p * part_stride + (size_t)g * kGroup * kHD + tid);
+        qraw[tid] = v;
+        if (writer && tid < kHD) {
+            float kk = 0.0f, vv = 0.0f;
+            for (int p = 0; p < n_part; p++) {
+                kk += __ldcg(row + p * part_stride + QD + g * kHD + tid);
+                vv += __ldcg(row + p * part_stride + QD + KVD + g * kHD + tid);
+            }
+            kraw[tid] = kk;
+            vraw[tid] = vv;
+        }
+    }
+    if (tid < kHD / 2) {
+        const float freq = 1.0f / powf(theta, (float)(2 * tid) / (float)kHD);
+        const float ang = (float)pos * freq;
+        cs[2 * tid] = cosf(ang);
+        cs[2 * tid + 1] = sinf(ang);
+    }
+    __syncthreads();
+    const int half = kHD / 2;
+    if (tid < kGroup * half) {
+        const int hh = tid / half, d = tid % half;
+        const float a = qraw[hh * kHD + 2 * d], bb = qraw[hh * kHD + 2 * d + 1];
+        const float cv = cs[2 * d], sv = cs[2 * d + 1];
+        qs[hh][2 * d] = a * cv - bb * sv;
+        qs[hh][2 * d + 1] = a * sv + bb * cv;
+    } else if (writer && tid < kGroup * half + half) {
+        const int d = tid - kGroup * half;
+        const float a = kraw[2 * d], bb = kraw[2 * d + 1];
+        const float cv = cs[2 * d], sv = cs[2 * d + 1];
+        float *dst = Kc + (size_t)pos * KVD + g * kHD;
+        dst[2 * d] = a * cv - bb * sv;
+        dst[2 * d + 1] = a * sv + bb * cv;
+        __threadfence();
+    } else if (writer && tid >= 384 && tid < 384 + kHD) {
+        const int d = tid - 384;
+        Vc[(size_t)pos * KVD + g * kHD + d] = vraw[d];
+        __threadfence();
+    }
+    __syncthreads();
+
+    const int hh = warp & 3, ss = warp >> 2;
+    const float4 q4 = *reinterpret_cast<const float4 *>(&qs[hh][4 * lane]);
+    float mx = -1e30f, den = 0.0f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = j0 + ss; j < j1; j += kBtSubsets) {
+        const float4 kv = vb_ldcg4(Kc + (size_t)j * KVD + g * kHD + 4 * lane);
+        const float4 vv = vb_ldcg4(Vc + (size_t)j * KVD + g * kHD + 4 * lane);
+        float d = q4.x * kv.x + q4.y * kv.y + q4.z * kv.z + q4.w * kv.w;
+        d = vb_warp_sum(d) * scale;
+        if (d > mx) {
+            const float corr = expf(mx - d);
+            den = den * corr + 1.0f;
+            o.x = o.x * corr + vv.x; o.y = o.y * corr + vv.y;
+            o.z = o.z * corr + vv.z; o.w = o.w * corr + vv.w;
+            mx = d;
+        } else {
+            const float w = expf(d - mx);
+            den += w;
+            o.x += w * vv.x; o.y += w * vv.y; o.z += w * vv.z; o.w += w * vv.w;
+        }
+    }
+    *reinterpret_cast<float4 *>(&attn_o[ss][hh][4 * lane]) = o;
+    if (lane == 0) { attn_ml[ss][hh][0] = mx; attn_ml[ss][hh][1] = den; }
+    __syncthreads();
+
+    /* merge the four key subsets: thread = (head, dim) */
+    const int th = tid / kHD, td = tid % kHD;
+    float M0 = -1e30f;
+#pragma unroll
+    for (int u = 0; u < kBtSubsets; u++) M0 = fmaxf(M0, attn_ml[u][th][0]);
+    float L = 0.0f, O = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kBtSubsets; u++) {
+        const float w = (attn_ml[u][th][1] > 0.0f) ? expf(attn_ml[u][th][0] - M0) : 0.0f;
+        L += attn_ml[u][th][1] * w;
+        O += attn_o[u][th][td] * w;
+    }
+    float result;
+    if (S == 1) {
+        result = (L > 0.0f) ? O * (1.0f / L) : 0.0f;
+    } else {
+        /* several CTAs share this KV head: publish the slice, the last arrival merges */
+        const int stride = kHD + 2;
+        float *po = scratch + (size_t)(b * G + g) * max_s * kGroup * stride;   /* [max_s][group][kHD + 2] */
+        float *mine = po + ((size_t)sp * kGroup + th) * stride;
+        mine[td] = O;
+        if (td == 0) { mine[kHD] = M0; mine[kHD + 1] = L; }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned t = atomicAdd(&tickets[b * G + g], 1u);
+            last_flag = (t == (unsigned)(S - 1));
+            if (last_flag) tickets[b * G + g] = 0u;
+        }
+        __syncthreads();
+        if (!last_flag) return;
+        __threadfence();
+        float Mg = -1e30f;
+        for (int u = 0; u < S; u++) Mg = fmaxf(Mg, __ldcg(po + ((size_t)u * kGroup + th) * stride + kHD));
+        float Lg = 0.0f, Og = 0.0f;
+        for (int u = 0; u < S; u++) {
+            const float *pu = po + ((size_t)u * kGroup + th) * stride;
+            const float lu = __ldcg(pu + kHD + 1);
+            const float w = (lu > 0.0f) ? expf(__ldcg(pu + kHD) - Mg) : 0.0f;
+            Lg += lu * w;
+            Og += __ldcg(pu + td) * w;
+        }
+        result = (Lg > 0.0f) ? Og * (1.0f / Lg) : 0.0f;
+    }
+    uint16_t t0, t1, t2;
+    vb_split3(result, t0, t1, t2);
+    const size_t off = (size_t)b * QD + (size_t)(g * kGroup + th) * kHD + td, term = (size_t)rows_pad * QD;
+    terms[off] = t0;
+    terms[term + off] = t1;
+    terms[2 * term + off] = t2;
+}
+
+/* End of the decoder step: last residual add (split-K partials of the last down projection),
+ * final RMSNorm (voxtral_tts_llm.c:267), hidden rows out as fp32 and as BF16 terms for the two
+ * head GEMMs. grid = B, 1024 threads. */
+__global__ void __launch_bounds__(1024)
+bt_final_kernel(float *hidden, uint16_t *terms, int rows_pad, const float *X, const float *part, int n_part,
+                size_t part_stride, const float *gain, float eps) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float v[3];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const int c = tid + i * 1024;
+        float s = 0.0f;
+        for (int p = 0; p < n_part; p++) s += __ldcg(part + p * part_stride + (size_t)b * D + c);
+        v[i] = __ldcg(X + (size_t)b * D + c) + s;
+        ss += v[i] * v[i];
+    }
+    ss = vb_warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < 32; w++) t += red[w];
+    const float inv = 1.0f / sqrtf(t / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const int c = tid + i * 1024;
+        const float h = v[i] * inv * __ldg(gain + c);
+        hidden[(size_t)b * D + c] = h;
+        uint16_t t0, t1, t2;
+        vb_split3(h, t0, t1, t2);
+        const size_t off = (size_t)b * D + c, term = (size_t)rows_pad * D;
+        terms[off] = t0;
+        terms[term + off] = t1;
+        terms[2 * term + off] = t2;
+    }
+}
+
+/* Masked greedy argmax over every utterance's semantic logits (voxtral_tts_acoustic.c:290-309):
+ * index 0 and indices >= valid_end are excluded, the first strict maximum wins. The logits
+ * arrive as split-K partials. grid = B, 1024 threads. */
+__global__ void __launch_bounds__(1024)
+bt_argmax_kernel(int *codes, const float *part, int n_part, size_t part_stride, const float *bias, int N,
+                 int valid_end) {
+    __shared__ float rv[32];
+    __shared__ int ri[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float best = -1e30f;
+    int bi = 0;
+    for (int i = tid; i < N; i += 1024) {
+        float v = -1e30f;
+        if (i != 0 && i < valid_end) {
+            v = 0.0f;
+            for (int p = 0; p < n_part; p++) v += __ldcg(part + p * part_stride + (size_t)b * N + i);
+            if (bias) v += __ldg(bias + i);
+        }
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((tid & 31) == 0) { rv[tid >> 5] = best; ri[tid >> 5] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 0; w < 32; w++)
+            if (rv[w] > best || (rv[w] == best && ri[w] < bi)) { best = rv[w]; bi = ri[w]; }
+        codes[(size_t)b * kCodeStride] = bi;
+    }
+}
+
+/* ------------------------------------------------------------------ host */
+static int bt_alloc(void **p, size_t bytes, std::vector<void *> *owner) {
+    if (cudaMalloc(p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    owner->push_back(*p);
+    return cudaMemset(*p, 0, bytes) == cudaSuccess ? 0 : -1;
+}
+
+static void bt_free(std::vector<void *> *owner) {
+    for (void *p : *owner) cudaFree(p);
+    owner->clear();
+}
+
+/* Tile-contiguous copies of the decoder's matrices and of the two heads, made once per
+ * weight upload. */
+static int bt_weights() {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (t.weights_ready) return 0;
+    if (tc_init()) return -1;
+    bt_free(&t.weight_allocs);
+    auto tiled = [&](TcWeight *w, const uint16_t *src, int N, int K) -> int {
+        void *dst = nullptr;
+        if (bt_alloc(&dst, tc_tiled_bytes(N, K), &t.weight_allocs)) return -1;
+        return tc_weight_tiled(w, src, N, K, (uint16_t *)dst, m.st);
+    };
+    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+        const LayerDev &L = m.dec[l];
+        if (tiled(&t.wqkv[l], L.wqkv, QKV, D) || tiled(&t.wo[l], L.wo, D, QD) || tiled(&t.w13[l], L.w13, 2 * HID, D) ||
+            tiled(&t.w2[l], L.w2, D, HID))
+            return -1;
+    }
+    if (tiled(&t.wsem, m.ac_sem_out, NSEM, D) || tiled(&t.wllm, m.ac_llm_proj, D, D)) return -1;
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    t.s_qkv = tc_pick_splits(QKV, D, m.sm_count);
+    t.s_wo = tc_pick_splits(D, QD, m.sm_count);
+    t.s_w2 = tc_pick_splits(D, HID, m.sm_count);
+    t.s_sem = tc_pick_splits(NSEM, D, m.sm_count);
+    t.s_llm = tc_pick_splits(D, D, m.sm_count);
+    t.weights_ready = true;
+    return 0;
+}
+
+/* Called when weights are uploaded again: the copies and any captured graph are stale. */
+void batch_invalidate() {
+    Batch &t = g_bt;
+    if (t.exec) { cudaGraphExecDestroy(t.exec); t.exec = nullptr; }
+    t.direct_calls = 0;
+    t.weights_ready = false;
+}
+
+void batch_close() {
+    Batch &t = g_bt;
+    if (t.exec) { cudaGraphExecDestroy(t.exec); t.exec = nullptr; }
+    if (model().st) cudaStreamSynchronize(model().st);
+    bt_free(&t.allocs);
+    if (t.e0) { cudaEventDestroy(t.e0); t.e0 = nullptr; }
+    if (t.e1) { cudaEventDestroy(t.e1); t.e1 = nullptr; }
+    t.open = t.begun = false;
+    t.B = 0;
+    t.noise_all = nullptr; t.codes_all = nullptr;
+    t.ac = AcBuffers();
+    t.direct_calls = 0;
+}
+
+void batch_free_all() {
+    batch_close();
+    bt_free(&g_bt.weight_allocs);
+    g_bt.weights_ready = false;
+}
+
+int batch_open(int n_utt, int kv_max, int max_frames) {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (!m.inited || !m.llm_ready || !m.ac_ready || !m.embed_ready || !acoustic_tc_ready()) return -1;
+    if (n_utt < 1 || n_utt > kBtMaxUtt || kv_max < 1 || max_frames < 1) return -1;
+    batch_close();
+    if (bt_weights()) return -1;
+    t.B = n_utt; t.kv_max = kv_max; t.cap = max_frames;
+    t.slab = (size_t)VB200_DEC_LAYERS * kv_max * KVD;
+    const int B = n_utt;
+    int rc = 0;
+    rc |= bt_alloc((void **)&t.kv_k, sizeof(float) * t.slab * B, &t.allocs);
+    rc |= bt_alloc((void **)&t.kv_v, sizeof(float) * t.slab * B, &t.allocs);
+    rc |= bt_alloc((void **)&t.dyn, sizeof(VbDyn) * B, &t.allocs);
+    rc |= bt_alloc((void **)&t.X, sizeof(float) * B * D, &t.allocs);
+    rc |= bt_alloc((void **)&t.hidden, sizeof(float) * B * D, &t.allocs);
+    rc |= bt_alloc((void **)&t.lat, sizeof(float) * B * VB200_FLOW_STEPS * A, &t.allocs);
+    rc |= bt_alloc((void **)&t.vel, sizeof(float) * B * 2 * A, &t.allocs);
+    rc |= bt_alloc((void **)&t.ltok, sizeof(float) * B * D, &t.allocs);
+    rc |= bt_alloc((void **)&t.codes, sizeof(int) * B * kCodeStride, &t.allocs);
+    rc |= bt_alloc((void **)&t.status, sizeof(int) * 4, &t.allocs);
+    rc |= bt_alloc((void **)&t.noise_all, sizeof(float) * (size_t)B * max_frames * A, &t.allocs);
+    rc |= bt_alloc((void **)&t.codes_all, sizeof(int) * (size_t)B * max_frames * VB200_CODES, &t.allocs);
+    rc |= bt_alloc((void **)&t.bD, tc_acts_bytes(16, D), &t.allocs);
+    rc |= bt_alloc((void **)&t.bQ, tc_acts_bytes(16, QD), &t.allocs);
+    rc |= bt_alloc((void **)&t.bH, tc_acts_bytes(16, HID), &t.allocs);
+    rc |= bt_alloc((void **)&t.part, sizeof(float) * kTcMaxSplits * B * QKV, &t.allocs);
+    rc |= bt_alloc((void **)&t.ssq, sizeof(float) * 16 * 16, &t.allocs);
+    rc |= bt_alloc((void **)&t.logit_part, sizeof(float) * kTcMaxSplits * B * NSEM, &t.allocs);
+    rc |= bt_alloc((void **)&t.attn_scratch,
+                   sizeof(float) * (size_t)B * VB200_KV_HEADS * kBtKeySplits * kGroup * (kHD + 2), &t.allocs);
+    rc |= bt_alloc((void **)&t.tickets, sizeof(unsigned) * B * VB200_KV_HEADS, &t.allocs);
+    if (rc) { batch_close(); return -1; }
+    if (tc_acts(&t.aD, t.bD, 16, D) || tc_acts(&t.aQ, t.bQ, 16, QD) || tc_acts(&t.aH, t.bH, 16, HID)) {
+        batch_close();
+        return -1;
+    }
+    t.ac = AcBuffers();
+    if (acoustic_buffers_alloc(&t.ac, B, &t.allocs)) { batch_close(); return -1; }
+    t.ac.lat = t.lat; t.ac.vel = t.vel; t.ac.ltok = t.ltok; t.ac.codes = t.codes; t.ac.dyn = t.dyn;
+    t.ac.status = t.status;
+    t.ac.sd.lat = VB200_FLOW_STEPS * A; t.ac.sd.vel = 2 * A; t.ac.sd.codes = kCodeStride;
+    t.ac.sd.noise = (size_t)max_frames * A; t.ac.sd.codes_all = (size_t)max_frames * VB200_CODES;
+    if (cudaEventCreate(&t.e0) != cudaSuccess || cudaEventCreate(&t.e1) != cudaSuccess) { batch_close(); return -1; }
+    t.open = true;
+    return 0;
+}
+
+/* Prompt rows of one utterance into its own cache slab (the single-utterance prefill,
+ * pointed at the slab for the duration of the call). */
+int batch_prefill(int utt, const float *embeds, int n_rows) {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (!t.open || utt < 0 || utt >= t.B || n_rows < 1 || n_rows > t.kv_max) return -1;
+    float *k0 = m.kv_k, *v0 = m.kv_v;
+    const int max0 = m.kv_max;
+    m.kv_k = t.kv_k + (size_t)utt * t.slab;
+    m.kv_v = t.kv_v + (size_t)utt * t.slab;
+    m.kv_max = t.kv_max;
+    const int rc = prefill(embeds, n_rows, 0);
+    m.kv_k = k0; m.kv_v = v0; m.kv_max = max0;
+    return rc;
+}
+
+int batch_begin(const float *first_embeds, const int *start_pos, const float *noise) {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (!t.open || !first_embeds || !start_pos || !noise) return -1;
+    std::vector<VbDyn> d(t.B);
+    for (int b = 0; b < t.B; b++) {
+        if (start_pos[b] < 0 || start_pos[b] >= t.kv_max) return -1;
+        d[b].pos = start_pos[b]; d[b].kv_max = t.kv_max; d[b].frame = 0; d[b].done = 0;
+    }
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    if (cudaMemcpy(t.dyn, d.data(), sizeof(VbDyn) * t.B, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(t.X, first_embeds, sizeof(float) * t.B * D, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(t.noise_all, noise, sizeof(float) * (size_t)t.B * t.cap * A, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemset(t.codes_all, 0, sizeof(int) * (size_t)t.B * t.cap * VB200_CODES) != cudaSuccess ||
+        cudaMemset(t.status, 0, sizeof(int) * 4) != cudaSuccess ||
+        cudaMemset(t.tickets, 0, sizeof(unsigned) * t.B * VB200_KV_HEADS) != cudaSuccess)
+        return -1;
+    t.launched = 0;
+    t.begun = true;
+    return 0;
+}
+
+/* One frame of every utterance, enqueued launch by launch. */
+static int bt_enqueue_frame() {
+    Model &m = model();
+    Batch &t = g_bt;
+    cudaStream_t st = m.st;
+    const int B = t.B;
+    const float scale = 1.0f / sqrtf((float)kHD);
+    const int chunksD = tc_prepare_chunks(D);
+    const size_t psD = (size_t)B * D, psQ = (size_t)B * QKV;
+    launch_pdl(bt_embed_kernel, dim3((D + 255) / 256, B), dim3(256), 0, st, t.X, (const uint16_t *)m.audio_table,
+               (const int *)t.codes, (const VbDyn *)t.dyn, VB200_CODES, 8194, 23);
+    TcGemm g;
+    g.M = B; g.status = t.status;
+    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+        const LayerDev &L = m.dec[l];
+        if (l == 0) tc_prepare(t.aD, t.X, D, B, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
+        else tc_prepare(t.aD, nullptr, D, B, t.part, t.s_w2, psD, t.X, t.X, L.attn_norm, t.ssq, st);
+        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+        g.splits = t.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+        if (tc_gemm(t.wqkv[l], t.aD, g, st)) return -1;
+        launch_pdl(bt_attn_kernel, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ, 16,
+                   (const float *)t.part, t.s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn, scale,
+                   VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status);
+        g.splits = t.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+        if (tc_gemm(t.wo[l], t.aQ, g, st)) return -1;
+        tc_prepare(t.aD, nullptr, D, B, t.part, t.s_wo, psD, t.X, t.X, L.ffn_norm, t.ssq, st);
+        g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
+        g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
+        if (tc_gemm(t.w13[l], t.aD, g, st)) return -1;
+        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+        g.splits = t.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+        if (tc_gemm(t.w2[l], t.aH, g, st)) return -1;
+    }
+    launch_pdl(bt_final_kernel, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
+               (const float *)t.part, t.s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS);
+    /* semantic head + argmax (voxtral_tts_acoustic.c:283-309), llm token (:204) */
+    g.epi = TC_EPI_PARTIAL; g.out = t.logit_part; g.splits = t.s_sem; g.ld_out = NSEM; g.ssq = nullptr; g.ssq_chunks = 0;
+    if (tc_gemm(t.wsem, t.aD, g, st)) return -1;
+    launch_pdl(bt_argmax_kernel, dim3(B), dim3(1024), 0, st, t.codes, (const float *)t.logit_part, t.s_sem,
+               (size_t)B * NSEM, (const float *)m.ac_sem_bias, NSEM, VB200_SEM_VALID_END);
+    g.out = t.part; g.splits = t.s_llm; g.ld_out = D;
+    if (tc_gemm(t.wllm, t.aD, g, st)) return -1;
+    tc_reduce(t.ltok, t.part, t.s_llm, psD, psD, nullptr, D, st);
+    if (acoustic_tc_enqueue_on(t.ac, t.noise_all, t.codes_all, t.cap, true, m.ignore_end)) return -1;
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+/* Queues n more frames; returns without waiting. The first frame runs launch by launch
+ * (kernel attributes are set on first use, which must not happen inside a capture), the
+ * second is captured as a CUDA graph and every later frame replays it. */
+int batch_run(int n) {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (!t.begun || n < 0) return -1;
+    const bool no_graph = getenv("VB200_NO_GRAPH") != nullptr;
+    cudaEventRecord(t.e0, m.st);
+    for (int i = 0; i < n && t.launched < t.cap; i++, t.launched++) {
+        if (t.exec) {
+            if (cudaGraphLaunch(t.exec, m.st) != cudaSuccess) return -1;
+            continue;
+        }
+        if (no_graph || t.direct_calls++ == 0) {
+            if (bt_enqueue_frame()) return -1;
+            continue;
+        }
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(m.st, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+            cudaGetLastError();
+            if (bt_enqueue_frame()) return -1;
+            continue;
+        }
+        const int rc = bt_enqueue_frame();
+        const cudaError_t ee = cudaStreamEndCapture(m.st, &graph);
+        if (rc || ee != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            return -1;
+        }
+        const cudaError_t ie = cudaGraphInstantiate(&t.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) {
+            t.exec = nullptr;
+            cudaGetLastError();
+            return -1;
+        }
+        if (cudaGraphLaunch(t.exec, m.st) != cudaSuccess) return -1;
+    }
+    cudaEventRecord(t.e1, m.st);
+    return 0;
+}
+
+/* Waits for the queued frames. codes_out [B][max_frames][37] (rows past frames_done[b] are
+ * zero), frames_done[b], hit_end[b] (1 when the utterance produced END; that frame is counted),
+ * device_ms = device time of the last batch_run. */
+int batch_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms) {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (!t.begun) return -1;
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    std::vector<VbDyn> d(t.B);
+    int status = 0;
+    if (cudaMemcpy(d.data(), t.dyn, sizeof(VbDyn) * t.B, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(&status, t.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -1;
+    m.last_status = status;
+    if (codes_out &&
+        cudaMemcpy(codes_out, t.codes_all, sizeof(int) * (size_t)t.B * t.cap * VB200_CODES, cudaMemcpyDeviceToHost) !=
+            cudaSuccess)
+        return -1;
+    for (int b = 0; b < t.B; b++) {
+        if (frames_done) frames_done[b] = d[b].frame;
+        if (hit_end) hit_end[b] = d[b].done == 2 ? 1 : 0;
+    }
+    if (device_ms) {
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, t.e0, t.e1);
+        *device_ms = ms;
+    }
+    return status ? -2 : 0;
+}
+
+/* The decoder's hidden rows of the last frame decoded [B][3072]. */
+int batch_hidden(float *out) {
+    Model &m = model();
+    Batch &t = g_bt;
+    if (!t.open || !out) return -1;
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    return cudaMemcpy(out, t.hidden, sizeof(float) * t.B * D, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+
+int batch_launches_per_frame() { return 1 + VB200_DEC_LAYERS * 7 + 5 + (VB200_FLOW_STEPS - 1) * (2 + VB200_AC_LAYERS * 7) + 1; }
+
+} // namespace vb

@@ -160,6 +160,7 @@ void model_free() {
     Model &m = g_model;
     if (!m.inited) return;
     cudaDeviceSynchronize();
+    batch_free_all();
     for (void *p : m.allocs) cudaFree(p);
     m.allocs.clear();
     if (m.h_in) cudaFreeHost(m.h_in);
@@ -246,6 +247,7 @@ int model_upload_llm(const vb200_decoder_weights_t *w) {
     g_cuda.tok_embeddings_gpu = m.tok_emb;
     g_cuda.dec_norm_gpu = m.dec_norm;
     m.llm_ready = true;
+    batch_invalidate();
     prefill_tc_setup();
     return model_rebuild_programs();
 }
@@ -304,6 +306,7 @@ int model_upload_acoustic(const vb200_acoustic_weights_t *w) {
     dev_release(temb_d);
     if (rc) { upload_failed(); return -1; }
     if (acoustic_tc_setup()) { upload_failed(); return -1; }
+    batch_invalidate();
     m.ac_ready = true;
     return model_rebuild_programs();
 }

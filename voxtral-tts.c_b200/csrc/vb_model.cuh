@@ -122,6 +122,18 @@ int acoustic_tc_setup();
 bool acoustic_tc_ready();
 int acoustic_tc_enqueue(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end);
 
+/* several utterances in lock step (vb_batch.cu) */
+int batch_open(int n_utt, int kv_max, int max_frames);
+int batch_prefill(int utt, const float *embeds, int n_rows);
+int batch_begin(const float *first_embeds, const int *start_pos, const float *noise);
+int batch_run(int n);
+int batch_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
+int batch_hidden(float *out);
+int batch_launches_per_frame();
+void batch_close();
+void batch_invalidate();
+void batch_free_all();
+
 int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);
 int utterance_run(int n);
 int utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
