@@ -268,6 +268,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="frames of the host-ABI measurement (default: min(steps, 64))")
     ap.add_argument("--cpu-budget", type=float, default=25.0, help="seconds of CPU-baseline frames")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--utterances", type=int, default=8,
+                    help="utterances per GPU of the additional lock-step measurement (1 = skip it)")
     ap.add_argument("--micro", default="", choices=["", "gemv"],
                     help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
     ap.add_argument("--m", type=int, default=1)
@@ -384,48 +386,101 @@ def main():
     e2e_value, _ = aggregate(e2e_s * 1000.0, Ke, dist)
 
     # ---- roofline of the dominant kernel --------------------------------------------------------
-    # Per frame the work is one launch of vb_engine_kernel (re-embedding, the 26-layer decoder
-    # step, semantic head + llm token: the streaming GEMV path) followed, when the tensor-core
-    # path is up, by 84 vb_tc_gemm_kernel launches (the acoustic layers, 7 steps x 3 layers x 4
-    # matrices) and small glue kernels. The frame kernel has the largest share of the frame; its
-    # launches are timed one by one with CUDA events inside the timed region.
     peak, peak_src = measured_hbm_peak()
-    n_eng = C.c_int(0)
-    eng_ms_total = float(Lb.vb200_utterance_engine_ms(C.byref(n_eng)))
-    tc_path = os.environ.get("VB200_NO_TC") is None
+    on_tc = bool(Lb.vb200_frame_on_tensor_cores())
     head_bytes = 51_118_080 + 18_874_368                      # semantic head + llm_proj
-    dec_bytes = lambda pos: LLM_WEIGHT_BYTES + LLM_NORM_BYTES + 26 * (pos + 1) * 8192 + KV_WRITE_BYTES
     mean_frame_bytes = float(np.mean([frame_bytes(PROMPT_ROWS + W + f) for f in range(K)]))
-    if tc_path and n_eng.value == K:
-        eng_bytes = float(np.mean([dec_bytes(PROMPT_ROWS + W + f) for f in range(K)])) + head_bytes + REEMBED_BYTES
-        launch_ms = eng_ms_total / n_eng.value
-        kernel_desc = "vb_engine_kernel (one launch per frame: re-embedding + decoder step + semantic head)"
-    else:                                                     # whole frame inside the frame kernel
-        eng_bytes = mean_frame_bytes
-        launch_ms = (eng_ms_total / n_eng.value) if n_eng.value == K else total_ms / K
-        kernel_desc = "vb_engine_kernel (one launch = one whole frame)"
-    achieved = eng_bytes / (launch_ms / 1000.0) / 1e9
-    traffic = None
-    try:
-        with open(os.path.join(ROOT, "profiles", "frame_kernel_traffic.json")) as f:
-            ratio = json.load(f).get("dram_read_over_algorithmic")
-            traffic = eng_bytes * ratio if ratio else None
-    except Exception:
-        pass
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "kernel": kernel_desc, "algorithmic_bytes_per_launch": eng_bytes,
-                "launch_ms": launch_ms, "share_of_frame_time": launch_ms / (total_ms / K), "peak_source": peak_src,
-                "whole_frame": {"algorithmic_bytes": mean_frame_bytes, "ms": total_ms / K,
-                                "achieved": mean_frame_bytes / (total_ms / K / 1000.0) / 1e9,
-                                "frac": mean_frame_bytes / (total_ms / K / 1000.0) / 1e9 / peak}}
-    if tc_path and n_eng.value == K:
-        rest_ms = total_ms / K - launch_ms
-        ac_bytes = ACOUSTIC_BYTES - head_bytes
-        roofline["acoustic_tensor_core_path"] = {
-            "kernels": "84 x vb_tc_gemm_kernel<16> + prepare / attention / velocity / FSQ glue, one CUDA graph",
-            "algorithmic_bytes": ac_bytes, "ms": rest_ms, "achieved": ac_bytes / (rest_ms / 1000.0) / 1e9,
-            "frac": ac_bytes / (rest_ms / 1000.0) / 1e9 / peak}
-    launches_per_frame = 1 + (84 + 42 + 21 + 14 + 1 if tc_path else 0)
+    frame_ms = total_ms / K
+    whole = {"algorithmic_bytes": mean_frame_bytes, "ms": frame_ms,
+             "achieved": mean_frame_bytes / (frame_ms / 1000.0) / 1e9,
+             "frac": mean_frame_bytes / (frame_ms / 1000.0) / 1e9 / peak}
+    if on_tc:
+        # A frame is one CUDA graph of 350 launches; 190 of them are vb_tc_gemm_kernel<16> and
+        # carry every weight byte (104 decoder-layer GEMMs, 2 head GEMMs, 84 acoustic-layer
+        # GEMMs). Launches inside a graph cannot be bracketed one by one, so the kernel's own
+        # launch time is measured live on the decoder's 104 GEMMs launched back to back (every
+        # decoder weight byte once per sweep: 6.05 GB, far beyond L2) between two CUDA events.
+        sweeps = 10
+        sms, sbytes, sn = C.c_float(0.0), C.c_double(0.0), C.c_int(0)
+        assert Lb.vb200_gemm_sweep(0, 2, C.byref(sms), C.byref(sbytes), C.byref(sn)) == 0
+        assert Lb.vb200_gemm_sweep(0, sweeps, C.byref(sms), C.byref(sbytes), C.byref(sn)) == 0
+        launch_ms = sms.value / (sweeps * sn.value)
+        bytes_per_launch = sbytes.value / sn.value
+        achieved = bytes_per_launch / (launch_ms / 1000.0) / 1e9
+        gemm_bytes_frame = LLM_WEIGHT_BYTES + ACOUSTIC_BYTES
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "tc_gemm_traffic.json")) as f:
+                ratio = json.load(f).get("dram_bytes_over_algorithmic")
+                traffic = bytes_per_launch * ratio if ratio else None
+        except Exception:
+            pass
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": traffic,
+                    "kernel": "vb_tc_gemm_kernel<16> (tcgen05 skinny GEMM; 190 of a frame's 350 launches, all weight bytes)",
+                    "algorithmic_bytes_per_launch": bytes_per_launch, "launch_ms": launch_ms,
+                    "measured_on": f"{sweeps} sweeps of the decoder's {sn.value} layer GEMMs, back to back, CUDA events",
+                    "share_of_frame_time": (gemm_bytes_frame / 1e9 / achieved * 1000.0) / frame_ms,
+                    "peak_source": peak_src, "whole_frame": whole}
+        launches_per_frame = int(Lb.vb200_batch_launches_per_frame())
+    else:
+        n_eng = C.c_int(0)
+        eng_ms_total = float(Lb.vb200_utterance_engine_ms(C.byref(n_eng)))
+        tc_ac = os.environ.get("VB200_NO_TC") is None
+        dec_bytes = lambda pos: LLM_WEIGHT_BYTES + LLM_NORM_BYTES + 26 * (pos + 1) * 8192 + KV_WRITE_BYTES
+        if tc_ac and n_eng.value == K:
+            eng_bytes = float(np.mean([dec_bytes(PROMPT_ROWS + W + f) for f in range(K)])) + head_bytes + REEMBED_BYTES
+            launch_ms = eng_ms_total / n_eng.value
+            kernel_desc = "vb_engine_kernel (one launch per frame: re-embedding + decoder step + semantic head)"
+        else:                                                     # whole frame inside the frame kernel
+            eng_bytes = mean_frame_bytes
+            launch_ms = (eng_ms_total / n_eng.value) if n_eng.value == K else frame_ms
+            kernel_desc = "vb_engine_kernel (one launch = one whole frame)"
+        achieved = eng_bytes / (launch_ms / 1000.0) / 1e9
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "frame_kernel_traffic.json")) as f:
+                ratio = json.load(f).get("dram_read_over_algorithmic")
+                traffic = eng_bytes * ratio if ratio else None
+        except Exception:
+            pass
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": traffic, "kernel": kernel_desc, "algorithmic_bytes_per_launch": eng_bytes,
+                    "launch_ms": launch_ms, "share_of_frame_time": launch_ms / frame_ms, "peak_source": peak_src,
+                    "whole_frame": whole}
+        launches_per_frame = 1 + (84 + 42 + 21 + 14 + 1 if tc_ac else 0)
+
+    # ---- several utterances per GPU in lock step (weights read once per frame for all) -----------
+    batched = None
+    if on_tc and args.utterances > 1:
+        Bu = args.utterances
+        Kb, Wb = min(K, 64), min(W, 5)
+        cap = Wb + Kb
+        assert Lb.vb200_batch_open(Bu, PROMPT_ROWS + cap + 8, cap) == 0
+        for u in range(Bu):
+            pr = rows if u == 0 else prompt_rows(pkg, model, seeds["prompt"] + 17 * u)
+            assert Lb.vb200_batch_prefill(u, pr.ctypes.data, PROMPT_ROWS) == 0
+        nb = np.stack([noise_rows(seeds["noise"] + 31 * u, cap) for u in range(Bu)]).astype(np.float32)
+        fe = np.ascontiguousarray(np.stack([first] * Bu), dtype=np.float32)
+        sp = np.full(Bu, PROMPT_ROWS, dtype=np.int32)
+        assert Lb.vb200_batch_begin(fe.ctypes.data, sp.ctypes.data, nb.ctypes.data) == 0
+        assert Lb.vb200_batch_run(Wb) == 0
+        torch.cuda.synchronize()
+        barrier()
+        assert Lb.vb200_batch_run(Kb) == 0
+        bdone = np.zeros(Bu, dtype=np.int32)
+        bms = C.c_float(0.0)
+        assert Lb.vb200_batch_end(None, bdone.ctypes.data, None, C.byref(bms)) == 0
+        if int(bdone.min()) != cap:
+            raise SystemExit(f"batched loop ran {bdone.tolist()} of {cap} frames")
+        Lb.vb200_batch_close()
+        bval, bmax = aggregate(bms.value, Kb * Bu, dist)
+        per_utt = float(np.mean([26 * (PROMPT_ROWS + Wb + f + 1) * 8192 for f in range(Kb)])) + KV_WRITE_BYTES + REEMBED_BYTES
+        step_bytes = LLM_WEIGHT_BYTES + LLM_NORM_BYTES + ACOUSTIC_BYTES + Bu * per_utt
+        batched = {"utterances_per_gpu": Bu, "value": bval, "unit": "frames/s", "steps": Kb, "ms_per_step": bmax / Kb,
+                   "algorithmic_bytes_per_step": step_bytes,
+                   "hbm_frac": step_bytes / (bmax / Kb / 1000.0) / 1e9 / peak,
+                   "workload": "BASELINE config 5 per GPU: 8 utterances, 256-row prompts, lock-step frames"}
 
     if rank != 0:
         eng.close()
@@ -447,7 +502,8 @@ def main():
             "data": "synthetic", "config": config, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "frames/s", "steps": Ke,
                     "h2d_bytes_per_step": 16 + 3072 * 4 + 36 * 4, "d2h_bytes_per_step": 176 + 3072 * 4},
-            "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu}
+            "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu,
+            "batched": batched}
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

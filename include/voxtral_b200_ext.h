@@ -75,6 +75,15 @@ int vb200_batch_hidden(float *out);
 int vb200_batch_launches_per_frame(void);
 void vb200_batch_close(void);
 
+/* Measurement aid: the decoder's 104 layer GEMMs (every decoder weight byte once) launched
+ * back to back `iters` times between two CUDA events, on the single-utterance buffers
+ * (which = 0) or on the open batch (which = 1). Returns the elapsed ms, the weight bytes of
+ * one sweep and its launch count. */
+int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, int *launches_per_sweep);
+/* 1 when vb200_frame / vb200_utterance_* run as the graph of tensor-core GEMM launches, 0 when
+ * they run on the streaming frame kernel (VB200_NO_TC=1, or per-layer taps enabled). */
+int vb200_frame_on_tensor_cores(void);
+
 /* Options by name. "ignore_end" (0/1): a device-resident run started after this call
  * treats END as an ordinary code, for fixed-length timing runs. Returns -1 for an
  * unknown name. */

@@ -52,7 +52,9 @@ def test_frame_equals_separate_calls(pkg, engine, oracle):
     codes, hidden = engine.frame(e, noise, pos)
     h2 = engine.llm_forward(e, pos)
     c2, _ = engine.acoustic_frame(h2, noise)
-    assert np.array_equal(hidden, h2) and np.array_equal(codes, c2)
+    # the frame runs the decoder step on the tensor-core GEMM, the separate call on the streaming
+    # kernel: same arithmetic, different summation order
+    assert rel_l2(hidden, h2) < 1e-4 and np.array_equal(codes, c2)
 
 
 def test_device_resident_loop_matches_golden(pkg, engine, oracle):

@@ -171,6 +171,10 @@ int vb200_batch_end(int *codes_out, int *frames_done, int *hit_end, float *devic
 int vb200_batch_hidden(float *out) { return batch_hidden(out); }
 int vb200_batch_launches_per_frame(void) { return batch_launches_per_frame(); }
 void vb200_batch_close(void) { batch_close(); }
+int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, int *launches_per_sweep) {
+    return gemm_sweep(which, iters, ms, bytes_per_sweep, launches_per_sweep);
+}
+int vb200_frame_on_tensor_cores(void) { return single_tc_usable() ? 1 : 0; }
 
 double vb200_utterance_engine_ms(int *launches) {
     if (launches) *launches = model().run_engine_n;

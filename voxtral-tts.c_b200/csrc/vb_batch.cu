@@ -35,18 +35,44 @@ constexpr int kBtSubsets = 4;              /* warp subsets of a CTA's key range 
 constexpr int kBtAttnThreads = 512;
 constexpr int kCodeStride = 40;            /* ints per utterance in the codes block */
 
-struct Batch {
-    bool open = false, begun = false;
-    int B = 0, kv_max = 0, cap = 0, launched = 0;
-    std::vector<void *> allocs;
-    /* decoder weights on the tensor-core path (tile-contiguous copies) */
-    bool weights_ready = false;
+/* Decoder weights on the tensor-core path (tile-contiguous copies), shared by every context. */
+struct BtWeights {
+    bool ready = false;
     TcWeight wqkv[VB200_DEC_LAYERS], wo[VB200_DEC_LAYERS], w13[VB200_DEC_LAYERS], w2[VB200_DEC_LAYERS];
     TcWeight wsem, wllm;
-    std::vector<void *> weight_allocs;
+    std::vector<void *> allocs;
     int s_qkv = 1, s_wo = 1, s_w2 = 1, s_sem = 1, s_llm = 1;
+};
+static BtWeights g_w;
+
+/* Host <-> device blocks of the single-utterance context: one copy each way per frame. */
+struct OneIn {
+    VbDyn dyn;
+    alignas(16) float X[VB200_DIM];
+    alignas(16) float noise[VB200_ACOUSTIC_DIM];
+};
+struct OneOut {
+    int status[4];
+    int codes[40];
+    alignas(16) float hidden[VB200_DIM];
+};
+
+/* How a frame gets its decoder input row. */
+enum EmbedMode {
+    EMBED_HOST = 0,        /* the host wrote it */
+    EMBED_CODES = 1,       /* always from the previous frame's codes */
+    EMBED_CODES_AFTER0 = 2 /* from the codes, except for frame 0 of a run */
+};
+
+constexpr int kVariants = 3;   /* captured graphs: run loop, single frame, single chained frame */
+
+struct Batch {
+    bool open = false, begun = false, single = false;
+    int B = 0, kv_max = 0, cap = 0, launched = 0;
+    int alloc_cap = 0;                          /* frames the noise / code arrays were allocated for */
+    std::vector<void *> allocs;
     /* per-utterance state */
-    float *kv_k = nullptr, *kv_v = nullptr;     /* [B][layers][kv_max][1024] */
+    float *kv_k = nullptr, *kv_v = nullptr;     /* [B][layers][kv_max][1024] (single: the library's cache) */
     size_t slab = 0;                            /* floats per utterance */
     VbDyn *dyn = nullptr;                       /* [B] */
     float *X = nullptr, *hidden = nullptr;      /* [B][3072] */
@@ -54,6 +80,9 @@ struct Batch {
     int *codes = nullptr, *status = nullptr;
     float *noise_all = nullptr;                 /* [B][cap][36] */
     int *codes_all = nullptr;                   /* [B][cap][37] */
+    float *noise1 = nullptr;                    /* single context: the noise row of a single-frame call */
+    OneIn *d_in = nullptr, *h_in = nullptr;     /* single context */
+    OneOut *d_out = nullptr, *h_out = nullptr;
     /* decoder-step activations */
     TcActs aD, aQ, aH;
     uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
@@ -61,23 +90,25 @@ struct Batch {
     float *attn_scratch = nullptr;
     unsigned *tickets = nullptr;
     AcBuffers ac;
-    cudaGraphExec_t exec = nullptr;
-    int direct_calls = 0;
+    cudaGraphExec_t exec[kVariants] = {};
+    int direct_calls[kVariants] = {};
+    int graph_cap = 0;                          /* frame cap baked into exec[0] */
     cudaEvent_t e0 = nullptr, e1 = nullptr;
 };
-static Batch g_bt;
+static Batch g_bt;    /* vb200_batch_*: up to 8 utterances, own cache slabs */
+static Batch g_one;   /* the single-utterance calls on the library's cache */
 
 /* ------------------------------------------------------------------ kernels */
 
 /* Next decoder input of every utterance: the sum of the 37 code rows of the audio table in
- * codebook order (voxtral_tts_voice.c:292-315, offsets :275-283). Frame 0 keeps the row the
- * host supplied. grid = (dim / 256, B). */
+ * codebook order (voxtral_tts_voice.c:292-315, offsets :275-283). Frame 0 of a run keeps the
+ * row the host supplied. grid = (dim / 256, B). */
 __global__ void bt_embed_kernel(float *X, const uint16_t *table, const int *codes, const VbDyn *dyn, int n_codes,
-                                int rows0, int rows_other) {
+                                int rows0, int rows_other, int mode) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y;
-    if (dyn[b].done || dyn[b].frame == 0) return;
+    if (dyn[b].done || (mode == EMBED_CODES_AFTER0 && dyn[b].frame == 0)) return;
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= D) return;
     const int *cb = codes + (size_t)b * kCodeStride;
@@ -343,87 +374,110 @@ static void bt_free(std::vector<void *> *owner) {
     owner->clear();
 }
 
+static void drop_graphs(Batch &t) {
+    for (int v = 0; v < kVariants; v++) {
+        if (t.exec[v]) cudaGraphExecDestroy(t.exec[v]);
+        t.exec[v] = nullptr;
+        t.direct_calls[v] = 0;
+    }
+}
+
 /* Tile-contiguous copies of the decoder's matrices and of the two heads, made once per
  * weight upload. */
 static int bt_weights() {
     Model &m = model();
-    Batch &t = g_bt;
-    if (t.weights_ready) return 0;
+    BtWeights &w = g_w;
+    if (w.ready) return 0;
     if (tc_init()) return -1;
-    bt_free(&t.weight_allocs);
-    auto tiled = [&](TcWeight *w, const uint16_t *src, int N, int K) -> int {
+    bt_free(&w.allocs);
+    auto tiled = [&](TcWeight *tw, const uint16_t *src, int N, int K) -> int {
         void *dst = nullptr;
-        if (bt_alloc(&dst, tc_tiled_bytes(N, K), &t.weight_allocs)) return -1;
-        return tc_weight_tiled(w, src, N, K, (uint16_t *)dst, m.st);
+        if (bt_alloc(&dst, tc_tiled_bytes(N, K), &w.allocs)) return -1;
+        return tc_weight_tiled(tw, src, N, K, (uint16_t *)dst, m.st);
     };
     for (int l = 0; l < VB200_DEC_LAYERS; l++) {
         const LayerDev &L = m.dec[l];
-        if (tiled(&t.wqkv[l], L.wqkv, QKV, D) || tiled(&t.wo[l], L.wo, D, QD) || tiled(&t.w13[l], L.w13, 2 * HID, D) ||
-            tiled(&t.w2[l], L.w2, D, HID))
+        if (tiled(&w.wqkv[l], L.wqkv, QKV, D) || tiled(&w.wo[l], L.wo, D, QD) || tiled(&w.w13[l], L.w13, 2 * HID, D) ||
+            tiled(&w.w2[l], L.w2, D, HID))
             return -1;
     }
-    if (tiled(&t.wsem, m.ac_sem_out, NSEM, D) || tiled(&t.wllm, m.ac_llm_proj, D, D)) return -1;
+    if (tiled(&w.wsem, m.ac_sem_out, NSEM, D) || tiled(&w.wllm, m.ac_llm_proj, D, D)) return -1;
     if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
-    t.s_qkv = tc_pick_splits(QKV, D, m.sm_count);
-    t.s_wo = tc_pick_splits(D, QD, m.sm_count);
-    t.s_w2 = tc_pick_splits(D, HID, m.sm_count);
-    t.s_sem = tc_pick_splits(NSEM, D, m.sm_count);
-    t.s_llm = tc_pick_splits(D, D, m.sm_count);
-    t.weights_ready = true;
+    w.s_qkv = tc_pick_splits(QKV, D, m.sm_count);
+    w.s_wo = tc_pick_splits(D, QD, m.sm_count);
+    w.s_w2 = tc_pick_splits(D, HID, m.sm_count);
+    w.s_sem = tc_pick_splits(NSEM, D, m.sm_count);
+    w.s_llm = tc_pick_splits(D, D, m.sm_count);
+    w.ready = true;
     return 0;
 }
 
-/* Called when weights are uploaded again: the copies and any captured graph are stale. */
-void batch_invalidate() {
-    Batch &t = g_bt;
-    if (t.exec) { cudaGraphExecDestroy(t.exec); t.exec = nullptr; }
-    t.direct_calls = 0;
-    t.weights_ready = false;
-}
-
-void batch_close() {
-    Batch &t = g_bt;
-    if (t.exec) { cudaGraphExecDestroy(t.exec); t.exec = nullptr; }
+static void ctx_close(Batch &t) {
+    drop_graphs(t);
     if (model().st) cudaStreamSynchronize(model().st);
     bt_free(&t.allocs);
-    if (t.e0) { cudaEventDestroy(t.e0); t.e0 = nullptr; }
-    if (t.e1) { cudaEventDestroy(t.e1); t.e1 = nullptr; }
-    t.open = t.begun = false;
-    t.B = 0;
-    t.noise_all = nullptr; t.codes_all = nullptr;
-    t.ac = AcBuffers();
-    t.direct_calls = 0;
+    if (t.h_in) cudaFreeHost(t.h_in);
+    if (t.h_out) cudaFreeHost(t.h_out);
+    if (t.e0) cudaEventDestroy(t.e0);
+    if (t.e1) cudaEventDestroy(t.e1);
+    t = Batch();
 }
+
+/* Called when weights are uploaded again: the copies and every captured graph are stale. */
+void batch_invalidate() {
+    drop_graphs(g_bt);
+    drop_graphs(g_one);
+    g_w.ready = false;
+}
+
+void batch_close() { ctx_close(g_bt); }
 
 void batch_free_all() {
-    batch_close();
-    bt_free(&g_bt.weight_allocs);
-    g_bt.weights_ready = false;
+    ctx_close(g_bt);
+    ctx_close(g_one);
+    bt_free(&g_w.allocs);
+    g_w.ready = false;
 }
 
-int batch_open(int n_utt, int kv_max, int max_frames) {
+/* Buffers of a context. single: one utterance on the library's own cache, with pinned
+ * staging blocks; otherwise n_utt cache slabs of kv_max rows. */
+static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames) {
     Model &m = model();
-    Batch &t = g_bt;
-    if (!m.inited || !m.llm_ready || !m.ac_ready || !m.embed_ready || !acoustic_tc_ready()) return -1;
-    if (n_utt < 1 || n_utt > kBtMaxUtt || kv_max < 1 || max_frames < 1) return -1;
-    batch_close();
+    ctx_close(t);
     if (bt_weights()) return -1;
-    t.B = n_utt; t.kv_max = kv_max; t.cap = max_frames;
+    t.single = single;
+    t.B = n_utt; t.kv_max = kv_max; t.cap = max_frames; t.alloc_cap = max_frames;
     t.slab = (size_t)VB200_DEC_LAYERS * kv_max * KVD;
     const int B = n_utt;
     int rc = 0;
-    rc |= bt_alloc((void **)&t.kv_k, sizeof(float) * t.slab * B, &t.allocs);
-    rc |= bt_alloc((void **)&t.kv_v, sizeof(float) * t.slab * B, &t.allocs);
-    rc |= bt_alloc((void **)&t.dyn, sizeof(VbDyn) * B, &t.allocs);
-    rc |= bt_alloc((void **)&t.X, sizeof(float) * B * D, &t.allocs);
-    rc |= bt_alloc((void **)&t.hidden, sizeof(float) * B * D, &t.allocs);
+    if (single) {
+        t.kv_k = m.kv_k; t.kv_v = m.kv_v;
+        rc |= bt_alloc((void **)&t.d_in, sizeof(OneIn), &t.allocs);
+        rc |= bt_alloc((void **)&t.d_out, sizeof(OneOut), &t.allocs);
+        if (!rc) {
+            t.dyn = &t.d_in->dyn; t.X = t.d_in->X; t.noise1 = t.d_in->noise;
+            t.status = t.d_out->status; t.codes = t.d_out->codes; t.hidden = t.d_out->hidden;
+            if (cudaMallocHost((void **)&t.h_in, sizeof(OneIn)) != cudaSuccess ||
+                cudaMallocHost((void **)&t.h_out, sizeof(OneOut)) != cudaSuccess)
+                rc = -1;
+            else { memset(t.h_in, 0, sizeof(OneIn)); memset(t.h_out, 0, sizeof(OneOut)); }
+        }
+    } else {
+        rc |= bt_alloc((void **)&t.kv_k, sizeof(float) * t.slab * B, &t.allocs);
+        rc |= bt_alloc((void **)&t.kv_v, sizeof(float) * t.slab * B, &t.allocs);
+        rc |= bt_alloc((void **)&t.dyn, sizeof(VbDyn) * B, &t.allocs);
+        rc |= bt_alloc((void **)&t.X, sizeof(float) * B * D, &t.allocs);
+        rc |= bt_alloc((void **)&t.hidden, sizeof(float) * B * D, &t.allocs);
+        rc |= bt_alloc((void **)&t.codes, sizeof(int) * B * kCodeStride, &t.allocs);
+        rc |= bt_alloc((void **)&t.status, sizeof(int) * 4, &t.allocs);
+    }
     rc |= bt_alloc((void **)&t.lat, sizeof(float) * B * VB200_FLOW_STEPS * A, &t.allocs);
     rc |= bt_alloc((void **)&t.vel, sizeof(float) * B * 2 * A, &t.allocs);
     rc |= bt_alloc((void **)&t.ltok, sizeof(float) * B * D, &t.allocs);
-    rc |= bt_alloc((void **)&t.codes, sizeof(int) * B * kCodeStride, &t.allocs);
-    rc |= bt_alloc((void **)&t.status, sizeof(int) * 4, &t.allocs);
-    rc |= bt_alloc((void **)&t.noise_all, sizeof(float) * (size_t)B * max_frames * A, &t.allocs);
-    rc |= bt_alloc((void **)&t.codes_all, sizeof(int) * (size_t)B * max_frames * VB200_CODES, &t.allocs);
+    if (max_frames > 0) {
+        rc |= bt_alloc((void **)&t.noise_all, sizeof(float) * (size_t)B * max_frames * A, &t.allocs);
+        rc |= bt_alloc((void **)&t.codes_all, sizeof(int) * (size_t)B * max_frames * VB200_CODES, &t.allocs);
+    }
     rc |= bt_alloc((void **)&t.bD, tc_acts_bytes(16, D), &t.allocs);
     rc |= bt_alloc((void **)&t.bQ, tc_acts_bytes(16, QD), &t.allocs);
     rc |= bt_alloc((void **)&t.bH, tc_acts_bytes(16, HID), &t.allocs);
@@ -433,20 +487,126 @@ int batch_open(int n_utt, int kv_max, int max_frames) {
     rc |= bt_alloc((void **)&t.attn_scratch,
                    sizeof(float) * (size_t)B * VB200_KV_HEADS * kBtKeySplits * kGroup * (kHD + 2), &t.allocs);
     rc |= bt_alloc((void **)&t.tickets, sizeof(unsigned) * B * VB200_KV_HEADS, &t.allocs);
-    if (rc) { batch_close(); return -1; }
+    if (rc) { ctx_close(t); return -1; }
     if (tc_acts(&t.aD, t.bD, 16, D) || tc_acts(&t.aQ, t.bQ, 16, QD) || tc_acts(&t.aH, t.bH, 16, HID)) {
-        batch_close();
+        ctx_close(t);
         return -1;
     }
     t.ac = AcBuffers();
-    if (acoustic_buffers_alloc(&t.ac, B, &t.allocs)) { batch_close(); return -1; }
+    if (acoustic_buffers_alloc(&t.ac, B, &t.allocs)) { ctx_close(t); return -1; }
     t.ac.lat = t.lat; t.ac.vel = t.vel; t.ac.ltok = t.ltok; t.ac.codes = t.codes; t.ac.dyn = t.dyn;
     t.ac.status = t.status;
     t.ac.sd.lat = VB200_FLOW_STEPS * A; t.ac.sd.vel = 2 * A; t.ac.sd.codes = kCodeStride;
     t.ac.sd.noise = (size_t)max_frames * A; t.ac.sd.codes_all = (size_t)max_frames * VB200_CODES;
-    if (cudaEventCreate(&t.e0) != cudaSuccess || cudaEventCreate(&t.e1) != cudaSuccess) { batch_close(); return -1; }
+    if (cudaEventCreate(&t.e0) != cudaSuccess || cudaEventCreate(&t.e1) != cudaSuccess) { ctx_close(t); return -1; }
     t.open = true;
     return 0;
+}
+
+/* One frame of every utterance of the context, enqueued launch by launch. */
+static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *noise, int *codes_log, int cap) {
+    Model &m = model();
+    const BtWeights &w = g_w;
+    cudaStream_t st = m.st;
+    const int B = t.B;
+    const float scale = 1.0f / sqrtf((float)kHD);
+    const int chunksD = tc_prepare_chunks(D);
+    const size_t psD = (size_t)B * D, psQ = (size_t)B * QKV;
+    if (embed_mode != EMBED_HOST)
+        launch_pdl(bt_embed_kernel, dim3((D + 255) / 256, B), dim3(256), 0, st, t.X, (const uint16_t *)m.audio_table,
+                   (const int *)t.codes, (const VbDyn *)t.dyn, VB200_CODES, 8194, 23, embed_mode);
+    TcGemm g;
+    g.M = B; g.status = t.status;
+    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+        const LayerDev &L = m.dec[l];
+        if (l == 0) tc_prepare(t.aD, t.X, D, B, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
+        else tc_prepare(t.aD, nullptr, D, B, t.part, w.s_w2, psD, t.X, t.X, L.attn_norm, t.ssq, st);
+        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+        g.splits = w.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+        if (tc_gemm(w.wqkv[l], t.aD, g, st)) return -1;
+        launch_pdl(bt_attn_kernel, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ, 16,
+                   (const float *)t.part, w.s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn, scale,
+                   VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status);
+        g.splits = w.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+        if (tc_gemm(w.wo[l], t.aQ, g, st)) return -1;
+        tc_prepare(t.aD, nullptr, D, B, t.part, w.s_wo, psD, t.X, t.X, L.ffn_norm, t.ssq, st);
+        g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
+        g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
+        if (tc_gemm(w.w13[l], t.aD, g, st)) return -1;
+        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+        g.splits = w.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+        if (tc_gemm(w.w2[l], t.aH, g, st)) return -1;
+    }
+    launch_pdl(bt_final_kernel, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
+               (const float *)t.part, w.s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS);
+    /* semantic head + argmax (voxtral_tts_acoustic.c:283-309), llm token (:204) */
+    g.epi = TC_EPI_PARTIAL; g.out = t.logit_part; g.splits = w.s_sem; g.ld_out = NSEM; g.ssq = nullptr; g.ssq_chunks = 0;
+    if (tc_gemm(w.wsem, t.aD, g, st)) return -1;
+    launch_pdl(bt_argmax_kernel, dim3(B), dim3(1024), 0, st, t.codes, (const float *)t.logit_part, w.s_sem,
+               (size_t)B * NSEM, (const float *)m.ac_sem_bias, NSEM, VB200_SEM_VALID_END);
+    g.out = t.part; g.splits = w.s_llm; g.ld_out = D;
+    if (tc_gemm(w.wllm, t.aD, g, st)) return -1;
+    tc_reduce(t.ltok, t.part, w.s_llm, psD, psD, nullptr, D, st);
+    if (acoustic_tc_enqueue_on(t.ac, noise, codes_log, cap, advance, m.ignore_end)) return -1;
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+/* Variant v of the frame: 0 = a frame of a device-resident run, 1 = single frame with the
+ * host's input row, 2 = single frame re-embedding the previous codes. */
+static int enqueue_variant(Batch &t, int v) {
+    switch (v) {
+    case 0: return enqueue_frame(t, EMBED_CODES_AFTER0, true, t.noise_all, t.codes_all, t.cap);
+    case 1: return enqueue_frame(t, EMBED_HOST, false, t.noise1, nullptr, 0);
+    default: return enqueue_frame(t, EMBED_CODES, false, t.noise1, nullptr, 0);
+    }
+}
+
+/* The first call of a variant runs launch by launch (kernel attributes are set on first use,
+ * which must not happen inside a capture), the second is captured as a CUDA graph and every
+ * later call replays it. */
+static int launch_variant(Batch &t, int v) {
+    Model &m = model();
+    static const bool no_graph = getenv("VB200_NO_GRAPH") != nullptr;
+    if (t.exec[v]) return cudaGraphLaunch(t.exec[v], m.st) == cudaSuccess ? 0 : -1;
+    if (no_graph || t.direct_calls[v]++ == 0) return enqueue_variant(t, v);
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(m.st, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+        cudaGetLastError();
+        return enqueue_variant(t, v);
+    }
+    const int rc = enqueue_variant(t, v);
+    const cudaError_t ee = cudaStreamEndCapture(m.st, &graph);
+    if (rc || ee != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return -1;
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&t.exec[v], graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        t.exec[v] = nullptr;
+        cudaGetLastError();
+        return -1;
+    }
+    return cudaGraphLaunch(t.exec[v], m.st) == cudaSuccess ? 0 : -1;
+}
+
+static int ctx_run(Batch &t, int n) {
+    Model &m = model();
+    if (!t.begun || n < 0) return -1;
+    cudaEventRecord(t.e0, m.st);
+    for (int i = 0; i < n && t.launched < t.cap; i++, t.launched++)
+        if (launch_variant(t, 0)) return -1;
+    cudaEventRecord(t.e1, m.st);
+    return 0;
+}
+
+/* ---- several utterances ---- */
+int batch_open(int n_utt, int kv_max, int max_frames) {
+    Model &m = model();
+    if (!m.inited || !m.llm_ready || !m.ac_ready || !m.embed_ready || !acoustic_tc_ready()) return -1;
+    if (n_utt < 1 || n_utt > kBtMaxUtt || kv_max < 1 || max_frames < 1) return -1;
+    return ctx_open(g_bt, false, n_utt, kv_max, max_frames);
 }
 
 /* Prompt rows of one utterance into its own cache slab (the single-utterance prefill,
@@ -454,7 +614,7 @@ int batch_open(int n_utt, int kv_max, int max_frames) {
 int batch_prefill(int utt, const float *embeds, int n_rows) {
     Model &m = model();
     Batch &t = g_bt;
-    if (!t.open || utt < 0 || utt >= t.B || n_rows < 1 || n_rows > t.kv_max) return -1;
+    if (!t.open || !embeds || utt < 0 || utt >= t.B || n_rows < 1 || n_rows > t.kv_max) return -1;
     float *k0 = m.kv_k, *v0 = m.kv_v;
     const int max0 = m.kv_max;
     m.kv_k = t.kv_k + (size_t)utt * t.slab;
@@ -487,96 +647,8 @@ int batch_begin(const float *first_embeds, const int *start_pos, const float *no
     return 0;
 }
 
-/* One frame of every utterance, enqueued launch by launch. */
-static int bt_enqueue_frame() {
-    Model &m = model();
-    Batch &t = g_bt;
-    cudaStream_t st = m.st;
-    const int B = t.B;
-    const float scale = 1.0f / sqrtf((float)kHD);
-    const int chunksD = tc_prepare_chunks(D);
-    const size_t psD = (size_t)B * D, psQ = (size_t)B * QKV;
-    launch_pdl(bt_embed_kernel, dim3((D + 255) / 256, B), dim3(256), 0, st, t.X, (const uint16_t *)m.audio_table,
-               (const int *)t.codes, (const VbDyn *)t.dyn, VB200_CODES, 8194, 23);
-    TcGemm g;
-    g.M = B; g.status = t.status;
-    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
-        const LayerDev &L = m.dec[l];
-        if (l == 0) tc_prepare(t.aD, t.X, D, B, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
-        else tc_prepare(t.aD, nullptr, D, B, t.part, t.s_w2, psD, t.X, t.X, L.attn_norm, t.ssq, st);
-        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
-        g.splits = t.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
-        if (tc_gemm(t.wqkv[l], t.aD, g, st)) return -1;
-        launch_pdl(bt_attn_kernel, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ, 16,
-                   (const float *)t.part, t.s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn, scale,
-                   VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status);
-        g.splits = t.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
-        if (tc_gemm(t.wo[l], t.aQ, g, st)) return -1;
-        tc_prepare(t.aD, nullptr, D, B, t.part, t.s_wo, psD, t.X, t.X, L.ffn_norm, t.ssq, st);
-        g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
-        g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
-        if (tc_gemm(t.w13[l], t.aD, g, st)) return -1;
-        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
-        g.splits = t.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
-        if (tc_gemm(t.w2[l], t.aH, g, st)) return -1;
-    }
-    launch_pdl(bt_final_kernel, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
-               (const float *)t.part, t.s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS);
-    /* semantic head + argmax (voxtral_tts_acoustic.c:283-309), llm token (:204) */
-    g.epi = TC_EPI_PARTIAL; g.out = t.logit_part; g.splits = t.s_sem; g.ld_out = NSEM; g.ssq = nullptr; g.ssq_chunks = 0;
-    if (tc_gemm(t.wsem, t.aD, g, st)) return -1;
-    launch_pdl(bt_argmax_kernel, dim3(B), dim3(1024), 0, st, t.codes, (const float *)t.logit_part, t.s_sem,
-               (size_t)B * NSEM, (const float *)m.ac_sem_bias, NSEM, VB200_SEM_VALID_END);
-    g.out = t.part; g.splits = t.s_llm; g.ld_out = D;
-    if (tc_gemm(t.wllm, t.aD, g, st)) return -1;
-    tc_reduce(t.ltok, t.part, t.s_llm, psD, psD, nullptr, D, st);
-    if (acoustic_tc_enqueue_on(t.ac, t.noise_all, t.codes_all, t.cap, true, m.ignore_end)) return -1;
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
-}
-
-/* Queues n more frames; returns without waiting. The first frame runs launch by launch
- * (kernel attributes are set on first use, which must not happen inside a capture), the
- * second is captured as a CUDA graph and every later frame replays it. */
-int batch_run(int n) {
-    Model &m = model();
-    Batch &t = g_bt;
-    if (!t.begun || n < 0) return -1;
-    const bool no_graph = getenv("VB200_NO_GRAPH") != nullptr;
-    cudaEventRecord(t.e0, m.st);
-    for (int i = 0; i < n && t.launched < t.cap; i++, t.launched++) {
-        if (t.exec) {
-            if (cudaGraphLaunch(t.exec, m.st) != cudaSuccess) return -1;
-            continue;
-        }
-        if (no_graph || t.direct_calls++ == 0) {
-            if (bt_enqueue_frame()) return -1;
-            continue;
-        }
-        cudaGraph_t graph = nullptr;
-        if (cudaStreamBeginCapture(m.st, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
-            cudaGetLastError();
-            if (bt_enqueue_frame()) return -1;
-            continue;
-        }
-        const int rc = bt_enqueue_frame();
-        const cudaError_t ee = cudaStreamEndCapture(m.st, &graph);
-        if (rc || ee != cudaSuccess || !graph) {
-            if (graph) cudaGraphDestroy(graph);
-            cudaGetLastError();
-            return -1;
-        }
-        const cudaError_t ie = cudaGraphInstantiate(&t.exec, graph, 0);
-        cudaGraphDestroy(graph);
-        if (ie != cudaSuccess) {
-            t.exec = nullptr;
-            cudaGetLastError();
-            return -1;
-        }
-        if (cudaGraphLaunch(t.exec, m.st) != cudaSuccess) return -1;
-    }
-    cudaEventRecord(t.e1, m.st);
-    return 0;
-}
+/* Queues n more frames; returns without waiting. */
+int batch_run(int n) { return ctx_run(g_bt, n); }
 
 /* Waits for the queued frames. codes_out [B][max_frames][37] (rows past frames_done[b] are
  * zero), frames_done[b], hit_end[b] (1 when the utterance produced END; that frame is counted),
@@ -618,5 +690,151 @@ int batch_hidden(float *out) {
 }
 
 int batch_launches_per_frame() { return 1 + VB200_DEC_LAYERS * 7 + 5 + (VB200_FLOW_STEPS - 1) * (2 + VB200_AC_LAYERS * 7) + 1; }
+
+/* The decoder's 104 layer GEMMs (QKV, O, gate/up, down x 26 layers: every decoder weight byte
+ * once) launched back to back on the stream, `iters` times, between two events: the GEMM
+ * kernel's own average launch time at the shapes and row count the frame uses, without the
+ * glue kernels. which = 0: the single-utterance context, 1: the open batch. */
+static int one_ready(int frames);
+int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int *launches_per_sweep) {
+    Model &m = model();
+    if (which == 0 && one_ready(0)) return -1;
+    Batch &t = which == 0 ? g_one : g_bt;
+    if (!t.open || iters < 1) return -1;
+    const BtWeights &w = g_w;
+    const int chunksD = tc_prepare_chunks(D);
+    TcGemm g;
+    g.M = t.B; g.status = t.status; g.eps = VB200_NORM_EPS;
+    cudaEventRecord(t.e0, m.st);
+    for (int it = 0; it < iters; it++) {
+        for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+            g.splits = w.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD;
+            if (tc_gemm(w.wqkv[l], t.aD, g, m.st)) return -1;
+            g.splits = w.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+            if (tc_gemm(w.wo[l], t.aQ, g, m.st)) return -1;
+            g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
+            g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
+            if (tc_gemm(w.w13[l], t.aD, g, m.st)) return -1;
+            g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
+            g.splits = w.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+            if (tc_gemm(w.w2[l], t.aH, g, m.st)) return -1;
+        }
+    }
+    cudaEventRecord(t.e1, m.st);
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    if (ms_out && cudaEventElapsedTime(ms_out, t.e0, t.e1) != cudaSuccess) return -1;
+    if (bytes_per_sweep)
+        *bytes_per_sweep = 2.0 * VB200_DEC_LAYERS * ((double)QKV * D + (double)D * QD + 2.0 * HID * D + (double)D * HID);
+    if (launches_per_sweep) *launches_per_sweep = 4 * VB200_DEC_LAYERS;
+    return 0;
+}
+
+/* ---- one utterance on the library's own cache ---- */
+bool single_tc_usable() {
+    Model &m = model();
+    static const bool off = getenv("VB200_NO_TC") != nullptr;
+    return !off && m.inited && m.llm_ready && m.ac_ready && acoustic_tc_ready() && !m.tap_on;
+}
+
+/* (Re)creates the single-utterance context when needed; the code / noise arrays grow on demand. */
+static int one_ready(int frames) {
+    Model &m = model();
+    Batch &t = g_one;
+    if (t.open && t.kv_k == m.kv_k && t.kv_max == m.kv_max && frames <= t.alloc_cap) return bt_weights();
+    const int cap = frames > t.alloc_cap ? frames : t.alloc_cap;
+    return ctx_open(t, true, 1, m.kv_max, cap);
+}
+
+static int one_status(Batch &t) {
+    Model &m = model();
+    m.last_status = t.h_out->status[0];
+    if (m.last_status == 0) return 0;
+    fprintf(stderr, "voxtral_b200: a frame kernel gave up with status %d\n", m.last_status);
+    cudaMemsetAsync(t.tickets, 0, sizeof(unsigned) * VB200_KV_HEADS, m.st);
+    cudaMemsetAsync(t.status, 0, sizeof(int) * 4, m.st);
+    cudaStreamSynchronize(m.st);
+    return -1;
+}
+
+/* tts_llm_forward + tts_acoustic_forward of one frame (voxtral_tts.c:303-318) as one graph
+ * launch between one copy in and one copy out. */
+int single_frame(const float *embed, const float *noise, int pos, float *hidden_out, int *codes, bool chained) {
+    Model &m = model();
+    if (one_ready(0)) return -1;
+    Batch &t = g_one;
+    if (chained && !m.embed_ready) return -1;
+    t.h_in->dyn.pos = pos; t.h_in->dyn.kv_max = m.kv_max; t.h_in->dyn.frame = 0; t.h_in->dyn.done = 0;
+    memcpy(t.h_in->noise, noise, sizeof(float) * A);
+    if (chained) {
+        if (cudaMemcpyAsync(&t.d_in->dyn, &t.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice, m.st) != cudaSuccess ||
+            cudaMemcpyAsync(t.d_in->noise, t.h_in->noise, sizeof(float) * A, cudaMemcpyHostToDevice, m.st) != cudaSuccess)
+            return -1;
+    } else {
+        memcpy(t.h_in->X, embed, sizeof(float) * D);
+        if (cudaMemcpyAsync(t.d_in, t.h_in, sizeof(OneIn), cudaMemcpyHostToDevice, m.st) != cudaSuccess) return -1;
+    }
+    if (m.timing) {
+        flush_launch_time();
+        cudaEventRecord(m.ev0, m.st);
+    }
+    if (launch_variant(t, chained ? 2 : 1)) return -1;
+    if (m.timing) {
+        cudaEventRecord(m.ev1, m.st);
+        m.time_pending = true;
+    }
+    if (cudaMemcpyAsync(t.h_out, t.d_out, sizeof(OneOut), cudaMemcpyDeviceToHost, m.st) != cudaSuccess ||
+        cudaStreamSynchronize(m.st) != cudaSuccess)
+        return -1;
+    flush_launch_time();
+    if (one_status(t)) return -1;
+    memcpy(codes, t.h_out->codes, sizeof(int) * VB200_CODES);
+    if (hidden_out) memcpy(hidden_out, t.h_out->hidden, sizeof(float) * D);
+    return 0;
+}
+
+int single_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames) {
+    Model &m = model();
+    if (!m.embed_ready || one_ready(n_frames)) return -1;
+    Batch &t = g_one;
+    if (t.graph_cap != n_frames) {
+        /* the frame cap is an argument of the captured launches */
+        if (t.exec[0]) { cudaGraphExecDestroy(t.exec[0]); t.exec[0] = nullptr; }
+        if (t.direct_calls[0] > 1) t.direct_calls[0] = 1;
+        t.graph_cap = n_frames;
+    }
+    t.cap = n_frames;
+    t.ac.sd.noise = (size_t)n_frames * A; t.ac.sd.codes_all = (size_t)n_frames * VB200_CODES;
+    t.h_in->dyn.pos = start_pos; t.h_in->dyn.kv_max = m.kv_max; t.h_in->dyn.frame = 0; t.h_in->dyn.done = 0;
+    memcpy(t.h_in->X, first_embed, sizeof(float) * D);
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    if (cudaMemcpy(t.d_in, t.h_in, sizeof(OneIn), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(t.noise_all, noise_all, sizeof(float) * (size_t)n_frames * A, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemset(t.codes_all, 0, sizeof(int) * (size_t)n_frames * VB200_CODES) != cudaSuccess)
+        return -1;
+    t.launched = 0;
+    t.begun = true;
+    return 0;
+}
+
+int single_run(int n) { return ctx_run(g_one, n); }
+
+int single_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms) {
+    Model &m = model();
+    Batch &t = g_one;
+    if (!t.begun) return -1;
+    if (cudaMemcpyAsync(t.h_out, t.d_out, sizeof(OneOut), cudaMemcpyDeviceToHost, m.st) != cudaSuccess ||
+        cudaMemcpyAsync(&t.h_in->dyn, &t.d_in->dyn, sizeof(VbDyn), cudaMemcpyDeviceToHost, m.st) != cudaSuccess ||
+        cudaStreamSynchronize(m.st) != cudaSuccess)
+        return -1;
+    if (device_ms && cudaEventElapsedTime(device_ms, t.e0, t.e1) != cudaSuccess) *device_ms = -1.0f;
+    const int done = t.h_in->dyn.frame;
+    if (frames_done) *frames_done = done;
+    if (hit_end) *hit_end = t.h_in->dyn.done == 2 ? 1 : 0;
+    if (codes_out && done > 0 &&
+        cudaMemcpy(codes_out, t.codes_all, sizeof(int) * (size_t)done * VB200_CODES, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -1;
+    return one_status(t);
+}
 
 } // namespace vb

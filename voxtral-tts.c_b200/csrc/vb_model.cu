@@ -625,6 +625,9 @@ int frame(const float *embed, const float *noise, int pos, float *hidden_out, in
         fprintf(stderr, "voxtral_b200: position %d outside the %d-row cache\n", pos, m.kv_max);
         return -1;
     }
+    /* the whole frame as one graph of tensor-core GEMM launches; the streaming kernel serves
+     * when that path is off or per-layer taps are wanted */
+    if (single_tc_usable()) return single_frame(embed, noise, pos, hidden_out, codes, chained);
     m.h_in->dyn.pos = pos; m.h_in->dyn.kv_max = m.kv_max; m.h_in->dyn.frame = 0; m.h_in->dyn.done = 0;
     memcpy(m.h_in->lat[0], noise, sizeof(float) * A);
     if (chained) {
@@ -691,6 +694,8 @@ int utterance_begin(const float *first_embed, int start_pos, const float *noise_
     Model &m = g_model;
     if (!m.inited || !m.llm_ready || !m.ac_ready || !m.embed_ready) return -1;
     if (n_frames <= 0 || start_pos < 0 || start_pos >= m.kv_max) return -1;
+    m.run_on_tc = single_tc_usable();
+    if (m.run_on_tc) return single_begin(first_embed, start_pos, noise_all, n_frames);
     drop(&m.noise_all);
     drop(&m.codes_all);
     if (dev_alloc(&m.noise_all, (size_t)n_frames * A) || dev_alloc(&m.codes_all, (size_t)n_frames * VB200_CODES))
@@ -727,6 +732,7 @@ int utterance_begin(const float *first_embed, int start_pos, const float *noise_
 /* Queues n more frames; returns without waiting. */
 int utterance_run(int n) {
     Model &m = g_model;
+    if (m.run_on_tc) return single_run(n);
     if (!m.noise_all || n < 0) return -1;
     const bool timing = m.timing;
     m.timing = false;                      /* one event pair around the whole batch instead */
@@ -759,6 +765,11 @@ int utterance_run(int n) {
  * END reports the END frame too (the reference drops it, voxtral_tts.c:307-311). */
 int utterance_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms) {
     Model &m = g_model;
+    if (m.run_on_tc) {
+        m.run_engine_ms = 0.0;
+        m.run_engine_n = 0;
+        return single_end(codes_out, frames_done, hit_end, device_ms);
+    }
     if (!m.noise_all) return -1;
     VB_CHECK(cudaMemcpyAsync(m.h_out, m.d_out, offsetof(DevOut, hidden), cudaMemcpyDeviceToHost, m.st));
     VB_CHECK(cudaMemcpyAsync(&m.h_in->dyn, &m.d_in->dyn, sizeof(VbDyn), cudaMemcpyDeviceToHost, m.st));

@@ -85,6 +85,7 @@ struct Model {
     float *noise_all = nullptr;   /* device-resident run: [frames, 36] */
     int *codes_all = nullptr;     /* [frames, 37] */
     int run_cap = 0, run_launched = 0;
+    bool run_on_tc = false;       /* the current device-resident run uses the tensor-core frame graph */
     std::vector<cudaEvent_t> run_ev;   /* event pairs around the frame-kernel launches of a run */
     int run_ev_used = 0, run_engine_n = 0;
     double run_engine_ms = 0.0;
@@ -130,6 +131,13 @@ int batch_run(int n);
 int batch_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
 int batch_hidden(float *out);
 int batch_launches_per_frame();
+/* one utterance on the library's cache, same launches (vb_batch.cu) */
+bool single_tc_usable();
+int single_frame(const float *embed, const float *noise, int pos, float *hidden_out, int *codes, bool chained);
+int single_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);
+int single_run(int n);
+int single_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
+int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int *launches_per_sweep);
 void batch_close();
 void batch_invalidate();
 void batch_free_all();
