@@ -232,9 +232,31 @@ def cpu_reference(pkg, model, kv_prefix, first_embed, noise, n_frames, budget_s)
             "ms_per_frame": 1000.0 / fps}
 
 
+def micro_gemm(args):
+    """The tensor-core GEMM kernel alone on one generated [n, k] matrix (no model upload): `reps`
+    launches between two CUDA events. Not the headline metric: a small case for profiling and the
+    per-shape table."""
+    pkg = load_package()
+    L = pkg.lib()
+    ms, splits = C.c_float(0.0), C.c_int(0)
+    rc = L.vb200_tc_gemm_probe(args.m, args.n, args.k, 1 if args.swiglu else 0, 0 if args.untiled else 1, args.reps,
+                               C.byref(ms), C.byref(splits))
+    if rc != 0:
+        raise SystemExit(f"vb200_tc_gemm_probe failed ({rc})")
+    peak, src = measured_hbm_peak()
+    us = ms.value * 1000.0 / args.reps
+    gbs = 2.0 * args.n * args.k / (us * 1e-6) / 1e9
+    print(json.dumps({"micro": "gemm", "m": args.m, "k": args.k, "n": args.n, "launches": args.reps,
+                      "epilogue": "swiglu_terms" if args.swiglu else "split_k_partials", "splits": splits.value,
+                      "tiled_weights": not args.untiled, "us_per_launch": us, "weight_bytes": 2 * args.n * args.k,
+                      "achieved_gbs": gbs, "frac_of_peak": gbs / peak, "peak_source": src}))
+
+
 def micro(args):
     """One GEMV op of the frame kernel through tts_cuda_linear_bf16 on device buffers:
     y[m,n] = x[m,k] . W[n,k]^T. Not the headline metric: a small, self-contained case for profiling."""
+    if args.micro == "gemm":
+        return micro_gemm(args)
     pkg = load_package()
     eng = pkg.Engine(kv_cache_max=64)
     L = eng.L
@@ -270,7 +292,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--utterances", type=int, default=8,
                     help="utterances per GPU of the additional lock-step measurement (1 = skip it)")
-    ap.add_argument("--micro", default="", choices=["", "gemv"],
+    ap.add_argument("--swiglu", action="store_true", help="--micro gemm: SwiGLU epilogue instead of split-K partials")
+    ap.add_argument("--untiled", action="store_true", help="--micro gemm: row-major weights instead of the tiled copy")
+    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm"],
                     help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--k", type=int, default=3072)

@@ -80,6 +80,11 @@ void vb200_batch_close(void);
  * (which = 0) or on the open batch (which = 1). Returns the elapsed ms, the weight bytes of
  * one sweep and its launch count. */
 int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, int *launches_per_sweep);
+/* Measurement aid without a model: a generated [N, K] BF16 matrix, M activation rows, `reps`
+ * launches of the tensor-core GEMM between two CUDA events on the default stream (split-K
+ * partial epilogue, or the SwiGLU epilogue when swiglu != 0; tiled != 0: tile-contiguous weight
+ * copy as the frame uses). Returns elapsed ms and the split-K factor chosen. */
+int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, float *ms, int *splits);
 /* 1 when vb200_frame / vb200_utterance_* run as the graph of tensor-core GEMM launches, 0 when
  * they run on the streaming frame kernel (VB200_NO_TC=1, or per-layer taps enabled). */
 int vb200_frame_on_tensor_cores(void);

@@ -7,6 +7,7 @@
 #include "../../include/voxtral_b200_ext.h"
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
+#include "vb_tc.cuh"
 
 #include <stddef.h>
 #include <stdio.h>
@@ -173,6 +174,11 @@ int vb200_batch_launches_per_frame(void) { return batch_launches_per_frame(); }
 void vb200_batch_close(void) { batch_close(); }
 int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, int *launches_per_sweep) {
     return gemm_sweep(which, iters, ms, bytes_per_sweep, launches_per_sweep);
+}
+int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, float *ms, int *splits) {
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    return tc_probe(M, N, K, swiglu ? TC_EPI_SWIGLU_TERMS : TC_EPI_PARTIAL, tiled, reps, n_sm, ms, splits);
 }
 int vb200_frame_on_tensor_cores(void) { return single_tc_usable() ? 1 : 0; }
 

@@ -209,21 +209,45 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     const float4 q4 = *reinterpret_cast<const float4 *>(&qs[hh][4 * lane]);
     float mx = -1e30f, den = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = j0 + ss; j < j1; j += kBtSubsets) {
-        const float4 kv = vb_ldcg4(Kc + (size_t)j * KVD + g * kHD + 4 * lane);
-        const float4 vv = vb_ldcg4(Vc + (size_t)j * KVD + g * kHD + 4 * lane);
-        float d = q4.x * kv.x + q4.y * kv.y + q4.z * kv.z + q4.w * kv.w;
-        d = vb_warp_sum(d) * scale;
-        if (d > mx) {
-            const float corr = expf(mx - d);
-            den = den * corr + 1.0f;
-            o.x = o.x * corr + vv.x; o.y = o.y * corr + vv.y;
-            o.z = o.z * corr + vv.z; o.w = o.w * corr + vv.w;
-            mx = d;
-        } else {
-            const float w = expf(d - mx);
-            den += w;
-            o.x += w * vv.x; o.y += w * vv.y; o.z += w * vv.z; o.w += w * vv.w;
+    /* four keys per pass: their eight loads are in flight together, the running-maximum
+     * update then takes them in key order as the reference does */
+    for (int jb = j0 + ss; jb < j1; jb += 4 * kBtSubsets) {
+        float4 kq[4], vq[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int j = jb + u * kBtSubsets;
+            if (j < j1) {
+                kq[u] = vb_ldcg4(Kc + (size_t)j * KVD + g * kHD + 4 * lane);
+                vq[u] = vb_ldcg4(Vc + (size_t)j * KVD + g * kHD + 4 * lane);
+            } else {
+                kq[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                vq[u] = kq[u];
+            }
+        }
+        float dq[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) dq[u] = q4.x * kq[u].x + q4.y * kq[u].y + q4.z * kq[u].z + q4.w * kq[u].w;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) dq[u] += __shfl_xor_sync(0xffffffffu, dq[u], off);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (jb + u * kBtSubsets >= j1) break;
+            const float d = dq[u] * scale;
+            const float4 vv = vq[u];
+            if (d > mx) {
+                const float corr = expf(mx - d);
+                den = den * corr + 1.0f;
+                o.x = o.x * corr + vv.x; o.y = o.y * corr + vv.y;
+                o.z = o.z * corr + vv.z; o.w = o.w * corr + vv.w;
+                mx = d;
+            } else {
+                const float w = expf(d - mx);
+                den += w;
+                o.x += w * vv.x; o.y += w * vv.y; o.z += w * vv.z; o.w += w * vv.w;
+            }
         }
     }
     *reinterpret_cast<float4 *>(&attn_o[ss][hh][4 * lane]) = o;

@@ -29,6 +29,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <vector>
 
 namespace vb {
 
@@ -188,12 +189,12 @@ VB_DEVINL void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync
 VB_DEVINL void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
 /* ---------------------------------------------------------------- the kernel */
-template <int NB>
+template <int NB, int ST>
 struct TcCfg {
     static constexpr int kStageA = kTcTileN * kTcBlockK * 2;        /* 16 KB */
     static constexpr int kTermB = NB * kTcBlockK * 2;               /* one BF16 term of the activations */
     static constexpr int kStage = kStageA + kTcTerms * kTermB;
-    static constexpr int kStages = NB == 16 ? 5 : NB == 64 ? 5 : 2;   /* NB=16: 110 KB, two CTAs fit one SM so that a GEMM can start under the tail of the previous one */
+    static constexpr int kStages = ST;   /* NB=16: several CTAs fit one SM, so the next GEMMs of the stream fetch their first weight tiles under the tail of the running one */
     /* The three BF16 terms of the activations lie one after another in a stage, so for
      * NB <= 64 they form ONE B operand of 3*NB rows: a single MMA per 16-wide K step writes the
      * three partial products to separate TMEM column groups (summed in the epilogue) instead of
@@ -203,6 +204,7 @@ struct TcCfg {
     static constexpr int kAccCols = kFusedTerms ? kTcTerms * NB : NB;
     static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : 256;
     static constexpr int kSmemBytes = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */ + 4 * NB;
+    static_assert(kSmemBytes <= 232448, "over the 227 KB a CTA may use");
 };
 
 constexpr int kTcThreads = 192;
@@ -221,11 +223,11 @@ struct TcKernelArgs {
     int *status;
 };
 
-template <int NB>
+template <int NB, int ST>
 __global__ void __launch_bounds__(kTcThreads, 1)
 vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                   const TcKernelArgs ka) {
-    using Cfg = TcCfg<NB>;
+    using Cfg = TcCfg<NB, ST>;
     const int N = ka.N, K = ka.K, M = ka.M, rows_pad = ka.rows_pad, ld_out = ka.ld_out, splits = ka.splits,
               epi = ka.epi;
     float *const out = ka.out;
@@ -417,18 +419,20 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     }
 }
 
-template <int NB>
+template <int NB, int ST>
 static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, cudaStream_t st) {
-    using Cfg = TcCfg<NB>;
+    using Cfg = TcCfg<NB, ST>;
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::kSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::kSmemBytes) != cudaSuccess) {
+            cudaGetLastError();
             return -1;
+        }
         attr = true;
     }
     const int tiles = (w.N + kTcTileN - 1) / kTcTileN;
-    return launch_pdl(vb_tc_gemm_kernel<NB>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
+    return launch_pdl(vb_tc_gemm_kernel<NB, ST>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
                       w.map, a.map, ka) == cudaSuccess
                ? 0
                : -1;
@@ -446,9 +450,17 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
     ka.epi = g.epi; ka.out = g.out; ka.bias = g.bias; ka.ssq = g.ssq; ka.ssq_chunks = g.ssq_chunks; ka.eps = g.eps;
     ka.out_terms = g.out_terms; ka.out_rows_pad = g.out_rows_pad; ka.status = g.status;
     switch (a.rows_pad) {
-    case 16: return launch_tc<16>(w, a, ka, st);
-    case 64: return launch_tc<64>(w, a, ka, st);
-    case 256: return launch_tc<256>(w, a, ka, st);
+    case 16: {
+        /* Pipeline depth of the 16-row kernel. Measured on the frame loop: 3 stages 3.74 ms per
+         * frame, 4: 3.46, 5: 3.40, 6: 3.36, 8: 3.39, 10: 3.48. With 6 (136 KB) one CTA fits an SM. */
+        static const int st16 = getenv("VB200_TC_STAGES") ? atoi(getenv("VB200_TC_STAGES")) : 6;
+        if (st16 == 4) return launch_tc<16, 4>(w, a, ka, st);
+        if (st16 == 5) return launch_tc<16, 5>(w, a, ka, st);
+        if (st16 == 8) return launch_tc<16, 8>(w, a, ka, st);
+        return launch_tc<16, 6>(w, a, ka, st);
+    }
+    case 64: return launch_tc<64, 5>(w, a, ka, st);
+    case 256: return launch_tc<256, 2>(w, a, ka, st);
     default: return -1;
     }
 }
@@ -472,10 +484,16 @@ __global__ void vb_tc_prepare_kernel(uint16_t *buf, int rows_pad, int K, const f
     if (c < K) {
         float4 v;
         if (partials) {
+            /* all partial loads in flight together, then the fixed-order sum */
+            float4 t[kTcMaxSplits];
+#pragma unroll
+            for (int p = 0; p < kTcMaxSplits; p++)
+                t[p] = p < n_part ? __ldcg(reinterpret_cast<const float4 *>(partials + (size_t)p * part_stride + (size_t)m * K + c))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
             v = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int p = 0; p < n_part; p++) {
-                const float4 t = *reinterpret_cast<const float4 *>(partials + (size_t)p * part_stride + (size_t)m * K + c);
-                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+#pragma unroll
+            for (int p = 0; p < kTcMaxSplits; p++) {
+                if (p < n_part) { v.x += t[p].x; v.y += t[p].y; v.z += t[p].z; v.w += t[p].w; }
             }
             if (residual) {
                 const float4 r = *reinterpret_cast<const float4 *>(residual + (size_t)m * ldx + c);
@@ -536,6 +554,80 @@ void tc_reduce(float *y, const float *partials, int n_part, size_t stride, size_
                cudaStream_t st) {
     if (count == 0) return;
     vb_tc_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(y, partials, n_part, stride, count, bias, N);
+}
+
+/* ---------------------------------------------------------------- stand-alone probe */
+__global__ void vb_tc_fill_kernel(uint16_t *p, size_t n, uint32_t seed) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    /* small BF16 values of both signs: 0x3c00 | 6 hashed mantissa bits, hashed sign */
+    uint32_t h = (uint32_t)i * 2654435761u + seed;
+    h ^= h >> 15;
+    p[i] = (uint16_t)(0x3c00u | (h & 0x3fu) | ((h & 0x40u) << 9));
+}
+
+/* One weight matrix [N, K] of generated values, M activation rows, `reps` launches of the GEMM
+ * between two events on the default stream. Needs no model: a measurement and profiling aid
+ * with a small memory footprint. epi: TC_EPI_PARTIAL (split-K as the frame uses it) or
+ * TC_EPI_SWIGLU_TERMS; tiled: tile-contiguous weight copy as the frame uses it. */
+int tc_probe(int M, int N, int K, int epi, int tiled, int reps, int n_sm, float *ms_out, int *splits_out) {
+    if (tc_init() || M < 1 || reps < 1 || (K % kTcBlockK) != 0) return -1;
+    const int rp = tc_rows_pad(M);
+    if (!rp) return -1;
+    /* enough copies of the matrix that successive launches cannot find their weights in L2 */
+    const int copies = (int)((size_t)512 * 1024 * 1024 / ((size_t)N * K * 2)) + 1;
+    std::vector<uint16_t *> Wc(copies, nullptr);
+    std::vector<TcWeight> wc(copies);
+    uint16_t *W = nullptr, *terms = nullptr, *out_terms = nullptr;
+    float *out = nullptr;
+    int *status = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = -1;
+    const size_t wn = (size_t)N * K;
+    const int splits = epi == TC_EPI_PARTIAL ? tc_pick_splits(N, K, n_sm) : 1;
+    do {
+        if (cudaMalloc(&W, wn * 2) != cudaSuccess || cudaMalloc(&terms, tc_acts_bytes(rp, K)) != cudaSuccess ||
+            cudaMalloc(&out, sizeof(float) * (size_t)kTcMaxSplits * M * N) != cudaSuccess ||
+            cudaMalloc(&out_terms, tc_acts_bytes(rp, N / 2 + 64)) != cudaSuccess ||
+            cudaMalloc(&status, sizeof(int)) != cudaSuccess)
+            break;
+        cudaMemset(status, 0, sizeof(int));
+        vb_tc_fill_kernel<<<(unsigned)((wn + 255) / 256), 256>>>(W, wn, 1u);
+        const size_t tn = tc_acts_bytes(rp, K) / 2;
+        vb_tc_fill_kernel<<<(unsigned)((tn + 255) / 256), 256>>>(terms, tn, 2u);
+        bool wok = true;
+        for (int c = 0; c < copies && wok; c++) {
+            const size_t bytes = tiled ? tc_tiled_bytes(N, K) : wn * 2;
+            wok = cudaMalloc(&Wc[c], bytes) == cudaSuccess;
+            if (wok && tiled) wok = tc_weight_tiled(&wc[c], W, N, K, Wc[c], 0) == 0;
+            else if (wok) wok = cudaMemcpy(Wc[c], W, bytes, cudaMemcpyDeviceToDevice) == cudaSuccess && tc_weight(&wc[c], Wc[c], N, K) == 0;
+        }
+        if (!wok) break;
+        TcActs a;
+        if (tc_acts(&a, terms, rp, K)) break;
+        TcGemm g;
+        g.M = M; g.splits = splits; g.epi = epi; g.out = out; g.ld_out = epi == TC_EPI_PARTIAL ? N : N / 2;
+        g.out_terms = out_terms; g.out_rows_pad = rp; g.status = status;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
+        bool ok = true;
+        for (int i = 0; i < 3 && ok; i++) ok = tc_gemm(wc[i % copies], a, g, 0) == 0;
+        cudaEventRecord(e0, 0);
+        for (int i = 0; i < reps && ok; i++) ok = tc_gemm(wc[(3 + i) % copies], a, g, 0) == 0;
+        cudaEventRecord(e1, 0);
+        if (!ok || cudaDeviceSynchronize() != cudaSuccess) break;
+        int st = 0;
+        cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+        if (st) break;
+        if (ms_out) cudaEventElapsedTime(ms_out, e0, e1);
+        if (splits_out) *splits_out = splits;
+        rc = 0;
+    } while (0);
+    cudaGetLastError();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    for (uint16_t *p : Wc) cudaFree(p);
+    cudaFree(W); cudaFree(terms); cudaFree(out); cudaFree(out_terms); cudaFree(status);
+    return rc;
 }
 
 } // namespace vb

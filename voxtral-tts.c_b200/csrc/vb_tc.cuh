@@ -88,6 +88,8 @@ int tc_gemm(const TcWeight &w, const TcActs &acts, const TcGemm &g, cudaStream_t
 void tc_reduce(float *y, const float *partials, int n_part, size_t stride, size_t count, const float *bias, int N,
                cudaStream_t st);
 
+int tc_probe(int M, int N, int K, int epi, int tiled, int reps, int n_sm, float *ms_out, int *splits_out);
+
 /* Launch with the programmatic-stream-serialization attribute: the kernel may begin (weight
  * prefetch, barrier set-up, TMEM allocation) while its predecessor in the stream is still
  * running; whatever depends on the predecessor sits behind griddepcontrol.wait in the kernel.
