@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json config 4, "full autoregressive utterance"): a 256-row prompt is
+Workload (configuration 4 of the benchmark description, "full autoregressive utterance"): a 256-row prompt is
 prefilled, then frames are generated one after another; one step = one audio frame = one
 26-layer decoder step at a growing cache (256, 257, ...) + one acoustic frame (semantic
 argmax, 7 Euler steps x 2 guidance branches, FSQ) + re-embedding of the 37 codes. Weights are
@@ -504,7 +504,7 @@ def main():
         batched = {"utterances_per_gpu": Bu, "value": bval, "unit": "frames/s", "steps": Kb, "ms_per_step": bmax / Kb,
                    "algorithmic_bytes_per_step": step_bytes,
                    "hbm_frac": step_bytes / (bmax / Kb / 1000.0) / 1e9 / peak,
-                   "workload": "BASELINE config 5 per GPU: 8 utterances, 256-row prompts, lock-step frames"}
+                   "workload": "config 5 per GPU: 8 utterances, 256-row prompts, lock-step frames"}
 
     if rank != 0:
         eng.close()

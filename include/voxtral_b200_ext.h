@@ -85,6 +85,16 @@ int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, i
  * partial epilogue, or the SwiGLU epilogue when swiglu != 0; tiled != 0: tile-contiguous weight
  * copy as the frame uses). Returns elapsed ms and the split-K factor chosen. */
 int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, float *ms, int *splits);
+/* y[M,N] = x[M,K] . W[N,K]^T (swiglu != 0: rows interleaved (gate, up), y[M, N/2] =
+ * silu(gate) * up) on DEVICE buffers through a one-op program of the persistent tensor-core
+ * kernel; M <= 10, K a multiple of 64. The first launch is followed by `reps` timed ones
+ * (elapsed ms in *ms). A check and measurement aid. */
+int vb200_ptc_linear(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N, int swiglu, int reps,
+                     float *ms);
+/* Measurement aid: the decoder's 104 layer GEMMs as one launch of the persistent tensor-core
+ * kernel, `iters` launches between two CUDA events (elapsed ms in *ms). Needs the decoder
+ * weights uploaded. */
+int vb200_ptc_decoder_sweep(int iters, float *ms);
 /* 1 when vb200_frame / vb200_utterance_* run as the graph of tensor-core GEMM launches, 0 when
  * they run on the streaming frame kernel (VB200_NO_TC=1, or per-layer taps enabled). */
 int vb200_frame_on_tensor_cores(void);

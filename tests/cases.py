@@ -1,6 +1,6 @@
 """Seeded inputs of the parity cases, shared by the golden generator and the tests.
 
-They follow BASELINE.json's configs: config 1 = one decoder step with a cache
+They follow the benchmark configurations: config 1 = one decoder step with a cache
 pre-filled with 64 positions of N(0,1); config 2 = one acoustic frame on a
 N(0,1) hidden state."""
 import numpy as np

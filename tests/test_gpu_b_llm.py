@@ -1,6 +1,6 @@
 """GPU parity of the decoder step (tts_cuda_llm_forward) against the CPU oracle and the golden
-fixtures of the reference CPU build: BASELINE config 1 (cache pre-filled with 64 positions).
-Tolerance from the north star: every layer's residual stream within 2e-3 relative L2."""
+fixtures of the reference CPU build: benchmark configuration 1 (cache pre-filled with 64 positions).
+Tolerance of the hot path: every layer's residual stream within 2e-3 relative L2."""
 import os
 
 import numpy as np

@@ -1,6 +1,6 @@
 """GPU parity of the acoustic transformer: tts_cuda_predict_velocity (one pass) and the fused
 frame (semantic argmax, 7 Euler steps x 2 guidance branches, FSQ) against the CPU oracle and
-the golden fixtures: BASELINE config 2. Bars from the north star: identical semantic argmax,
+the golden fixtures: benchmark configuration 2. Bars: identical semantic argmax,
 acoustic codes identical for >= 99 % of frames."""
 import os
 

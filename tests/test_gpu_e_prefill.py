@@ -1,5 +1,5 @@
 """GPU parity of the multi-token prefill (tts_cuda_llm_prefill): cache rows against the CPU
-oracle on a short prompt, and size-independent properties at BASELINE config 3's full size
+oracle on a short prompt, and size-independent properties at benchmark configuration 3's full size
 (256 rows: 224 voice-embedding rows ~N(0,0.5) followed by 32 token rows)."""
 import numpy as np
 import pytest

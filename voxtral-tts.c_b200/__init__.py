@@ -98,6 +98,8 @@ def lib():
         "vb200_batch_close": (None, []),
         "vb200_gemm_sweep": (C.c_int, [C.c_int, C.c_int, f32p, C.POINTER(C.c_double), i32p]),
         "vb200_frame_on_tensor_cores": (C.c_int, []),
+        "vb200_ptc_decoder_sweep": (C.c_int, [C.c_int, f32p]),
+        "vb200_ptc_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p]),
         "vb200_tc_gemm_probe": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]),
         "vb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
         "vb200_utterance_engine_ms": (C.c_double, [i32p]),

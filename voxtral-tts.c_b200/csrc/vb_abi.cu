@@ -8,6 +8,7 @@
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
 #include "vb_tc.cuh"
+#include "vb_ptc.cuh"
 
 #include <stddef.h>
 #include <stdio.h>
@@ -180,6 +181,11 @@ int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, fl
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     return tc_probe(M, N, K, swiglu ? TC_EPI_SWIGLU_TERMS : TC_EPI_PARTIAL, tiled, reps, n_sm, ms, splits);
 }
+int vb200_ptc_linear(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N, int swiglu, int reps,
+                     float *ms) {
+    return ptc_linear(d_y, d_x, d_W, M, K, N, swiglu, reps, ms);
+}
+int vb200_ptc_decoder_sweep(int iters, float *ms) { return ptc_decoder_sweep(iters, ms); }
 int vb200_frame_on_tensor_cores(void) { return single_tc_usable() ? 1 : 0; }
 
 double vb200_utterance_engine_ms(int *launches) {

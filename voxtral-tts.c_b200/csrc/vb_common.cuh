@@ -88,6 +88,12 @@ VB_DEVINL unsigned vb_atomic_add_release_gpu(unsigned *p, unsigned v) {
     return old;
 }
 
+VB_DEVINL unsigned vb_atomic_add_acq_rel_gpu(unsigned *p, unsigned v) {
+    unsigned old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
 VB_DEVINL unsigned vb_ld_acquire_gpu(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
