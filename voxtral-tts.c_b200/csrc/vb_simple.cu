@@ -124,24 +124,46 @@ __global__ void attention_rows_kernel(float *out, const float *Q, const float *K
 #pragma unroll
     for (int i = 0; i < DPL; i++) { q[i] = Q[(size_t)row * ldq + h * head_dim + lane + 32 * i]; o[i] = 0.0f; }
     float mx = -1e30f, den = 0.0f;
-    for (int j = 0; j < limit; j++) {
-        const float *kr = K + (size_t)j * ldk + kvh * head_dim;
-        const float *vr = V + (size_t)j * ldk + kvh * head_dim;
-        float d = 0.0f;
+    /* four keys per pass: their loads and the four warp reductions overlap; the running
+     * maximum then takes the keys in order, as the reference does */
+    for (int jb = 0; jb < limit; jb += 4) {
+        float kq[4][DPL], vq[4][DPL], dq[4];
 #pragma unroll
-        for (int i = 0; i < DPL; i++) d += q[i] * kr[lane + 32 * i];
-        d = vb_warp_sum(d) * scale;
-        if (d > mx) {
-            const float corr = expf(mx - d);
-            den = den * corr + 1.0f;
+        for (int u = 0; u < 4; u++) {
+            const int j = jb + u < limit ? jb + u : limit - 1;
+            const float *kr = K + (size_t)j * ldk + kvh * head_dim;
+            const float *vr = V + (size_t)j * ldk + kvh * head_dim;
 #pragma unroll
-            for (int i = 0; i < DPL; i++) o[i] = o[i] * corr + vr[lane + 32 * i];
-            mx = d;
-        } else {
-            const float w = expf(d - mx);
-            den += w;
+            for (int i = 0; i < DPL; i++) { kq[u][i] = kr[lane + 32 * i]; vq[u][i] = vr[lane + 32 * i]; }
+        }
 #pragma unroll
-            for (int i = 0; i < DPL; i++) o[i] += w * vr[lane + 32 * i];
+        for (int u = 0; u < 4; u++) {
+            float d = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) d += q[i] * kq[u][i];
+            dq[u] = d;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) dq[u] += __shfl_xor_sync(0xffffffffu, dq[u], off);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (jb + u >= limit) break;
+            const float d = dq[u] * scale;
+            if (d > mx) {
+                const float corr = expf(mx - d);
+                den = den * corr + 1.0f;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) o[i] = o[i] * corr + vq[u][i];
+                mx = d;
+            } else {
+                const float w = expf(d - mx);
+                den += w;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) o[i] += w * vq[u][i];
+            }
         }
     }
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
