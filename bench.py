@@ -63,9 +63,10 @@ def utterance_seeds(rank):
     return {"prompt": 100 + rank, "noise": 1000 + rank}
 
 
-def aggregate(local_ms, frames_per_rank, dist=None, device="cuda"):
+def aggregate(local_ms, frames_per_rank, dist=None, device="cuda", shared=False):
     """Whole-job frames/s: every rank ran frames_per_rank frames in local_ms of device time; the
-    job took the slowest rank's time. Returns (frames_per_s, max_ms)."""
+    job took the slowest rank's time. shared: all ranks worked on the SAME frames (tensor
+    parallelism), so they count once. Returns (frames_per_s, max_ms)."""
     import torch
     t = torch.tensor([float(local_ms)], dtype=torch.float64, device=device)
     world = 1
@@ -73,7 +74,7 @@ def aggregate(local_ms, frames_per_rank, dist=None, device="cuda"):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         world = dist.get_world_size()
     max_ms = float(t.item())
-    return world * frames_per_rank / (max_ms / 1000.0), max_ms
+    return (1 if shared else world) * frames_per_rank / (max_ms / 1000.0), max_ms
 
 
 def frame_bytes(pos):
@@ -312,6 +313,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="frames of the host-ABI measurement (default: min(steps, 64))")
     ap.add_argument("--cpu-budget", type=float, default=25.0, help="seconds of CPU-baseline frames")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp", action="store_true",
+                    help="with N > 1 ranks: ONE utterance, the decoder tensor-parallel over the N GPUs (strong scaling) "
+                         "instead of one utterance per GPU")
     ap.add_argument("--utterances", type=int, default=8,
                     help="utterances per GPU of the additional lock-step measurement (1 = skip it)")
     ap.add_argument("--swiglu", action="store_true", help="--micro gemm: SwiGLU epilogue instead of split-K partials")
@@ -385,7 +389,18 @@ def main():
     eng.upload(model, decoder=True, acoustic=True, audio_table=True)
     eng.L.vb200_set_option(b"ignore_end", 1)
 
-    seeds = utterance_seeds(rank)
+    tp = bool(args.tp and world > 1)
+    if tp:
+        # every rank maps the others' exchange arenas (CUDA IPC handles gathered over the process group)
+        handle = (C.c_ubyte * 64)()
+        assert eng.L.vb200_tp_arena(rank, world, handle) == 0, "tensor-parallel arena"
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle))
+        assert eng.L.vb200_tp_connect(b"".join(handles)) == 0, "tensor-parallel connect"
+        barrier()
+        config["parallelism"] = f"tp{world}"
+        config["utterances_per_gpu"] = f"1 utterance over {world} GPUs"
+    seeds = utterance_seeds(0 if tp else rank)               # tensor parallelism: all ranks decode the same utterance
     rows = prompt_rows(pkg, model, seeds["prompt"])
     eng.prefill(rows, 0)
     first = model.token_rows([24])[0]                      # embed(AUDIO), voxtral_tts.c:295
@@ -409,7 +424,7 @@ def main():
     assert Lb.vb200_utterance_end(codes.ctypes.data, C.byref(done), C.byref(end), C.byref(ms)) == 0
     if done.value != W + K:
         raise SystemExit(f"device loop ran {done.value} of {W + K} frames (status {Lb.vb200_last_status()})")
-    value, total_ms = aggregate(ms.value, K, dist)
+    value, total_ms = aggregate(ms.value, K, dist, shared=tp)
 
     # ---- e2e: one host-facing call per frame, re-embedding on the host ------------------------
     Ke = args.e2e_steps or min(K, 64)
@@ -438,7 +453,7 @@ def main():
         e = (table[offs + c].astype(np.uint32) << 16).view(np.float32).sum(axis=0, dtype=np.float32)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
-    e2e_value, _ = aggregate(e2e_s * 1000.0, Ke, dist)
+    e2e_value, _ = aggregate(e2e_s * 1000.0, Ke, dist, shared=tp)
 
     # ---- roofline of the dominant kernel --------------------------------------------------------
     peak, peak_src = measured_hbm_peak()
@@ -507,7 +522,7 @@ def main():
 
     # ---- several utterances per GPU in lock step (weights read once per frame for all) -----------
     batched = None
-    if on_tc and args.utterances > 1:
+    if on_tc and args.utterances > 1 and not tp:
         Bu = args.utterances
         Kb, Wb = min(K, 64), min(W, 5)
         cap = Wb + Kb
@@ -537,6 +552,8 @@ def main():
                    "hbm_frac": step_bytes / (bmax / Kb / 1000.0) / 1e9 / peak,
                    "workload": "config 5 per GPU: 8 utterances, 256-row prompts, lock-step frames"}
 
+    if tp:
+        barrier()                                            # nobody unmaps an arena a peer may still write to
     if rank != 0:
         eng.close()
         if dist is not None:
@@ -552,7 +569,7 @@ def main():
     eng.close()
 
     line = {"metric": "frames_per_s", "value": value, "unit": "frames/s", "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
+            "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
             "vs_baseline": None, "dtype": "f32 (BF16 weights, fp32 activations and accumulation)",
             "data": "synthetic", "config": config, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "frames/s", "steps": Ke,
@@ -561,7 +578,8 @@ def main():
             "batched": batched,
             "utterance": {"prefill_rows": PROMPT_ROWS, "prefill_ms": min(prefill_ms),
                           "first_frame_after_ms": min(prefill_ms) + 1000.0 / e2e_value,
-                          "frames": 212, "total_ms_at_measured_rates": min(prefill_ms) + 212 * 1000.0 * world / e2e_value,
+                          "frames": 212,
+                          "total_ms_at_measured_rates": min(prefill_ms) + 212 * 1000.0 * (1 if tp else world) / e2e_value,
                           "note": "tts_cuda_llm_prefill with host rows (wall clock, synchronous), then "
                                   "vb200_frame per frame; 212 frames = 16.96 s of audio at 12.5 frames/s"}}
     emit(line)

@@ -95,6 +95,24 @@ int vb200_ptc_linear(float *d_y, const float *d_x, const uint16_t *d_W, int M, i
  * kernel, `iters` launches between two CUDA events (elapsed ms in *ms). Needs the decoder
  * weights uploaded. */
 int vb200_ptc_decoder_sweep(int iters, float *ms);
+/* Tensor parallelism over the GPUs of one node, one process per GPU (no counterpart in the
+ * reference, which is single-GPU: voxtral_tts_cuda.cu:103). Every rank uploads all weights and
+ * makes the same vb200_frame / vb200_utterance_* calls with the same inputs; each decoder-layer
+ * GEMM then covers only the rank's slice of output tiles and stores its results into every
+ * rank's buffers over NVLink, ordered by per-site sequence flags (bounded waits).
+ *   arena:   after tts_cuda_init; allocates the exchange arena, returns its CUDA IPC handle
+ *            (64 bytes). world must divide 24 (1, 2, 3, 4, 6, 8).
+ *   connect: handles = world x 64 bytes, rank order, gathered by the caller (e.g. an
+ *            all-gather over the launcher's process group); maps the peers' arenas. The
+ *            caller puts a host barrier between connect and the first frame.
+ *   close:   back to single-GPU launches. */
+int vb200_tp_arena(int rank, int world, void *handle_out64);
+int vb200_tp_connect(const void *handles);
+void vb200_tp_close(void);
+/* Host arithmetic only: the slices rank `rank` of `world` computes. out9 = first tile and tile
+ * count (tiles of 128 output rows) of the QKV, O/down and gate/up GEMMs, then the split-K
+ * factors of QKV, O and down. -1 when world does not divide the tile counts. */
+int vb200_tp_plan(int rank, int world, int n_sm, int *out9);
 /* 1 when vb200_frame / vb200_utterance_* run as the graph of tensor-core GEMM launches, 0 when
  * they run on the streaming frame kernel (VB200_NO_TC=1, or per-layer taps enabled). */
 int vb200_frame_on_tensor_cores(void);

@@ -76,3 +76,28 @@ def test_synth_distribution(pkg):
 
 KNOWN_BF16 = [15464, 48249, 48069, 15246, 15483, 48292]
 KNOWN_F32_BITS = [1060438062, 3208829810, 3197773657, 1046328391, 1061402919, 3212802750]
+
+
+def test_tensor_parallel_slices_tile_every_matrix(pkg):
+    """The tile slices of all ranks partition the QKV (48 tiles), O / down (24) and gate/up (144)
+    GEMMs exactly, for every world size that divides them; others are refused."""
+    import ctypes as C
+    L = pkg.lib()
+    for world in (1, 2, 3, 4, 6, 8):
+        seen = [set(), set(), set()]
+        for rank in range(world):
+            out = (C.c_int * 9)()
+            assert L.vb200_tp_plan(rank, world, 148, out) == 0
+            for i, total in enumerate((48, 24, 144)):
+                t0, n = out[2 * i], out[2 * i + 1]
+                assert n == total // world
+                tiles = set(range(t0, t0 + n))
+                assert not (tiles & seen[i])
+                seen[i] |= tiles
+            assert 1 <= out[6] <= 8 and 1 <= out[7] <= 8 and 1 <= out[8] <= 8
+            assert out[1] * out[6] <= 148 and out[3] * out[7] <= 148      # one wave of CTAs
+        assert [len(s) for s in seen] == [48, 24, 144]
+    out = (C.c_int * 9)()
+    for world in (5, 7, 9, 0):
+        assert L.vb200_tp_plan(0, world, 148, out) == -1
+    assert L.vb200_tp_plan(2, 2, 148, out) == -1

@@ -186,6 +186,10 @@ int vb200_ptc_linear(float *d_y, const float *d_x, const uint16_t *d_W, int M, i
     return ptc_linear(d_y, d_x, d_W, M, K, N, swiglu, reps, ms);
 }
 int vb200_ptc_decoder_sweep(int iters, float *ms) { return ptc_decoder_sweep(iters, ms); }
+int vb200_tp_arena(int rank, int world, void *handle_out64) { return tp_arena(rank, world, handle_out64); }
+int vb200_tp_connect(const void *handles) { return tp_connect(handles); }
+void vb200_tp_close(void) { tp_close(); }
+int vb200_tp_plan(int rank, int world, int n_sm, int *out9) { return tp_plan(rank, world, n_sm, out9); }
 int vb200_frame_on_tensor_cores(void) { return single_tc_usable() ? 1 : 0; }
 
 double vb200_utterance_engine_ms(int *launches) {

@@ -17,6 +17,7 @@
 #include "vb_acoustic_tc.cuh"
 #include "vb_common.cuh"
 #include "vb_ptc.cuh"
+#include "vb_umma.cuh"
 
 #include <math.h>
 #include <stdio.h>
@@ -88,6 +89,8 @@ struct Batch {
     TcActs aD, aQ, aH;
     uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
     float *part = nullptr, *ssq = nullptr, *logit_part = nullptr;
+    float *part_qkv = nullptr, *part_wo = nullptr, *part_w2 = nullptr;   /* = part, or the tensor-parallel arena's */
+    bool tp = false;                            /* this context runs tensor-parallel */
     float *attn_scratch = nullptr;
     unsigned *tickets = nullptr;
     AcBuffers ac;
@@ -98,6 +101,86 @@ struct Batch {
 };
 static Batch g_bt;    /* vb200_batch_*: up to 8 utterances, own cache slabs */
 static Batch g_one;   /* the single-utterance calls on the library's cache */
+
+/* Tensor parallelism over the GPUs of one node, one process per GPU (single-utterance calls).
+ * Every rank holds all weights and runs the same launches, but each GEMM of a decoder or
+ * acoustic layer covers only this rank's slice of output tiles and stores its results into
+ * every rank's buffers over NVLink; the small kernels between the GEMMs run redundantly on
+ * identical data, so the residual stream and the caches stay bit-identical on all ranks. The
+ * exchanged buffers (split-K partials per GEMM type, the SwiGLU terms) and the flag words lie
+ * in one arena per rank at identical offsets; peers map it through CUDA IPC. */
+enum TpSlot { TP_QKV = 0, TP_WO = 1, TP_W13 = 2, TP_W2 = 3 };
+struct TpSet {                 /* exchanged buffers of one context (decoder rows / acoustic rows) */
+    size_t part[4];            /* byte offsets in the arena: partials of QKV, O, (unused), down */
+    size_t bH;                 /* SwiGLU terms [3][16][9216] */
+};
+struct Tp {
+    bool on = false;
+    int rank = 0, world = 1;
+    unsigned char *arena = nullptr;
+    unsigned char *peer[kTpMaxRanks] = {};
+    size_t bytes = 0, off_flags = 0;
+    TpSet ll, ac;
+    unsigned *epoch = nullptr, *tickets = nullptr;   /* local words */
+};
+static Tp g_tp;
+constexpr int kTpRowsLl = 1, kTpRowsAc = 6;
+
+static void tp_layout(Tp &t) {
+    size_t o = 4096;            /* flags: 8 slots x 8 ranks */
+    t.off_flags = 0;
+    auto take = [&](size_t bytes) { const size_t at = o; o += (bytes + 1023) & ~(size_t)1023; return at; };
+    for (int c = 0; c < 2; c++) {
+        TpSet &st = c == 0 ? t.ll : t.ac;
+        const size_t rows = c == 0 ? kTpRowsLl : kTpRowsAc;
+        st.part[TP_QKV] = take(sizeof(float) * kTcMaxSplits * rows * QKV);
+        st.part[TP_WO] = take(sizeof(float) * kTcMaxSplits * rows * D);
+        st.part[TP_W13] = 0;
+        st.part[TP_W2] = take(sizeof(float) * kTcMaxSplits * rows * D);
+        st.bH = take(tc_acts_bytes(16, HID));
+    }
+    t.bytes = o;
+}
+
+/* Slice of `tiles` output tiles this rank computes. */
+static void tp_slice(int tiles, int *t0, int *n) {
+    const int a = (int)((long long)tiles * g_tp.rank / g_tp.world), b = (int)((long long)tiles * (g_tp.rank + 1) / g_tp.world);
+    *t0 = a;
+    *n = b - a;
+}
+
+/* Producer side of visit `visit` (1-based, of visits_per_frame per frame) of an exchanged buffer. */
+static TcPush tp_push(int ctx, int slot, int visits_per_frame, int visit) {
+    TcPush p;
+    if (!g_tp.on) return p;
+    p.n_dst = g_tp.world;
+    /* destination 0 is the local copy (the kernel's plain store); the others follow */
+    int d = 1;
+    p.flag[0] = (unsigned *)(g_tp.arena + g_tp.off_flags) + (ctx * 4 + slot) * kTpMaxRanks + g_tp.rank;
+    for (int r = 0; r < g_tp.world; r++) {
+        if (r == g_tp.rank) continue;
+        p.dst_off[d] = (long long)(g_tp.peer[r] - g_tp.arena);
+        p.flag[d] = (unsigned *)(g_tp.peer[r] + g_tp.off_flags) + (ctx * 4 + slot) * kTpMaxRanks + g_tp.rank;
+        d++;
+    }
+    p.ticket = g_tp.tickets + (ctx * 4 + slot);
+    p.epoch = g_tp.epoch;
+    p.visits_per_frame = visits_per_frame; p.visit = visit;
+    return p;
+}
+
+static TcWait tp_wait_for(int ctx, int slot, int visits_per_frame, int visit, int *status) {
+    TcWait w;
+    if (!g_tp.on) return w;
+    w.flags = (const unsigned *)(g_tp.arena + g_tp.off_flags) + (ctx * 4 + slot) * kTpMaxRanks;
+    w.n = g_tp.world;
+    w.epoch = g_tp.epoch;
+    w.visits_per_frame = visits_per_frame; w.visit = visit;
+    w.status = status;
+    return w;
+}
+
+__global__ void tp_epoch_kernel(unsigned *epoch) { *epoch += 1u; }
 
 /* ------------------------------------------------------------------ kernels */
 
@@ -133,7 +216,7 @@ __global__ void bt_embed_kernel(float *X, const uint16_t *table, const int *code
 __global__ void __launch_bounds__(kBtAttnThreads)
 bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, size_t part_stride, float *kv_k,
                float *kv_v, size_t slab, int layer, const VbDyn *dyn, float scale, float theta, float *scratch,
-               unsigned *tickets, int *status) {
+               unsigned *tickets, int *status, const TcWait wait) {
     __shared__ float cs[kHD];
     __shared__ __align__(16) float qraw[kGroup * kHD];
     __shared__ float kraw[kHD], vraw[kHD];
@@ -143,6 +226,10 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     __shared__ int last_flag;
     pdl_launch_dependents();
     pdl_wait();
+    if (wait.n > 0) {   /* tensor parallelism: the QKV partials come from every rank */
+        if (threadIdx.x == 0) tp_wait(wait);
+        __syncthreads();
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int max_s = gridDim.x, G = gridDim.y;
@@ -312,10 +399,14 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
  * head GEMMs. grid = B, 1024 threads. */
 __global__ void __launch_bounds__(1024)
 bt_final_kernel(float *hidden, uint16_t *terms, int rows_pad, const float *X, const float *part, int n_part,
-                size_t part_stride, const float *gain, float eps) {
+                size_t part_stride, const float *gain, float eps, const TcWait wait) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
+    if (wait.n > 0) {
+        if (threadIdx.x == 0) tp_wait(wait);
+        __syncthreads();
+    }
     const int b = blockIdx.x, tid = threadIdx.x;
     float v[3];
     float ss = 0.0f;
@@ -455,11 +546,86 @@ void batch_invalidate() {
     g_w.ready = false;
 }
 
+static void ctx_close(Batch &t);
 void batch_close() { ctx_close(g_bt); }
+
+/* ---- tensor parallelism: set-up ---- */
+void tp_close() {
+    Tp &t = g_tp;
+    if (model().st) cudaStreamSynchronize(model().st);
+    ctx_close(g_one);
+    for (int r = 0; r < t.world; r++)
+        if (t.peer[r] && r != t.rank) cudaIpcCloseMemHandle(t.peer[r]);
+    if (t.arena) cudaFree(t.arena);
+    if (t.epoch) cudaFree(t.epoch);
+    cudaGetLastError();
+    t = Tp();
+}
+
+/* Step 1 (every rank): allocate this rank's exchange arena and return its IPC handle (64 bytes). */
+int tp_arena(int rank, int world, void *handle_out) {
+    Model &m = model();
+    if (!m.inited || !handle_out || world < 1 || world > kTpMaxRanks || rank < 0 || rank >= world) return -1;
+    if ((QKV / kTcTileN) % world || (D / kTcTileN) % world || (2 * HID / kTcTileN) % world) return -1;
+    tp_close();
+    Tp &t = g_tp;
+    t.rank = rank; t.world = world;
+    tp_layout(t);
+    if (cudaMalloc((void **)&t.arena, t.bytes) != cudaSuccess || cudaMemset(t.arena, 0, t.bytes) != cudaSuccess ||
+        cudaMalloc((void **)&t.epoch, 64 * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemset(t.epoch, 0, 64 * sizeof(unsigned)) != cudaSuccess ||
+        cudaIpcGetMemHandle((cudaIpcMemHandle_t *)handle_out, t.arena) != cudaSuccess) {
+        tp_close();
+        return -1;
+    }
+    t.tickets = t.epoch + 16;
+    return 0;
+}
+
+/* The tile slices and split-K factors a rank would use: out[0..8] = first tile and tile count of
+ * the QKV, O/down and gate/up GEMMs, then the split-K factors of QKV, O, down. Host arithmetic
+ * only (no GPU needed): lets a test check that the slices of all ranks tile every matrix. */
+int tp_plan(int rank, int world, int n_sm, int *out) {
+    if (!out || world < 1 || world > kTpMaxRanks || rank < 0 || rank >= world) return -1;
+    if ((QKV / kTcTileN) % world || (D / kTcTileN) % world || (2 * HID / kTcTileN) % world) return -1;
+    const int tiles[3] = {QKV / kTcTileN, D / kTcTileN, 2 * HID / kTcTileN};
+    for (int i = 0; i < 3; i++) {
+        out[2 * i] = (int)((long long)tiles[i] * rank / world);
+        out[2 * i + 1] = (int)((long long)tiles[i] * (rank + 1) / world) - out[2 * i];
+    }
+    out[6] = tc_pick_splits(out[1] * kTcTileN, D, n_sm);
+    out[7] = tc_pick_splits(out[3] * kTcTileN, QD, n_sm);
+    out[8] = tc_pick_splits(out[3] * kTcTileN, HID, n_sm);
+    return 0;
+}
+
+/* Step 2 (every rank, after the handles of all ranks were gathered by the caller): map the
+ * peers' arenas and switch the single-utterance calls to tensor-parallel launches. The caller
+ * synchronises the ranks (a host barrier) before the first frame and keeps them in lock step:
+ * every rank makes the same frame calls with the same inputs. */
+int tp_connect(const void *handles) {
+    Tp &t = g_tp;
+    if (!t.arena || !handles) return -1;
+    const cudaIpcMemHandle_t *h = (const cudaIpcMemHandle_t *)handles;
+    for (int r = 0; r < t.world; r++) {
+        if (r == t.rank) { t.peer[r] = t.arena; continue; }
+        void *p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            tp_close();
+            return -1;
+        }
+        t.peer[r] = (unsigned char *)p;
+    }
+    ctx_close(g_one);       /* reopened on first use with its exchanged buffers inside the arena */
+    t.on = t.world > 1;
+    return 0;
+}
 
 void batch_free_all() {
     ctx_close(g_bt);
     ctx_close(g_one);
+    tp_close();
     bt_free(&g_w.allocs);
     g_w.ready = false;
 }
@@ -506,7 +672,15 @@ static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames
     rc |= bt_alloc((void **)&t.bD, tc_acts_bytes(16, D), &t.allocs);
     rc |= bt_alloc((void **)&t.bQ, tc_acts_bytes(16, QD), &t.allocs);
     rc |= bt_alloc((void **)&t.bH, tc_acts_bytes(16, HID), &t.allocs);
+    if (single && g_tp.on) t.bH = (uint16_t *)(g_tp.arena + g_tp.ll.bH);
     rc |= bt_alloc((void **)&t.part, sizeof(float) * kTcMaxSplits * B * QKV, &t.allocs);
+    t.part_qkv = t.part_wo = t.part_w2 = t.part;
+    t.tp = single && g_tp.on;
+    if (t.tp) {
+        t.part_qkv = (float *)(g_tp.arena + g_tp.ll.part[TP_QKV]);
+        t.part_wo = (float *)(g_tp.arena + g_tp.ll.part[TP_WO]);
+        t.part_w2 = (float *)(g_tp.arena + g_tp.ll.part[TP_W2]);
+    }
     rc |= bt_alloc((void **)&t.ssq, sizeof(float) * 16 * 16, &t.allocs);
     rc |= bt_alloc((void **)&t.logit_part, sizeof(float) * kTcMaxSplits * B * NSEM, &t.allocs);
     rc |= bt_alloc((void **)&t.attn_scratch,
@@ -540,30 +714,62 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
     if (embed_mode != EMBED_HOST)
         launch_pdl(bt_embed_kernel, dim3((D + 255) / 256, B), dim3(256), 0, st, t.X, (const uint16_t *)m.audio_table,
                    (const int *)t.codes, (const VbDyn *)t.dyn, VB200_CODES, 8194, 23, embed_mode);
-    TcGemm g;
-    g.M = B; g.status = t.status;
+    /* Tensor parallelism: this rank's tile slice of each layer GEMM, split-K chosen for the slice. */
+    const bool tp = t.tp;
+    int q0 = 0, qn = 0, o0 = 0, on = 0, h0 = 0, hn = 0;
+    int s_qkv = w.s_qkv, s_wo = w.s_wo, s_w2 = w.s_w2;
+    if (tp) {
+        tp_slice(QKV / kTcTileN, &q0, &qn);
+        tp_slice(D / kTcTileN, &o0, &on);
+        tp_slice(2 * HID / kTcTileN, &h0, &hn);
+        s_qkv = tc_pick_splits(qn * kTcTileN, D, m.sm_count);
+        s_wo = tc_pick_splits(on * kTcTileN, QD, m.sm_count);
+        s_w2 = tc_pick_splits(on * kTcTileN, HID, m.sm_count);
+        tp_epoch_kernel<<<1, 1, 0, st>>>(g_tp.epoch);
+    }
     for (int l = 0; l < VB200_DEC_LAYERS; l++) {
         const LayerDev &L = m.dec[l];
+        const int NL = VB200_DEC_LAYERS;      /* every exchanged buffer is filled once per layer */
         if (l == 0) tc_prepare(t.aD, t.X, D, B, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
-        else tc_prepare(t.aD, nullptr, D, B, t.part, w.s_w2, psD, t.X, t.X, L.attn_norm, t.ssq, st);
-        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
-        g.splits = w.s_qkv; g.ld_out = QKV; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
+        else tc_prepare(t.aD, nullptr, D, B, t.part_w2, s_w2, psD, t.X, t.X, L.attn_norm, t.ssq, st,
+                        tp_wait_for(0, TP_W2, NL, l, t.status));
+        TcGemm g;
+        g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
+        g.epi = TC_EPI_PARTIAL; g.out = t.part_qkv; g.splits = s_qkv; g.ld_out = QKV;
+        g.ssq = t.ssq; g.ssq_chunks = chunksD;
+        if (tp) { g.tile0 = q0; g.n_tiles = qn; g.push = tp_push(0, TP_QKV, NL, l + 1); }
         if (tc_gemm(w.wqkv[l], t.aD, g, st)) return -1;
         launch_pdl(bt_attn_kernel, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ, 16,
-                   (const float *)t.part, w.s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn, scale,
-                   VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status);
-        g.splits = w.s_wo; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+                   (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn, scale,
+                   VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status,
+                   tp_wait_for(0, TP_QKV, NL, l + 1, t.status));
+        g = TcGemm();
+        g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
+        g.epi = TC_EPI_PARTIAL; g.out = t.part_wo; g.splits = s_wo; g.ld_out = D;
+        if (tp) { g.tile0 = o0; g.n_tiles = on; g.push = tp_push(0, TP_WO, NL, l + 1); }
         if (tc_gemm(w.wo[l], t.aQ, g, st)) return -1;
-        tc_prepare(t.aD, nullptr, D, B, t.part, w.s_wo, psD, t.X, t.X, L.ffn_norm, t.ssq, st);
-        g.epi = TC_EPI_SWIGLU_TERMS; g.out = nullptr; g.out_terms = t.bH; g.out_rows_pad = 16;
+        tc_prepare(t.aD, nullptr, D, B, t.part_wo, s_wo, psD, t.X, t.X, L.ffn_norm, t.ssq, st,
+                   tp_wait_for(0, TP_WO, NL, l + 1, t.status));
+        g = TcGemm();
+        g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
+        g.epi = TC_EPI_SWIGLU_TERMS; g.out_terms = t.bH; g.out_rows_pad = 16;
         g.splits = 1; g.ld_out = HID; g.ssq = t.ssq; g.ssq_chunks = chunksD;
+        if (tp) { g.tile0 = h0; g.n_tiles = hn; g.push = tp_push(0, TP_W13, NL, l + 1); }
         if (tc_gemm(w.w13[l], t.aD, g, st)) return -1;
-        g.epi = TC_EPI_PARTIAL; g.out = t.part; g.out_terms = nullptr;
-        g.splits = w.s_w2; g.ld_out = D; g.ssq = nullptr; g.ssq_chunks = 0;
+        g = TcGemm();
+        g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
+        g.epi = TC_EPI_PARTIAL; g.out = t.part_w2; g.splits = s_w2; g.ld_out = D;
+        if (tp) {
+            g.tile0 = o0; g.n_tiles = on; g.push = tp_push(0, TP_W2, NL, l + 1);
+            g.wait = tp_wait_for(0, TP_W13, NL, l + 1, t.status);     /* the SwiGLU terms come from every rank */
+        }
         if (tc_gemm(w.w2[l], t.aH, g, st)) return -1;
     }
     launch_pdl(bt_final_kernel, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
-               (const float *)t.part, w.s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS);
+               (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS,
+               tp_wait_for(0, TP_W2, VB200_DEC_LAYERS, VB200_DEC_LAYERS, t.status));
+    TcGemm g;
+    g.M = B; g.status = t.status;
     /* semantic head + argmax (voxtral_tts_acoustic.c:283-309), llm token (:204) */
     g.epi = TC_EPI_PARTIAL; g.out = t.logit_part; g.splits = w.s_sem; g.ld_out = NSEM; g.ssq = nullptr; g.ssq_chunks = 0;
     if (tc_gemm(w.wsem, t.aD, g, st)) return -1;

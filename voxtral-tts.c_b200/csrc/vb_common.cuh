@@ -100,6 +100,16 @@ VB_DEVINL unsigned vb_ld_acquire_gpu(const unsigned *p) {
     return v;
 }
 
+/* System scope: words that another GPU writes or reads over NVLink (tensor-parallel flags). */
+VB_DEVINL unsigned vb_ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+VB_DEVINL void vb_st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 VB_DEVINL int vb_ld_relaxed_gpu_s32(const int *p) {
     int v;
     asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

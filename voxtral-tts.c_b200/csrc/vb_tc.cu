@@ -167,6 +167,10 @@ struct TcKernelArgs {
     uint16_t *out_terms;     /* TC_EPI_SWIGLU_TERMS: BF16 terms of the result, [3][out_rows_pad][N/2] */
     int out_rows_pad;
     int *status;
+    int tile0;               /* first output tile of this launch */
+    int n_tiles_launch;      /* tiles this launch covers (host side: the grid) */
+    TcPush push;             /* tensor parallelism: results also go to the peers' buffers */
+    TcWait wait;             /* ... and the activation terms may be exchanged data */
 };
 
 template <int NB, int ST>
@@ -193,7 +197,7 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     float *rscale = (float *)(abort_flag + 1);   /* [NB] per-row scales */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x / splits, sp = blockIdx.x % splits;
+    const int tile = ka.tile0 + blockIdx.x / splits, sp = blockIdx.x % splits;
     const int kblocks = K / kTcBlockK;
     const int kb0 = (int)((long long)kblocks * sp / splits), kb1 = (int)((long long)kblocks * (sp + 1) / splits);
     const int n_it = kb1 - kb0;
@@ -228,6 +232,12 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             else tma_load_2d(sa, &mapA, (kb0 + it) * kTcBlockK, tile * kTcTileN, &full[it]);
         }
         pdl_wait();
+        if (ka.wait.n > 0) {
+            /* the activation terms were written by other GPUs: wait for all of them, then make
+             * those writes visible to the TMA engine's proxy */
+            if (!tp_wait(ka.wait)) *(volatile int *)abort_flag = 1;
+            asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int it = 0; it < first; it++) {
             unsigned char *sa = stages + (size_t)it * Cfg::kStage;
 #pragma unroll
@@ -336,14 +346,30 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                                 ka.out_terms[o] = t0;
                                 ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = t1;
                                 ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
+                                for (int d = 1; d < ka.push.n_dst; d++) {
+                                    uint16_t *pt = (uint16_t *)((char *)ka.out_terms + ka.push.dst_off[d]);
+                                    pt[o] = t0;
+                                    pt[(size_t)ka.out_rows_pad * ko + o] = t1;
+                                    pt[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
+                                }
                             }
                         }
                     } else if (m < M && row < N) {
                         if (epi == TC_EPI_STORE) out[(size_t)m * ld_out + row] = v + (bias ? __ldg(bias + row) : 0.0f);
-                        else out[((size_t)sp * M + m) * ld_out + row] = v;
+                        else {
+                            const size_t o = ((size_t)sp * M + m) * ld_out + row;
+                            out[o] = v;
+                            for (int d = 1; d < ka.push.n_dst; d++) *(float *)((char *)(out + o) + ka.push.dst_off[d]) = v;
+                        }
                     }
                 }
             }
+        }
+        if (ka.push.n_dst > 0) {
+            /* tensor parallelism: once every CTA of this launch has its results in all ranks'
+             * buffers, the last one publishes the visit to every rank */
+            vb_named_bar(1, 128);
+            if (threadIdx.x == 0) tp_publish(ka.push, gridDim.x);
         }
     }
 
@@ -377,7 +403,7 @@ static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka,
         }
         attr = true;
     }
-    const int tiles = (w.N + kTcTileN - 1) / kTcTileN;
+    const int tiles = ka.n_tiles_launch;
     return launch_pdl(vb_tc_gemm_kernel<NB, ST>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
                       w.map, a.map, ka) == cudaSuccess
                ? 0
@@ -395,6 +421,16 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
     ka.N = w.N; ka.K = w.K; ka.M = g.M; ka.rows_pad = a.rows_pad; ka.ld_out = g.ld_out; ka.splits = g.splits;
     ka.epi = g.epi; ka.out = g.out; ka.bias = g.bias; ka.ssq = g.ssq; ka.ssq_chunks = g.ssq_chunks; ka.eps = g.eps;
     ka.out_terms = g.out_terms; ka.out_rows_pad = g.out_rows_pad; ka.status = g.status;
+    {
+        const int tiles = (w.N + kTcTileN - 1) / kTcTileN;
+        ka.tile0 = g.n_tiles > 0 ? g.tile0 : 0;
+        ka.n_tiles_launch = g.n_tiles > 0 ? g.n_tiles : tiles;
+        if (ka.tile0 < 0 || ka.tile0 + ka.n_tiles_launch > tiles) return -1;
+        if (g.push.n_dst > kTpMaxRanks || (g.push.n_dst > 0 && (!g.push.ticket || !g.push.epoch))) return -1;
+    }
+    ka.push = g.push;
+    ka.wait = g.wait;
+    ka.wait.status = g.status;
     switch (a.rows_pad) {
     case 16: {
         /* Pipeline depth of the 16-row kernel. Measured on the frame loop: 3 stages 3.74 ms per
@@ -420,10 +456,15 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
  * CTA has to see a whole row and the kernel is a few microseconds instead of a serial pass. */
 __global__ void vb_tc_prepare_kernel(uint16_t *buf, int rows_pad, int K, const float *x, int ldx,
                                      const float *partials, int n_part, size_t part_stride,
-                                     const float *residual, float *x_out, const float *gain, float *ssq) {
+                                     const float *residual, float *x_out, const float *gain, float *ssq,
+                                     const TcWait wait) {
     __shared__ float red[8];
     pdl_launch_dependents();
     pdl_wait();
+    if (wait.n > 0) {   /* the partials come from every rank */
+        if (threadIdx.x == 0) tp_wait(wait);
+        __syncthreads();
+    }
     const int m = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     float ss = 0.0f;
@@ -479,10 +520,10 @@ int tc_prepare_chunks(int K) { return (K + 1023) / 1024; }
 
 void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float *partials, int n_part,
                 size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
-                cudaStream_t st) {
+                cudaStream_t st, const TcWait &wait) {
     if (M <= 0) return;
     launch_pdl(vb_tc_prepare_kernel, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf, acts.rows_pad,
-               acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq);
+               acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, wait);
 }
 
 /* y[i] = sum over the split-K partials in fixed order (+ bias[i % N]). */

@@ -50,6 +50,33 @@ struct TcActs {
     bool ok;
 };
 
+/* ---- tensor parallelism: every rank computes a slice of a GEMM's output tiles and stores
+ * its results into every rank's copy of the output buffer (peer memory over NVLink); the
+ * consumers wait for a per-site sequence number from every rank. ---- */
+constexpr int kTpMaxRanks = 8;
+
+/* Producer side: where a GEMM's results also go, and how completion is published: the last
+ * CTA of the launch (a local ticket) writes a sequence number, (frame - 1) * visits_per_frame +
+ * visit, into a flag word on every destination. (Counting every CTA in with remote atomics
+ * instead was measured slower: 4.6-4.9 ms against 4.3 ms per frame at two GPUs.) */
+struct TcPush {
+    int n_dst = 0;                        /* 0: single GPU, nothing below is used */
+    long long dst_off[kTpMaxRanks] = {};  /* byte offset from the local buffer to destination d's copy (0 = local) */
+    unsigned *flag[kTpMaxRanks] = {};     /* destination d's flag word for (this buffer, this rank) */
+    unsigned *ticket = nullptr;           /* local counter */
+    const unsigned *epoch = nullptr;      /* device word: frame number, 1-based */
+    int visits_per_frame = 0, visit = 0;  /* this buffer is exchanged visits_per_frame times per frame; 1-based index */
+};
+
+/* Consumer side: do not read the exchanged buffer before every rank has published the visit. */
+struct TcWait {
+    const unsigned *flags = nullptr;      /* [n] local flag words, one per source rank */
+    int n = 0;                            /* 0: nothing to wait for */
+    const unsigned *epoch = nullptr;
+    int visits_per_frame = 0, visit = 0;
+    int *status = nullptr;
+};
+
 /* One GEMM launch. */
 struct TcGemm {
     int M = 0, splits = 1, epi = TC_EPI_STORE;
@@ -62,6 +89,9 @@ struct TcGemm {
     uint16_t *out_terms = nullptr;    /* TC_EPI_SWIGLU_TERMS destination [3][out_rows_pad][N/2] */
     int out_rows_pad = 0;
     int *status = nullptr;            /* device int, set non-zero when a bounded wait runs out */
+    int tile0 = 0, n_tiles = 0;       /* output tiles [tile0, tile0 + n_tiles) of the weight matrix; 0 = all */
+    TcPush push;
+    TcWait wait;                      /* the activation terms (and ssq) are exchanged data */
 };
 
 int tc_init();                                     /* resolves cuTensorMapEncodeTiled; 0 when usable */
@@ -81,7 +111,7 @@ int tc_prepare_chunks(int K);                      /* column chunks (and ssq ent
  * (RMSNorm's scalar is applied by the consuming GEMM). */
 void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float *partials, int n_part,
                 size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
-                cudaStream_t st);
+                cudaStream_t st, const TcWait &wait = TcWait());
 
 int tc_gemm(const TcWeight &w, const TcActs &acts, const TcGemm &g, cudaStream_t st);
 

@@ -63,6 +63,37 @@ VB_DEVINL void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+/* Tensor-parallel consumer wait (one thread): every source rank has published this visit of
+ * the buffer. Bounded; false (and a status code) when it runs out. */
+VB_DEVINL bool tp_wait(const TcWait &w) {
+    if (w.n <= 0) return true;
+    const unsigned frame = *(volatile const unsigned *)w.epoch;
+    const unsigned target = (frame - 1u) * (unsigned)w.visits_per_frame + (unsigned)w.visit;
+    const long long t0 = clock64();
+    for (int i = 0; i < w.n; i++) {
+        while ((int)(vb_ld_acquire_sys(w.flags + i) - target) < 0) {
+            if (clock64() - t0 > VB_WAIT_CYCLES) {
+                if (w.status) atomicCAS(w.status, 0, 31);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+/* Tensor-parallel producer side, called by one thread of a CTA after the CTA's stores and a
+ * CTA-wide barrier: make them visible system-wide and take a ticket; the last CTA of the launch
+ * publishes the visit's sequence number on every rank. */
+VB_DEVINL void tp_publish(const TcPush &p, unsigned n_ctas) {
+    __threadfence_system();
+    const unsigned t = atomicAdd(p.ticket, 1u);
+    if (t != n_ctas - 1u) return;
+    *p.ticket = 0u;
+    __threadfence_system();
+    const unsigned seq = (*(volatile const unsigned *)p.epoch - 1u) * (unsigned)p.visits_per_frame + (unsigned)p.visit;
+    for (int d = 0; d < p.n_dst; d++) vb_st_release_sys(p.flag[d], seq);
+}
+
 VB_DEVINL void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 VB_DEVINL void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
