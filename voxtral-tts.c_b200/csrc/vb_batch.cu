@@ -108,7 +108,13 @@ static Batch g_one;   /* the single-utterance calls on the library's cache */
  * every rank's buffers over NVLink; the small kernels between the GEMMs run redundantly on
  * identical data, so the residual stream and the caches stay bit-identical on all ranks. The
  * exchanged buffers (split-K partials per GEMM type, the SwiGLU terms) and the flag words lie
- * in one arena per rank at identical offsets; peers map it through CUDA IPC. */
+ * in one arena per rank at identical offsets; peers map it through CUDA IPC.
+ *
+ * Why a fast rank never overwrites data a slow rank still reads, with one buffer per GEMM type:
+ * rank q stores exchange v+1 of a buffer only after its own consumer of exchange v of the
+ * NEXT buffer in the layer cycle (QKV -> O -> gate/up -> down -> QKV ...) has passed its wait,
+ * i.e. after every rank p has finished the GEMM that fills that next buffer; on p that GEMM is
+ * stream-ordered after p's reads of exchange v of the first buffer. */
 enum TpSlot { TP_QKV = 0, TP_WO = 1, TP_W13 = 2, TP_W2 = 3 };
 struct TpSet {                 /* exchanged buffers of one context (decoder rows / acoustic rows) */
     size_t part[4];            /* byte offsets in the arena: partials of QKV, O, (unused), down */
