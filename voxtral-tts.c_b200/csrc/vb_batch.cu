@@ -1,18 +1,23 @@
 /*
- * vb_batch.cu - several independent utterances decoded in lock step on one GPU.
+ * vb_batch.cu - the frame as a CUDA graph of tensor-core GEMM launches, for one utterance or
+ * for several independent utterances decoded in lock step on one GPU.
  *
  * The reference synthesises one utterance at a time (voxtral_tts.c:301-321: decoder step,
  * acoustic frame, re-embedding, per frame). Frames of different utterances do not depend on
  * one another, so B of them share every weight read: the decoder step becomes a B-row GEMM
  * and the acoustic passes a 6B-row GEMM on the tcgen05 kernel (vb_tc.cu); weights cross HBM
  * once per frame for all B utterances. Each utterance has its own KV cache slab, position,
- * noise rows and END state.
+ * noise rows and END state. B = 1 on the library's own cache serves the single-utterance calls
+ * (vb200_frame, vb200_utterance_*, the drop-in's tts_llm_forward).
  *
- * One frame of the batch is a fixed sequence of launches (captured as a CUDA graph):
+ * One frame is a fixed sequence of launches (captured as a CUDA graph):
  *   embed (from the previous frame's codes)
  *   26 x [prepare, QKV GEMM, decode attention, O GEMM, prepare, gate/up GEMM, down GEMM]
  *   final norm, semantic-head GEMM + argmax, llm_proj GEMM
  *   7 Euler steps + FSQ (vb_acoustic_tc.cu), which also advances every utterance.
+ *
+ * Also here: the tensor-parallel variant of the decoder layers over the GPUs of a node
+ * (struct Tp), and two measurement aids (gemm_sweep, ptc_decoder_sweep).
  */
 #include "vb_acoustic_tc.cuh"
 #include "vb_common.cuh"
