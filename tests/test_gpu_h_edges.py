@@ -81,3 +81,26 @@ def test_batch_refuses_bad_sizes(pkg, engine, synth_model):
     assert L.vb200_batch_begin(fe.ctypes.data, bad.ctypes.data, noise.ctypes.data) == -1
     L.vb200_batch_close()
     assert L.vb200_batch_hidden(fe.ctypes.data) == -1                 # nothing open
+
+
+def test_long_device_loop_equals_frame_by_frame(pkg, engine, oracle, synth_model):
+    """64 graph replays with state kept on the device == 64 single-frame calls with the host
+    carrying position and re-embedding (same kernels, so the codes must be identical)."""
+    frames = 64
+    p = _prompt(pkg, synth_model, 40, 7)
+    e0 = synth_model.token_rows([24])[0]
+    noise = _noise(oracle, 21, frames)
+    engine.L.vb200_set_option(b"ignore_end", 1)
+    try:
+        engine.prefill(p, 0)
+        codes, hit_end, _ = engine.utterance(e0, 40, noise)
+        assert codes.shape == (frames, 37) and not hit_end
+        engine.prefill(p, 0)
+        table = synth_model.audio_table()
+        e = e0
+        for f in range(frames):
+            c, _ = engine.frame(e, noise[f], 40 + f)
+            assert np.array_equal(c, codes[f]), f
+            e = oracle.audio_embed(table, c)
+    finally:
+        engine.L.vb200_set_option(b"ignore_end", 0)

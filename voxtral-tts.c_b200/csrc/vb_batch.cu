@@ -224,10 +224,11 @@ __global__ void bt_embed_kernel(float *X, const uint16_t *table, const int *code
  * four query heads of its KV head on one slice of the keys; the last CTA of a (utterance,
  * KV head) to finish merges the slices in fixed order and writes the result as the three
  * BF16 terms the O projection's GEMM consumes. */
+template <bool TP>
 __global__ void __launch_bounds__(kBtAttnThreads)
 bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, size_t part_stride, float *kv_k,
                float *kv_v, size_t slab, int layer, const VbDyn *dyn, float scale, float theta, float *scratch,
-               unsigned *tickets, int *status, const TcWait wait) {
+               unsigned *tickets, int *status, const typename TcWaitSel<TP>::type wait) {
     __shared__ float cs[kHD];
     __shared__ __align__(16) float qraw[kGroup * kHD];
     __shared__ float kraw[kHD], vraw[kHD];
@@ -237,7 +238,7 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     __shared__ int last_flag;
     pdl_launch_dependents();
     pdl_wait();
-    if (wait.n > 0) {   /* tensor parallelism: the QKV partials come from every rank */
+    if constexpr (TP) {   /* tensor parallelism: the QKV partials come from every rank */
         if (threadIdx.x == 0) tp_wait(wait);
         __syncthreads();
     }
@@ -408,13 +409,14 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
 /* End of the decoder step: last residual add (split-K partials of the last down projection),
  * final RMSNorm (voxtral_tts_llm.c:267), hidden rows out as fp32 and as BF16 terms for the two
  * head GEMMs. grid = B, 1024 threads. */
+template <bool TP>
 __global__ void __launch_bounds__(1024)
 bt_final_kernel(float *hidden, uint16_t *terms, int rows_pad, const float *X, const float *part, int n_part,
-                size_t part_stride, const float *gain, float eps, const TcWait wait) {
+                size_t part_stride, const float *gain, float eps, const typename TcWaitSel<TP>::type wait) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
-    if (wait.n > 0) {
+    if constexpr (TP) {
         if (threadIdx.x == 0) tp_wait(wait);
         __syncthreads();
     }
@@ -750,10 +752,15 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
         g.ssq = t.ssq; g.ssq_chunks = chunksD;
         if (tp) { g.tile0 = q0; g.n_tiles = qn; g.push = tp_push(0, TP_QKV, NL, l + 1); }
         if (tc_gemm(w.wqkv[l], t.aD, g, st)) return -1;
-        launch_pdl(bt_attn_kernel, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ, 16,
-                   (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn, scale,
-                   VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status,
-                   tp_wait_for(0, TP_QKV, NL, l + 1, t.status));
+        if (tp)
+            launch_pdl(bt_attn_kernel<true>, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
+                       16, (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn,
+                       scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status,
+                       tp_wait_for(0, TP_QKV, NL, l + 1, t.status));
+        else
+            launch_pdl(bt_attn_kernel<false>, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
+                       16, (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn,
+                       scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status, TcNoWait());
         g = TcGemm();
         g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
         g.epi = TC_EPI_PARTIAL; g.out = t.part_wo; g.splits = s_wo; g.ld_out = D;
@@ -776,9 +783,13 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
         }
         if (tc_gemm(w.w2[l], t.aH, g, st)) return -1;
     }
-    launch_pdl(bt_final_kernel, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
-               (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS,
-               tp_wait_for(0, TP_W2, VB200_DEC_LAYERS, VB200_DEC_LAYERS, t.status));
+    if (tp)
+        launch_pdl(bt_final_kernel<true>, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
+                   (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS,
+                   tp_wait_for(0, TP_W2, VB200_DEC_LAYERS, VB200_DEC_LAYERS, t.status));
+    else
+        launch_pdl(bt_final_kernel<false>, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
+                   (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS, TcNoWait());
     TcGemm g;
     g.M = B; g.status = t.status;
     /* semantic head + argmax (voxtral_tts_acoustic.c:283-309), llm token (:204) */

@@ -169,14 +169,23 @@ struct TcKernelArgs {
     int *status;
     int tile0;               /* first output tile of this launch */
     int n_tiles_launch;      /* tiles this launch covers (host side: the grid) */
-    TcPush push;             /* tensor parallelism: results also go to the peers' buffers */
-    TcWait wait;             /* ... and the activation terms may be exchanged data */
 };
 
-template <int NB, int ST>
+/* Tensor parallelism is a separate instantiation of every kernel that takes part in it, with
+ * its arguments in a parameter of their own: the single-GPU kernels keep their parameter block
+ * and code (carrying the extra 200 bytes and branches in every launch cost 0.3 ms per frame). */
+struct TcTpArgs {
+    TcPush push;             /* results also go to the peers' buffers */
+    TcWait wait;             /* the activation terms may be exchanged data */
+};
+struct TcNoTpArgs {};
+template <bool TP> struct TcTpSel { using type = TcNoTpArgs; };
+template <> struct TcTpSel<true> { using type = TcTpArgs; };
+
+template <int NB, int ST, bool TP>
 __global__ void __launch_bounds__(kTcThreads, 1)
 vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                  const TcKernelArgs ka) {
+                  const TcKernelArgs ka, const typename TcTpSel<TP>::type tp) {
     using Cfg = TcCfg<NB, ST>;
     const int N = ka.N, K = ka.K, M = ka.M, rows_pad = ka.rows_pad, ld_out = ka.ld_out, splits = ka.splits,
               epi = ka.epi;
@@ -232,11 +241,13 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             else tma_load_2d(sa, &mapA, (kb0 + it) * kTcBlockK, tile * kTcTileN, &full[it]);
         }
         pdl_wait();
-        if (ka.wait.n > 0) {
-            /* the activation terms were written by other GPUs: wait for all of them, then make
-             * those writes visible to the TMA engine's proxy */
-            if (!tp_wait(ka.wait)) *(volatile int *)abort_flag = 1;
-            asm volatile("fence.proxy.async;" ::: "memory");
+        if constexpr (TP) {
+            if (tp.wait.n > 0) {
+                /* the activation terms were written by other GPUs: wait for all of them, then make
+                 * those writes visible to the TMA engine's proxy */
+                if (!tp_wait(tp.wait)) *(volatile int *)abort_flag = 1;
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
         }
         for (int it = 0; it < first; it++) {
             unsigned char *sa = stages + (size_t)it * Cfg::kStage;
@@ -346,11 +357,13 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                                 ka.out_terms[o] = t0;
                                 ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = t1;
                                 ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
-                                for (int d = 1; d < ka.push.n_dst; d++) {
-                                    uint16_t *pt = (uint16_t *)((char *)ka.out_terms + ka.push.dst_off[d]);
-                                    pt[o] = t0;
-                                    pt[(size_t)ka.out_rows_pad * ko + o] = t1;
-                                    pt[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
+                                if constexpr (TP) {
+                                    for (int d = 1; d < tp.push.n_dst; d++) {
+                                        uint16_t *pt = (uint16_t *)((char *)ka.out_terms + tp.push.dst_off[d]);
+                                        pt[o] = t0;
+                                        pt[(size_t)ka.out_rows_pad * ko + o] = t1;
+                                        pt[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
+                                    }
                                 }
                             }
                         }
@@ -359,17 +372,22 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                         else {
                             const size_t o = ((size_t)sp * M + m) * ld_out + row;
                             out[o] = v;
-                            for (int d = 1; d < ka.push.n_dst; d++) *(float *)((char *)(out + o) + ka.push.dst_off[d]) = v;
+                            if constexpr (TP) {
+                                for (int d = 1; d < tp.push.n_dst; d++)
+                                    *(float *)((char *)(out + o) + tp.push.dst_off[d]) = v;
+                            }
                         }
                     }
                 }
             }
         }
-        if (ka.push.n_dst > 0) {
-            /* tensor parallelism: once every CTA of this launch has its results in all ranks'
-             * buffers, the last one publishes the visit to every rank */
-            vb_named_bar(1, 128);
-            if (threadIdx.x == 0) tp_publish(ka.push, gridDim.x);
+        if constexpr (TP) {
+            if (tp.push.n_dst > 0) {
+                /* once every CTA of this launch has its results in all ranks' buffers, the last one
+                 * publishes the visit to every rank */
+                vb_named_bar(1, 128);
+                if (threadIdx.x == 0) tp_publish(tp.push, gridDim.x);
+            }
         }
     }
 
@@ -391,12 +409,13 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     }
 }
 
-template <int NB, int ST>
-static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, cudaStream_t st) {
+template <int NB, int ST, bool TP>
+static int launch_tc_tp(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, const TcTpArgs &tpa,
+                        cudaStream_t st) {
     using Cfg = TcCfg<NB, ST>;
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemBytes) != cudaSuccess) {
             cudaGetLastError();
             return -1;
@@ -404,10 +423,18 @@ static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka,
         attr = true;
     }
     const int tiles = ka.n_tiles_launch;
-    return launch_pdl(vb_tc_gemm_kernel<NB, ST>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
-                      w.map, a.map, ka) == cudaSuccess
+    typename TcTpSel<TP>::type arg;
+    if constexpr (TP) arg = tpa;
+    return launch_pdl(vb_tc_gemm_kernel<NB, ST, TP>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
+                      w.map, a.map, ka, arg) == cudaSuccess
                ? 0
                : -1;
+}
+
+template <int NB, int ST>
+static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, const TcTpArgs &tpa, cudaStream_t st) {
+    if (tpa.push.n_dst > 0 || tpa.wait.n > 0) return launch_tc_tp<NB, ST, true>(w, a, ka, tpa, st);
+    return launch_tc_tp<NB, ST, false>(w, a, ka, tpa, st);
 }
 
 int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st) {
@@ -428,21 +455,22 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
         if (ka.tile0 < 0 || ka.tile0 + ka.n_tiles_launch > tiles) return -1;
         if (g.push.n_dst > kTpMaxRanks || (g.push.n_dst > 0 && (!g.push.ticket || !g.push.epoch))) return -1;
     }
-    ka.push = g.push;
-    ka.wait = g.wait;
-    ka.wait.status = g.status;
+    TcTpArgs tpa;
+    tpa.push = g.push;
+    tpa.wait = g.wait;
+    tpa.wait.status = g.status;
     switch (a.rows_pad) {
     case 16: {
         /* Pipeline depth of the 16-row kernel. Measured on the frame loop: 3 stages 3.74 ms per
          * frame, 4: 3.46, 5: 3.40, 6: 3.36, 8: 3.39, 10: 3.48. With 6 (136 KB) one CTA fits an SM. */
         static const int st16 = getenv("VB200_TC_STAGES") ? atoi(getenv("VB200_TC_STAGES")) : 6;
-        if (st16 == 4) return launch_tc<16, 4>(w, a, ka, st);
-        if (st16 == 5) return launch_tc<16, 5>(w, a, ka, st);
-        if (st16 == 8) return launch_tc<16, 8>(w, a, ka, st);
-        return launch_tc<16, 6>(w, a, ka, st);
+        if (st16 == 4) return launch_tc<16, 4>(w, a, ka, tpa, st);
+        if (st16 == 5) return launch_tc<16, 5>(w, a, ka, tpa, st);
+        if (st16 == 8) return launch_tc<16, 8>(w, a, ka, tpa, st);
+        return launch_tc<16, 6>(w, a, ka, tpa, st);
     }
-    case 64: return launch_tc<64, 5>(w, a, ka, st);
-    case 256: return launch_tc<256, 2>(w, a, ka, st);
+    case 64: return launch_tc<64, 5>(w, a, ka, tpa, st);
+    case 256: return launch_tc<256, 2>(w, a, ka, tpa, st);
     default: return -1;
     }
 }
@@ -454,14 +482,15 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
  * optional: x_out = v (the new residual stream); with a gain, the terms hold v*gain and the
  * CTA's sum of v^2 goes to ssq[m][chunk] - the consumer GEMM applies 1/sqrt(mean+eps), so no
  * CTA has to see a whole row and the kernel is a few microseconds instead of a serial pass. */
+template <bool TP>
 __global__ void vb_tc_prepare_kernel(uint16_t *buf, int rows_pad, int K, const float *x, int ldx,
                                      const float *partials, int n_part, size_t part_stride,
                                      const float *residual, float *x_out, const float *gain, float *ssq,
-                                     const TcWait wait) {
+                                     const typename TcWaitSel<TP>::type wait) {
     __shared__ float red[8];
     pdl_launch_dependents();
     pdl_wait();
-    if (wait.n > 0) {   /* the partials come from every rank */
+    if constexpr (TP) {   /* the partials come from every rank */
         if (threadIdx.x == 0) tp_wait(wait);
         __syncthreads();
     }
@@ -522,8 +551,12 @@ void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float 
                 size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
                 cudaStream_t st, const TcWait &wait) {
     if (M <= 0) return;
-    launch_pdl(vb_tc_prepare_kernel, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf, acts.rows_pad,
-               acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, wait);
+    if (wait.n > 0)
+        launch_pdl(vb_tc_prepare_kernel<true>, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf,
+                   acts.rows_pad, acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, wait);
+    else
+        launch_pdl(vb_tc_prepare_kernel<false>, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf,
+                   acts.rows_pad, acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, TcNoWait());
 }
 
 /* y[i] = sum over the split-K partials in fixed order (+ bias[i % N]). */

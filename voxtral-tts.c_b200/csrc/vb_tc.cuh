@@ -77,6 +77,12 @@ struct TcWait {
     int *status = nullptr;
 };
 
+/* Kernels that can wait for exchanged data come in two instantiations; the single-GPU one
+ * takes an empty parameter. */
+struct TcNoWait {};
+template <bool TP> struct TcWaitSel { using type = TcNoWait; };
+template <> struct TcWaitSel<true> { using type = TcWait; };
+
 /* One GEMM launch. */
 struct TcGemm {
     int M = 0, splits = 1, epi = TC_EPI_STORE;
