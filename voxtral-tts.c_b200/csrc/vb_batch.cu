@@ -235,6 +235,7 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     __shared__ __align__(16) float qs[kGroup][kHD];
     __shared__ __align__(16) float attn_o[kBtSubsets][kGroup][kHD];
     __shared__ float attn_ml[kBtSubsets][kGroup][2];
+    __shared__ float cmb_m[kBtKeySplits * kGroup], cmb_l[kBtKeySplits * kGroup];
     __shared__ int last_flag;
     pdl_launch_dependents();
     pdl_wait();
@@ -386,15 +387,30 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
         __syncthreads();
         if (!last_flag) return;
         __threadfence();
+        /* merge the S slices in slice order. All loads are issued before anything waits on them:
+         * the (max, sum) pairs go through shared memory, the S output values of this thread's
+         * (head, dim) are fetched in one unrolled batch. */
+        if (tid < S * kGroup) {
+            const float *pu = po + (size_t)tid * stride;           /* (slice, head) = tid / kGroup, tid % kGroup */
+            cmb_m[tid] = __ldcg(pu + kHD);
+            cmb_l[tid] = __ldcg(pu + kHD + 1);
+        }
+        float ov[kBtKeySplits];
+#pragma unroll
+        for (int u = 0; u < kBtKeySplits; u++)
+            ov[u] = u < S ? __ldcg(po + ((size_t)u * kGroup + th) * stride + td) : 0.0f;
+        __syncthreads();
         float Mg = -1e30f;
-        for (int u = 0; u < S; u++) Mg = fmaxf(Mg, __ldcg(po + ((size_t)u * kGroup + th) * stride + kHD));
+        for (int u = 0; u < S; u++) Mg = fmaxf(Mg, cmb_m[u * kGroup + th]);
         float Lg = 0.0f, Og = 0.0f;
-        for (int u = 0; u < S; u++) {
-            const float *pu = po + ((size_t)u * kGroup + th) * stride;
-            const float lu = __ldcg(pu + kHD + 1);
-            const float w = (lu > 0.0f) ? expf(__ldcg(pu + kHD) - Mg) : 0.0f;
-            Lg += lu * w;
-            Og += __ldcg(pu + td) * w;
+#pragma unroll
+        for (int u = 0; u < kBtKeySplits; u++) {
+            if (u < S) {
+                const float lu = cmb_l[u * kGroup + th];
+                const float w = (lu > 0.0f) ? expf(cmb_m[u * kGroup + th] - Mg) : 0.0f;
+                Lg += lu * w;
+                Og += ov[u] * w;
+            }
         }
         result = (Lg > 0.0f) ? Og * (1.0f / Lg) : 0.0f;
     }

@@ -336,11 +336,13 @@ __device__ void p_epilogue(PSmem *s, const PArgs &a, uint32_t tmem, int tid) {
 #pragma unroll
                 for (int p = 0; p < 8; p++)
                     pv[p] = (p < op.splits && row < N) ? __ldcg(op.part + ((size_t)p * M + m) * N + row) : 0.0f;
+                /* the residual's load is in flight together with the partials' */
+                const float rv = (op.res && row < N) ? __ldcg(op.res + (size_t)m * op.ldy + row) : 0.0f;
                 float acc = 0.0f;
 #pragma unroll
                 for (int p = 0; p < 8; p++) acc += pv[p];     /* split order; unused splits add 0 */
                 if (row < N) {
-                    if (op.res) acc = __ldcg(op.res + (size_t)m * op.ldy + row) + acc;
+                    if (op.res) acc = rv + acc;
                     op.y[(size_t)m * op.ldy + row] = acc;
                 } else {
                     acc = 0.0f;
