@@ -240,7 +240,8 @@ def micro_gemm(args):
     pkg = load_package()
     L = pkg.lib()
     ms, splits = C.c_float(0.0), C.c_int(0)
-    rc = L.vb200_tc_gemm_probe(args.m, args.n, args.k, 1 if args.swiglu else 0, 0 if args.untiled else 1, args.reps,
+    rc = L.vb200_tc_gemm_probe(args.m, args.n, args.k, 1 if args.swiglu else 0,
+                               (0 if args.untiled else 1) | (2 if args.l2_resident else 0), args.reps,
                                C.byref(ms), C.byref(splits))
     if rc != 0:
         raise SystemExit(f"vb200_tc_gemm_probe failed ({rc})")
@@ -249,7 +250,7 @@ def micro_gemm(args):
     gbs = 2.0 * args.n * args.k / (us * 1e-6) / 1e9
     print(json.dumps({"micro": "gemm", "m": args.m, "k": args.k, "n": args.n, "launches": args.reps,
                       "epilogue": "swiglu_terms" if args.swiglu else "split_k_partials", "splits": splits.value,
-                      "tiled_weights": not args.untiled, "us_per_launch": us, "weight_bytes": 2 * args.n * args.k,
+                      "tiled_weights": not args.untiled, "l2_resident": bool(args.l2_resident), "us_per_launch": us, "weight_bytes": 2 * args.n * args.k,
                       "achieved_gbs": gbs, "frac_of_peak": gbs / peak, "peak_source": src}))
 
 
@@ -320,6 +321,8 @@ def main():
                     help="utterances per GPU of the additional lock-step measurement (1 = skip it)")
     ap.add_argument("--swiglu", action="store_true", help="--micro gemm: SwiGLU epilogue instead of split-K partials")
     ap.add_argument("--untiled", action="store_true", help="--micro gemm: row-major weights instead of the tiled copy")
+    ap.add_argument("--l2-resident", action="store_true",
+                    help="--micro gemm: one weight copy (stays in L2 when it fits) instead of rotating copies")
     ap.add_argument("--micro", default="", choices=["", "gemv", "gemm"],
                     help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
     ap.add_argument("--m", type=int, default=1)

@@ -82,8 +82,9 @@ void vb200_batch_close(void);
 int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, int *launches_per_sweep);
 /* Measurement aid without a model: a generated [N, K] BF16 matrix, M activation rows, `reps`
  * launches of the tensor-core GEMM between two CUDA events on the default stream (split-K
- * partial epilogue, or the SwiGLU epilogue when swiglu != 0; tiled != 0: tile-contiguous weight
- * copy as the frame uses). Returns elapsed ms and the split-K factor chosen. */
+ * partial epilogue, or the SwiGLU epilogue when swiglu != 0; tiled bit 0: tile-contiguous weight
+ * copy as the frame uses; bit 1: a single copy, which stays in L2 when it fits, instead of
+ * rotating through 512 MB of copies). Returns elapsed ms and the split-K factor chosen. */
 int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, float *ms, int *splits);
 /* y[M,N] = x[M,K] . W[N,K]^T (swiglu != 0: rows interleaved (gate, up), y[M, N/2] =
  * silu(gate) * up) on DEVICE buffers through a one-op program of the persistent tensor-core

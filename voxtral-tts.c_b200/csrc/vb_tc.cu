@@ -589,13 +589,16 @@ __global__ void vb_tc_fill_kernel(uint16_t *p, size_t n, uint32_t seed) {
 /* One weight matrix [N, K] of generated values, M activation rows, `reps` launches of the GEMM
  * between two events on the default stream. Needs no model: a measurement and profiling aid
  * with a small memory footprint. epi: TC_EPI_PARTIAL (split-K as the frame uses it) or
- * TC_EPI_SWIGLU_TERMS; tiled: tile-contiguous weight copy as the frame uses it. */
+ * TC_EPI_SWIGLU_TERMS; tiled bit 0: tile-contiguous weight copy as the frame uses it; bit 1: one
+ * copy only, so that a matrix smaller than L2 stays resident (how fast is a launch whose weights
+ * need no HBM?). */
 int tc_probe(int M, int N, int K, int epi, int tiled, int reps, int n_sm, float *ms_out, int *splits_out) {
     if (tc_init() || M < 1 || reps < 1 || (K % kTcBlockK) != 0) return -1;
     const int rp = tc_rows_pad(M);
     if (!rp) return -1;
     /* enough copies of the matrix that successive launches cannot find their weights in L2 */
-    const int copies = (int)((size_t)512 * 1024 * 1024 / ((size_t)N * K * 2)) + 1;
+    const int copies = (tiled & 2) ? 1 : (int)((size_t)512 * 1024 * 1024 / ((size_t)N * K * 2)) + 1;
+    tiled &= 1;
     std::vector<uint16_t *> Wc(copies, nullptr);
     std::vector<TcWeight> wc(copies);
     uint16_t *W = nullptr, *terms = nullptr, *out_terms = nullptr;
