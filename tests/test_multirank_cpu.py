@@ -26,6 +26,8 @@ def _worker(rank, world, port, out):
     seeds = bench.utterance_seeds(rank)
     local_ms = 100.0 * (rank + 1)                 # rank 1 is the slow one
     value, max_ms = bench.aggregate(local_ms, 50, dist, device="cpu")
+    shared_value, _ = bench.aggregate(local_ms, 50, dist, device="cpu", shared=True)
+    assert abs(shared_value * world - value) < 1e-9      # the same frames on every rank count once
     gathered = [None] * world
     dist.all_gather_object(gathered, seeds)
     if rank == 0:
@@ -56,6 +58,9 @@ def test_single_rank_aggregate():
     bench = _bench()
     value, ms = bench.aggregate(4.0, 2, None, device="cpu")
     assert ms == 4.0 and abs(value - 500.0) < 1e-9
+    # tensor parallelism: all ranks worked on the same frames, which therefore count once
+    value, ms = bench.aggregate(4.0, 2, None, device="cpu", shared=True)
+    assert abs(value - 500.0) < 1e-9
 
 
 def test_frame_bytes_match_survey_figures():

@@ -131,7 +131,7 @@ struct Tp {
     unsigned char *arena = nullptr;
     unsigned char *peer[kTpMaxRanks] = {};
     size_t bytes = 0, off_flags = 0;
-    TpSet ll, ac;
+    TpSet ll, ac;              /* decoder rows; acoustic rows (reserved: the acoustic layers are not sliced) */
     unsigned *epoch = nullptr, *tickets = nullptr;   /* local words */
 };
 static Tp g_tp;
