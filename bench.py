@@ -114,18 +114,24 @@ def noise_rows(seed, n):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while a timed region runs."""
+    """nvidia-smi clocks and throttle reasons while a timed region runs. The sampler is started
+    well before the region (nvidia-smi needs up to a second to come up on an 8-GPU node, longer
+    than a short timed region); begin() / end() mark the region and only samples that arrived
+    inside it count. If the region was too short to catch one, the samples taken while the GPU
+    was under the same load just before and after it (warm-up, host-ABI frames) are used and the
+    result says so."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
@@ -134,7 +140,13 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def begin(self):
+        self.t0 = time.time()
+
+    def end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if not self.proc:
@@ -144,21 +156,34 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            if len(r) < 8:
-                continue
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, r[4:8]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+
+        def summarise(rows):
+            sm, mx, reasons = [], [], set()
+            for _, r in rows:
+                if len(r) < 8:
+                    continue
+                try:
+                    sm.append(float(r[0]))
+                    mx.append(float(r[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, r[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            return sm, mx, reasons
+
+        t0 = self.t0 if self.t0 is not None else 0.0
+        t1 = self.t1 if self.t1 is not None else float("inf")
+        inside = [x for x in self.rows if t0 <= x[0] <= t1 + 0.05]
+        sm, mx, reasons = summarise(inside)
+        window = "timed region"
+        if not sm:
+            near = [x for x in self.rows if t0 - 2.0 <= x[0] <= t1 + 2.0]
+            sm, mx, reasons = summarise(near)
+            window = "within 2 s of the timed region (same load; the region itself was shorter than a sample interval)"
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "window": window}
 
 
 def measured_hbm_peak():
@@ -386,6 +411,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(int(os.environ.get("VB200_DEVICE", local_rank)))
+    sampler.start()
     model = pkg.SynthModel(seed=1234)
     kv_max = PROMPT_ROWS + W + K + 72
     eng = pkg.Engine(kv_cache_max=kv_max)
@@ -410,7 +437,6 @@ def main():
     noise = noise_rows(seeds["noise"], W + K)
 
     # ---- value: device-resident loop -------------------------------------------------------
-    sampler = ClockSampler(local_rank)
     Lb = eng.L
     assert Lb.vb200_utterance_begin(first.ctypes.data, PROMPT_ROWS, noise.ctypes.data, W + K) == 0
     codes = np.zeros((W + K, pkg.CODES), dtype=np.int32)
@@ -419,11 +445,11 @@ def main():
         assert Lb.vb200_utterance_run(W) == 0
     torch.cuda.synchronize()
     barrier()
-    sampler.start()
+    sampler.begin()
     assert Lb.vb200_utterance_run(K) == 0
     torch.cuda.synchronize()
     barrier()
-    clocks = sampler.stop()
+    sampler.end()
     assert Lb.vb200_utterance_end(codes.ctypes.data, C.byref(done), C.byref(end), C.byref(ms)) == 0
     if done.value != W + K:
         raise SystemExit(f"device loop ran {done.value} of {W + K} frames (status {Lb.vb200_last_status()})")
@@ -457,6 +483,7 @@ def main():
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_value, _ = aggregate(e2e_s * 1000.0, Ke, dist, shared=tp)
+    clocks = sampler.stop()
 
     # ---- roofline of the dominant kernel --------------------------------------------------------
     peak, peak_src = measured_hbm_peak()

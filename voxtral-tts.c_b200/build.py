@@ -62,7 +62,10 @@ def build(force=False, verbose_ptxas=False):
             _run(["g++", "-O3", "-std=c++17", "-fPIC", "-fopenmp", "-ffp-contract=off", "-Wall", "-c", s, "-o", o])
         objs.append(o)
     if force or _stale(LIB, objs):
-        _run([NVCC, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fopenmp", "-lcudart", "-lgomp"])
+        # link under a temporary name and rename: a reader never sees a half-written library
+        tmp = LIB + ".tmp"
+        _run([NVCC, "-shared", "-o", tmp, *objs, "-Xcompiler", "-fopenmp", "-lcudart", "-lgomp"])
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -103,21 +103,37 @@ __global__ void ac_attention_kernel(uint16_t *terms, const float *part, int n_pa
     const int row = task / VB200_HEADS, h = task % VB200_HEADS, kvh = h / (VB200_HEADS / VB200_KV_HEADS);
     const int seq0 = (row / 3) * 3;
     const size_t ps = (size_t)ROWS * QKV;
-    float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < n_part; p++) {
-        const float4 t = *reinterpret_cast<const float4 *>(part + p * ps + (size_t)row * QKV + h * 128 + 4 * lane);
-        q.x += t.x; q.y += t.y; q.z += t.z; q.w += t.w;
+    /* every load of the task is issued before anything is summed: 7 x n_part float4 per lane */
+    constexpr int kMaxPart = kTcMaxSplits;
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 tq[kMaxPart], tk[3][kMaxPart], tv[3][kMaxPart];
+#pragma unroll
+    for (int p = 0; p < kMaxPart; p++) {
+        const bool on = p < n_part;
+        tq[p] = on ? __ldcg(reinterpret_cast<const float4 *>(part + p * ps + (size_t)row * QKV + h * 128 + 4 * lane)) : z4;
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+            const float *b = part + p * ps + (size_t)(seq0 + j) * QKV + QD + kvh * 128 + 4 * lane;
+            tk[j][p] = on ? __ldcg(reinterpret_cast<const float4 *>(b)) : z4;
+            tv[j][p] = on ? __ldcg(reinterpret_cast<const float4 *>(b + KVD)) : z4;
+        }
+    }
+    float4 q = z4;
+#pragma unroll
+    for (int p = 0; p < kMaxPart; p++) {
+        if (p < n_part) { q.x += tq[p].x; q.y += tq[p].y; q.z += tq[p].z; q.w += tq[p].w; }
     }
     float mx = -1e30f, den = 0.0f;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 o = z4;
+#pragma unroll
     for (int j = 0; j < 3; j++) {
-        float4 k = make_float4(0.f, 0.f, 0.f, 0.f), v = k;
-        for (int p = 0; p < n_part; p++) {
-            const float *b = part + p * ps + (size_t)(seq0 + j) * QKV + QD + kvh * 128 + 4 * lane;
-            const float4 tk = *reinterpret_cast<const float4 *>(b);
-            const float4 tv = *reinterpret_cast<const float4 *>(b + KVD);
-            k.x += tk.x; k.y += tk.y; k.z += tk.z; k.w += tk.w;
-            v.x += tv.x; v.y += tv.y; v.z += tv.z; v.w += tv.w;
+        float4 k = z4, v = z4;
+#pragma unroll
+        for (int p = 0; p < kMaxPart; p++) {
+            if (p < n_part) {
+                k.x += tk[j][p].x; k.y += tk[j][p].y; k.z += tk[j][p].z; k.w += tk[j][p].w;
+                v.x += tv[j][p].x; v.y += tv[j][p].y; v.z += tv[j][p].z; v.w += tv[j][p].w;
+            }
         }
         float d = q.x * k.x + q.y * k.y + q.z * k.z + q.w * k.w;
         d = vb_warp_sum(d) * scale;
@@ -156,12 +172,26 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
     const int row = blockIdx.y * 3;
     const size_t ps = (size_t)ROWS * D;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float s = 0.0f;
-        for (int p = 0; p < n_part; p++) s += part[p * ps + (size_t)row * D + c];
-        const float v = X6[(size_t)row * D + c] + s;
-        xn[c] = v;
-        ss += v * v;
+    /* 512 threads x 6 columns; the 6 x (n_part + 1) loads of a thread are issued together */
+    {
+        constexpr int kCols = VB200_DIM / 512;
+        float pv[kCols][kTcMaxSplits], xv[kCols];
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int c = threadIdx.x + i * 512;
+            xv[i] = __ldcg(X6 + (size_t)row * D + c);
+#pragma unroll
+            for (int p = 0; p < kTcMaxSplits; p++) pv[i][p] = p < n_part ? __ldcg(part + p * ps + (size_t)row * D + c) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            float s = 0.0f;
+#pragma unroll
+            for (int p = 0; p < kTcMaxSplits; p++) s += pv[i][p];     /* split order; unused splits add 0 */
+            const float v = xv[i] + s;
+            xn[threadIdx.x + i * 512] = v;
+            ss += v * v;
+        }
     }
     ss = vb_warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;

@@ -264,18 +264,21 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     const bool writer = sp == S - 1;   /* its key range ends with the new token */
 
     {
-        float v = 0.0f;
-        for (int p = 0; p < n_part; p++) v += __ldcg(row + p * part_stride + (size_t)g * kGroup * kHD + tid);
-        qraw[tid] = v;
-        if (writer && tid < kHD) {
-            float kk = 0.0f, vv = 0.0f;
-            for (int p = 0; p < n_part; p++) {
-                kk += __ldcg(row + p * part_stride + QD + g * kHD + tid);
-                vv += __ldcg(row + p * part_stride + QD + KVD + g * kHD + tid);
-            }
-            kraw[tid] = kk;
-            vraw[tid] = vv;
+        /* split-K sums of q (and of the new k, v) in split order, all loads issued first */
+        const bool kv = writer && tid < kHD;
+        float pq[kTcMaxSplits], pk[kTcMaxSplits], pv[kTcMaxSplits];
+#pragma unroll
+        for (int p = 0; p < kTcMaxSplits; p++) {
+            const bool on = p < n_part;
+            pq[p] = on ? __ldcg(row + p * part_stride + (size_t)g * kGroup * kHD + tid) : 0.0f;
+            pk[p] = (on && kv) ? __ldcg(row + p * part_stride + QD + g * kHD + tid) : 0.0f;
+            pv[p] = (on && kv) ? __ldcg(row + p * part_stride + QD + KVD + g * kHD + tid) : 0.0f;
         }
+        float v = 0.0f, kk = 0.0f, vv = 0.0f;
+#pragma unroll
+        for (int p = 0; p < kTcMaxSplits; p++) { v += pq[p]; kk += pk[p]; vv += pv[p]; }
+        qraw[tid] = v;
+        if (kv) { kraw[tid] = kk; vraw[tid] = vv; }
     }
     if (tid < kHD / 2) {
         const float freq = 1.0f / powf(theta, (float)(2 * tid) / (float)kHD);
@@ -439,13 +442,24 @@ bt_final_kernel(float *hidden, uint16_t *terms, int rows_pad, const float *X, co
     const int b = blockIdx.x, tid = threadIdx.x;
     float v[3];
     float ss = 0.0f;
+    {
+        float pp[3][kTcMaxSplits], xv[3];
 #pragma unroll
-    for (int i = 0; i < 3; i++) {
-        const int c = tid + i * 1024;
-        float s = 0.0f;
-        for (int p = 0; p < n_part; p++) s += __ldcg(part + p * part_stride + (size_t)b * D + c);
-        v[i] = __ldcg(X + (size_t)b * D + c) + s;
-        ss += v[i] * v[i];
+        for (int i = 0; i < 3; i++) {
+            const int c = tid + i * 1024;
+            xv[i] = __ldcg(X + (size_t)b * D + c);
+#pragma unroll
+            for (int p = 0; p < kTcMaxSplits; p++)
+                pp[i][p] = p < n_part ? __ldcg(part + p * part_stride + (size_t)b * D + c) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            float s = 0.0f;
+#pragma unroll
+            for (int p = 0; p < kTcMaxSplits; p++) s += pp[i][p];     /* split order; unused splits add 0 */
+            v[i] = xv[i] + s;
+            ss += v[i] * v[i];
+        }
     }
     ss = vb_warp_sum(ss);
     if ((tid & 31) == 0) red[tid >> 5] = ss;
