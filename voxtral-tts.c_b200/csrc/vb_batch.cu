@@ -207,13 +207,22 @@ __global__ void bt_embed_kernel(float *X, const uint16_t *table, const int *code
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= D) return;
     const int *cb = codes + (size_t)b * kCodeStride;
-    float acc = 0.0f;
-    int base = 0;
-    for (int c = 0; c < n_codes; c++) {
-        const int row = base + __ldcg(cb + c);
-        acc += __uint_as_float((uint32_t)__ldg(table + (size_t)row * D + n) << 16);
-        base += (c == 0) ? rows0 : rows_other;
+    /* the 37 code loads, then the 37 table loads, are each in flight together; the sum keeps
+     * the codebook order */
+    constexpr int kMaxCodes = VB200_CODES;
+    int rowi[kMaxCodes];
+    uint16_t val[kMaxCodes];
+#pragma unroll
+    for (int c = 0; c < kMaxCodes; c++) rowi[c] = c < n_codes ? __ldcg(cb + c) : 0;
+#pragma unroll
+    for (int c = 0; c < kMaxCodes; c++) {
+        const int base = c == 0 ? 0 : rows0 + (c - 1) * rows_other;
+        val[c] = c < n_codes ? __ldg(table + (size_t)(base + rowi[c]) * D + n) : (uint16_t)0;
     }
+    float acc = 0.0f;
+#pragma unroll
+    for (int c = 0; c < kMaxCodes; c++)
+        if (c < n_codes) acc += __uint_as_float((uint32_t)val[c] << 16);
     X[(size_t)b * D + n] = acc;
 }
 
@@ -313,12 +322,13 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     const float4 q4 = *reinterpret_cast<const float4 *>(&qs[hh][4 * lane]);
     float mx = -1e30f, den = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    /* four keys per pass: their eight loads are in flight together, the running-maximum
+    /* eight keys per pass: their sixteen loads are in flight together, the running-maximum
      * update then takes them in key order as the reference does */
-    for (int jb = j0 + ss; jb < j1; jb += 4 * kBtSubsets) {
-        float4 kq[4], vq[4];
+    constexpr int kKeysPerPass = 8;
+    for (int jb = j0 + ss; jb < j1; jb += kKeysPerPass * kBtSubsets) {
+        float4 kq[kKeysPerPass], vq[kKeysPerPass];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < kKeysPerPass; u++) {
             const int j = jb + u * kBtSubsets;
             if (j < j1) {
                 kq[u] = vb_ldcg4(Kc + (size_t)j * KVD + g * kHD + 4 * lane);
@@ -328,16 +338,17 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
                 vq[u] = kq[u];
             }
         }
-        float dq[4];
+        float dq[kKeysPerPass];
 #pragma unroll
-        for (int u = 0; u < 4; u++) dq[u] = q4.x * kq[u].x + q4.y * kq[u].y + q4.z * kq[u].z + q4.w * kq[u].w;
+        for (int u = 0; u < kKeysPerPass; u++)
+            dq[u] = q4.x * kq[u].x + q4.y * kq[u].y + q4.z * kq[u].z + q4.w * kq[u].w;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) dq[u] += __shfl_xor_sync(0xffffffffu, dq[u], off);
+            for (int u = 0; u < kKeysPerPass; u++) dq[u] += __shfl_xor_sync(0xffffffffu, dq[u], off);
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < kKeysPerPass; u++) {
             if (jb + u * kBtSubsets >= j1) break;
             const float d = dq[u] * scale;
             const float4 vv = vq[u];
