@@ -168,6 +168,16 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
     __shared__ float xn[VB200_DIM];
     __shared__ float red[32];
     pdl_launch_dependents();
+    /* this warp's slice of its output row of acoustic_out: static data, fetched before the wait
+     * for the previous kernel (24 BF16 values per lane) */
+    constexpr int kWPerLane = VB200_DIM / 4 / 32;
+    uint16_t wv[kWPerLane];
+    {
+        const int pw = threadIdx.x >> 5, pl = threadIdx.x & 31;
+        const uint16_t *pr = Wout + (size_t)(blockIdx.x * 4 + (pw >> 2)) * VB200_DIM + (pw & 3) * (VB200_DIM / 4) + pl;
+#pragma unroll
+        for (int i = 0; i < kWPerLane; i++) wv[i] = __ldg(pr + 32 * i);
+    }
     pdl_wait();
     const int row = blockIdx.y * 3;
     const size_t ps = (size_t)ROWS * D;
@@ -205,10 +215,10 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
     __shared__ float wsum[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 4 + (warp >> 2), q = warp & 3;
-    const uint16_t *wr = Wout + (size_t)n * D;
     float acc = 0.0f;
-    for (int c = q * (D / 4) + lane; c < (q + 1) * (D / 4); c += 32)
-        acc = fmaf(__uint_as_float((uint32_t)wr[c] << 16), xn[c], acc);
+#pragma unroll
+    for (int i = 0; i < kWPerLane; i++)
+        acc = fmaf(__uint_as_float((uint32_t)wv[i] << 16), xn[q * (D / 4) + lane + 32 * i], acc);
     acc = vb_warp_sum(acc);
     if (lane == 0) wsum[warp] = acc;
     __syncthreads();
