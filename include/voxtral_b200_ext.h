@@ -75,27 +75,6 @@ int vb200_batch_hidden(float *out);
 int vb200_batch_launches_per_frame(void);
 void vb200_batch_close(void);
 
-/* Measurement aid: the decoder's 104 layer GEMMs (every decoder weight byte once) launched
- * back to back `iters` times between two CUDA events, on the single-utterance buffers
- * (which = 0) or on the open batch (which = 1). Returns the elapsed ms, the weight bytes of
- * one sweep and its launch count. */
-int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, int *launches_per_sweep);
-/* Measurement aid without a model: a generated [N, K] BF16 matrix, M activation rows, `reps`
- * launches of the tensor-core GEMM between two CUDA events on the default stream (split-K
- * partial epilogue, or the SwiGLU epilogue when swiglu != 0; tiled bit 0: tile-contiguous weight
- * copy as the frame uses; bit 1: a single copy, which stays in L2 when it fits, instead of
- * rotating through 512 MB of copies). Returns elapsed ms and the split-K factor chosen. */
-int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, float *ms, int *splits);
-/* y[M,N] = x[M,K] . W[N,K]^T (swiglu != 0: rows interleaved (gate, up), y[M, N/2] =
- * silu(gate) * up) on DEVICE buffers through a one-op program of the persistent tensor-core
- * kernel; M <= 10, K a multiple of 64. The first launch is followed by `reps` timed ones
- * (elapsed ms in *ms). A check and measurement aid. */
-int vb200_ptc_linear(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N, int swiglu, int reps,
-                     float *ms);
-/* Measurement aid: the decoder's 104 layer GEMMs as one launch of the persistent tensor-core
- * kernel, `iters` launches between two CUDA events (elapsed ms in *ms). Needs the decoder
- * weights uploaded. */
-int vb200_ptc_decoder_sweep(int iters, float *ms);
 /* Tensor parallelism over the GPUs of one node, one process per GPU (no counterpart in the
  * reference, which is single-GPU: voxtral_tts_cuda.cu:103). Every rank uploads all weights and
  * makes the same vb200_frame / vb200_utterance_* calls with the same inputs; each decoder-layer
@@ -156,12 +135,6 @@ int vb200_tap_read(float *out);
 int vb200_linear_bf16_static(float *d_y, const float *d_x, const uint16_t *d_W, int seq_len,
                              int in_dim, int out_dim);
 int vb200_linear_bf16_static_status(void);
-
-/* How the frame kernel splits a [N,K] matrix product with M activation rows
- * over `n_cta` CTAs (host logic, usable without a GPU). out[0..6] = first row,
- * end row, column passes, columns per pass, rows per chunk, row blocks, chunks of
- * CTA `cta`; the return value is 0 when the shape is runnable, negative if not. */
-int vb200_debug_gemv_plan(int N, int K, int M, int swiglu, int cta, int n_cta, int *out);
 
 int vb200_last_status(void);
 int vb200_sm_count(void);

@@ -7,8 +7,8 @@ oracle/build_oracle.py). Run it where the reference checkout is present:
 
 Inputs are the seeded synthetic tensors of the package (SynthModel, synth_f32),
 so the fixtures hold outputs only:
-  config1_decode.npz   one decoder step at cache length 64 (BASELINE config 1)
-  config2_acoustic.npz one acoustic frame, RNG seed 42 (BASELINE config 2)
+  config1_decode.npz   one decoder step at cache length 64
+  config2_acoustic.npz one acoustic frame, RNG seed 42
   frames3.npz          three chained frames: decode -> acoustic -> re-embed
   primitives.npz       the kernel-level functions on small seeded inputs
 """

@@ -102,8 +102,6 @@ def lib():
         "vb200_tp_connect": (C.c_int, [C.c_void_p]),
         "vb200_tp_close": (None, []),
         "vb200_tp_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, i32p]),
-        "vb200_ptc_decoder_sweep": (C.c_int, [C.c_int, f32p]),
-        "vb200_ptc_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p]),
         "vb200_tc_gemm_probe": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p]),
         "vb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
         "vb200_utterance_engine_ms": (C.c_double, [i32p]),

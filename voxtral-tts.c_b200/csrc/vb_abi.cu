@@ -5,10 +5,10 @@
  */
 #include "../../include/voxtral_b200.h"
 #include "../../include/voxtral_b200_ext.h"
+#include "../../include/voxtral_b200_probe.h"
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
 #include "vb_tc.cuh"
-#include "vb_ptc.cuh"
 
 #include <stddef.h>
 #include <stdio.h>
@@ -181,11 +181,6 @@ int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, fl
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     return tc_probe(M, N, K, swiglu ? TC_EPI_SWIGLU_TERMS : TC_EPI_PARTIAL, tiled, reps, n_sm, ms, splits);
 }
-int vb200_ptc_linear(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N, int swiglu, int reps,
-                     float *ms) {
-    return ptc_linear(d_y, d_x, d_W, M, K, N, swiglu, reps, ms);
-}
-int vb200_ptc_decoder_sweep(int iters, float *ms) { return ptc_decoder_sweep(iters, ms); }
 int vb200_tp_arena(int rank, int world, void *handle_out64) { return tp_arena(rank, world, handle_out64); }
 int vb200_tp_connect(const void *handles) { return tp_connect(handles); }
 void vb200_tp_close(void) { tp_close(); }
@@ -199,7 +194,15 @@ double vb200_utterance_engine_ms(int *launches) {
 
 int vb200_set_option(const char *name, int value) {
     if (!name) return -1;
-    if (!strcmp(name, "ignore_end")) { model().ignore_end = value != 0; return 0; }
+    if (!strcmp(name, "ignore_end")) {
+        const bool v = value != 0;
+        if (v != model().ignore_end) {
+            if (model().st) cudaStreamSynchronize(model().st);
+            model().ignore_end = v;
+            batch_options_changed();
+        }
+        return 0;
+    }
     return -1;
 }
 

@@ -17,11 +17,10 @@
  *   7 Euler steps + FSQ (vb_acoustic_tc.cu), which also advances every utterance.
  *
  * Also here: the tensor-parallel variant of the decoder layers over the GPUs of a node
- * (struct Tp), and two measurement aids (gemm_sweep, ptc_decoder_sweep).
+ * (struct Tp), and a measurement aid (gemm_sweep).
  */
 #include "vb_acoustic_tc.cuh"
 #include "vb_common.cuh"
-#include "vb_ptc.cuh"
 #include "vb_umma.cuh"
 
 #include <math.h>
@@ -601,6 +600,15 @@ void batch_invalidate() {
     g_w.ready = false;
 }
 
+/* Called when an option that is baked into captured launches as a kernel argument changes
+ * (ignore_end): the run-loop graphs are captured again on their next use. */
+void batch_options_changed() {
+    for (Batch *t : {&g_bt, &g_one}) {
+        if (t->exec[0]) { cudaGraphExecDestroy(t->exec[0]); t->exec[0] = nullptr; }
+        if (t->direct_calls[0] > 1) t->direct_calls[0] = 1;
+    }
+}
+
 static void ctx_close(Batch &t);
 void batch_close() { ctx_close(g_bt); }
 
@@ -1023,94 +1031,6 @@ int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int
         *bytes_per_sweep = 2.0 * VB200_DEC_LAYERS * ((double)QKV * D + (double)D * QD + 2.0 * HID * D + (double)D * HID);
     if (launches_per_sweep) *launches_per_sweep = 4 * VB200_DEC_LAYERS;
     return 0;
-}
-
-/* The decoder's 104 layer GEMMs as ONE launch of the persistent tensor-core kernel (ops
- * chained by completion counters; the O projection reads a fixed attention row), `iters`
- * launches between two events: what keeping the weight stream alive across GEMM boundaries
- * buys over the separate launches of gemm_sweep. Measurement aid; allocates and frees its own
- * weight images (6 GB). */
-int ptc_decoder_sweep(int iters, float *ms_out) {
-    Model &m = model();
-    if (!m.inited || !m.llm_ready || iters < 1) return -1;
-    std::vector<void *> own;
-    auto fail = [&]() { bt_free(&own); cudaGetLastError(); return -1; };
-    float *X = nullptr, *qkv = nullptr, *attn = nullptr, *h = nullptr, *part = nullptr, *ssq = nullptr;
-    unsigned *tickets = nullptr, *done = nullptr;
-    int *status = nullptr;
-    POp *d_ops = nullptr;
-    const int n_ops = 4 * VB200_DEC_LAYERS;
-    if (bt_alloc((void **)&X, sizeof(float) * D, &own) || bt_alloc((void **)&qkv, sizeof(float) * QKV, &own) ||
-        bt_alloc((void **)&attn, sizeof(float) * QD, &own) || bt_alloc((void **)&h, sizeof(float) * HID, &own) ||
-        bt_alloc((void **)&part, sizeof(float) * 8 * QKV, &own) || bt_alloc((void **)&ssq, sizeof(float) * 64, &own) ||
-        bt_alloc((void **)&tickets, sizeof(unsigned) * 256, &own) ||
-        bt_alloc((void **)&done, sizeof(unsigned) * n_ops, &own) || bt_alloc((void **)&status, sizeof(int) * 4, &own) ||
-        bt_alloc((void **)&d_ops, sizeof(POp) * n_ops, &own))
-        return fail();
-    std::vector<POp> ops(n_ops);
-    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
-        const LayerDev &L = m.dec[l];
-        const struct { const uint16_t *src; int N, K; } mats[4] = {
-            {L.wqkv, QKV, D}, {L.wo, D, QD}, {L.w13, 2 * HID, D}, {L.w2, D, HID}};
-        uint16_t *img[4];
-        for (int j = 0; j < 4; j++) {
-            if (bt_alloc((void **)&img[j], ptc_image_bytes(mats[j].N, mats[j].K), &own) ||
-                ptc_make_image(img[j], mats[j].src, mats[j].N, mats[j].K, m.st))
-                return fail();
-        }
-        POp *o = &ops[4 * l];
-        for (int j = 0; j < 4; j++) {
-            o[j] = POp();
-            if (ptc_gemm_op(&o[j], 1, mats[j].N, mats[j].K, j == 2 ? P_EPI_SWIGLU : P_EPI_FIXUP, m.sm_count)) return fail();
-            o[j].W = img[j]; o[j].part = part; o[j].tickets = tickets; o[j].eps = VB200_NORM_EPS;
-            o[j].dep = 4 * l + j - 1;
-            o[j].dep_count = o[j].dep >= 0 ? ptc_units(ops[o[j].dep]) : 0;
-        }
-        const int tilesD = D / 128;
-        o[0].x = X; o[0].ldx = D; o[0].gain = L.attn_norm; o[0].y = qkv; o[0].ldy = QKV;
-        if (l > 0) { o[0].ssq = ssq; o[0].ssq_n = tilesD; }
-        o[1].x = attn; o[1].ldx = QD; o[1].y = X; o[1].ldy = D; o[1].res = X; o[1].ssq_out = ssq;
-        o[2].x = X; o[2].ldx = D; o[2].gain = L.ffn_norm; o[2].ssq = ssq; o[2].ssq_n = tilesD; o[2].y = h; o[2].ldy = HID;
-        o[3].x = h; o[3].ldx = HID; o[3].y = X; o[3].ldy = D; o[3].res = X; o[3].ssq_out = ssq;
-    }
-    if (cudaMemcpy(d_ops, ops.data(), sizeof(POp) * n_ops, cudaMemcpyHostToDevice) != cudaSuccess) return fail();
-    if (cudaStreamSynchronize(m.st) != cudaSuccess) return fail();
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return fail();
-    PtcLaunch l;
-    l.d_ops = d_ops; l.n_ops = n_ops; l.d_done = done; l.d_status = status;
-    unsigned epoch = 0;
-    bool ok = true;
-    for (int i = 0; i < 2 && ok; i++) { l.epoch = ++epoch; ok = ptc_launch(l, m.sm_count, m.st) == 0; }
-    cudaEventRecord(e0, m.st);
-    for (int i = 0; i < iters && ok; i++) { l.epoch = ++epoch; ok = ptc_launch(l, m.sm_count, m.st) == 0; }
-    cudaEventRecord(e1, m.st);
-    int st = 0;
-    if (!ok || cudaStreamSynchronize(m.st) != cudaSuccess) st = -1;
-    if (!st) cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
-    if (!st && ms_out) cudaEventElapsedTime(ms_out, e0, e1);
-    if (!st && getenv("VB200_PTC_TIMELINE")) {
-        /* one more launch with CTA 0 writing its per-op timestamps */
-        long long *tl = nullptr;
-        if (bt_alloc((void **)&tl, sizeof(long long) * 8 * n_ops, &own) == 0) {
-            l.epoch = ++epoch; l.d_timeline = tl;
-            if (ptc_launch(l, m.sm_count, m.st) == 0 && cudaStreamSynchronize(m.st) == cudaSuccess) {
-                std::vector<long long> h(8 * n_ops);
-                cudaMemcpy(h.data(), tl, sizeof(long long) * 8 * n_ops, cudaMemcpyDeviceToHost);
-                const long long t0 = h[0];
-                for (int i = 0; i < 12 && i < n_ops; i++) {
-                    fprintf(stderr, "op %2d:", i);
-                    for (int k = 0; k < 8; k++) fprintf(stderr, " %8.2f", (double)(h[8 * i + k] - t0) / 1000.0);
-                    fprintf(stderr, "\n");
-                }
-            }
-        }
-    }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    bt_free(&own);
-    if (st) fprintf(stderr, "voxtral_b200: persistent GEMM sweep failed (status %d)\n", st);
-    return st ? -1 : 0;
 }
 
 /* ---- one utterance on the library's own cache ---- */

@@ -809,12 +809,16 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
     Model &m = g_model;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     const bool aligned = ((uintptr_t)d_x % 16 == 0) && ((uintptr_t)d_W % 16 == 0);
-    if (!aligned || gemv_validate(N, K, 1, VB_EPI_STORE, m.n_cta) != 0) {
+    const bool tc_rows = M >= 2 && (K % kTcBlockK) == 0 && !getenv("VB200_NO_TC");
+    /* the streaming engine is checked for the widest row block it would get (8 rows, unless the
+     * tensor-core GEMM takes the multi-row case) */
+    const int m_engine = tc_rows ? 1 : (M < kMaxM ? M : kMaxM);
+    if (!aligned || (m_engine > 1 && (K & 3)) || gemv_validate(N, K, m_engine, VB_EPI_STORE, m.n_cta) != 0) {
         linear_generic(d_y, d_x, d_W, nullptr, M, K, N, m.st);
         return 0;
     }
     /* Two or more rows: the tensor-core GEMM (fp32 rows as three BF16 terms, vb_tc.cu). */
-    if (M >= 2 && (K % kTcBlockK) == 0 && !getenv("VB200_NO_TC") && tc_init() == 0) {
+    if (tc_rows && tc_init() == 0) {
         TcWeight w;
         if (tc_weight(&w, d_W, N, K) == 0) {
             int rc = 0;
@@ -846,6 +850,10 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
             }
             return rc;
         }
+    }
+    if (gemv_validate(N, K, M < kMaxM ? M : kMaxM, VB_EPI_STORE, m.n_cta) != 0 || (M > 1 && (K & 3))) {
+        linear_generic(d_y, d_x, d_W, nullptr, M, K, N, m.st);
+        return 0;
     }
     for (int r = 0; r < M; r += kMaxM) {
         const int rows = (M - r < kMaxM) ? M - r : kMaxM;

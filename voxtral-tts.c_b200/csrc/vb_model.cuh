@@ -138,13 +138,13 @@ int single_begin(const float *first_embed, int start_pos, const float *noise_all
 int single_run(int n);
 int single_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
 int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int *launches_per_sweep);
-int ptc_decoder_sweep(int iters, float *ms_out);
 int tp_arena(int rank, int world, void *handle_out);
 int tp_connect(const void *handles);
 int tp_plan(int rank, int world, int n_sm, int *out);
 void tp_close();
 void batch_close();
 void batch_invalidate();
+void batch_options_changed();
 void batch_free_all();
 
 int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);

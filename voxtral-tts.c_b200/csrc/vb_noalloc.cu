@@ -85,7 +85,11 @@ extern "C" int vb200_linear_bf16_static(float *d_y, const float *d_x, const uint
     PerDevice &d = g_dev[dev];
 
     const bool aligned = (((uintptr_t)d_x | (uintptr_t)d_W) & 15) == 0;
-    if (!aligned || vb::gemv_validate(out_dim, in_dim, 1, VB_EPI_STORE, d.n_cta) != 0) {
+    /* validated for the widest row block the ops below use: the cross-pass accumulators of a
+     * K > 4096 matrix hold rows-per-CTA x M floats */
+    const int m_max = seq_len < vb::kMaxM ? seq_len : vb::kMaxM;
+    if (!aligned || (seq_len > 1 && (in_dim & 3)) ||
+        vb::gemv_validate(out_dim, in_dim, m_max, VB_EPI_STORE, d.n_cta) != 0) {
         /* shapes the streaming kernel does not take: the plain kernel needs no scratch at all */
         vb::linear_generic(d_y, d_x, d_W, nullptr, seq_len, in_dim, out_dim, 0);
         return cudaGetLastError() == cudaSuccess ? 0 : -1;

@@ -182,7 +182,12 @@ int prefill(const float *embeds, int seq_len, int start_pos) {
             int status = 0;
             cudaMemcpy(&status, &m.d_out->status, sizeof(int), cudaMemcpyDeviceToHost);
             m.last_status = status;
-            if (status) rc = -1;
+            if (status) {
+                /* the word is sticky on the device (kernels only set it from 0): clear it so the
+                 * next call starts clean */
+                cudaMemset(&m.d_out->status, 0, sizeof(int));
+                rc = -1;
+            }
         }
         return rc;
     }
@@ -238,7 +243,12 @@ int prefill(const float *embeds, int seq_len, int start_pos) {
         int status = 0;
         cudaMemcpy(&status, &m.d_out->status, sizeof(int), cudaMemcpyDeviceToHost);
         m.last_status = status;
-        if (status) rc = -1;
+        if (status) {
+            cudaMemset(&m.d_out->status, 0, sizeof(int));
+            cudaMemset(m.bar, 0, 16 * sizeof(unsigned));
+            cudaMemset(m.exitc, 0, 16 * sizeof(unsigned));
+            rc = -1;
+        }
     }
     return rc;
 }

@@ -206,6 +206,7 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     float *rscale = (float *)(abort_flag + 1);   /* [NB] per-row scales */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int issued = 0;   /* producer thread only: pipeline iterations whose loads were requested */
     const int tile = ka.tile0 + blockIdx.x / splits, sp = blockIdx.x % splits;
     const int kblocks = K / kTcBlockK;
     const int kb0 = (int)((long long)kblocks * sp / splits), kb1 = (int)((long long)kblocks * (sp + 1) / splits);
@@ -240,6 +241,7 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             if (ka.a_tiled) tma_load_2d(sa, &mapA, 0, (tile * kblocks + kb0 + it) * kTcTileN, &full[it]);
             else tma_load_2d(sa, &mapA, (kb0 + it) * kTcBlockK, tile * kTcTileN, &full[it]);
         }
+        issued = first;
         pdl_wait();
         if constexpr (TP) {
             if (tp.wait.n > 0) {
@@ -270,6 +272,7 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 #pragma unroll
             for (int j = 0; j < kTcTerms; j++)
                 tma_load_2d(sa + Cfg::kStageA + j * Cfg::kTermB, &mapB, kx, j * rows_pad, &full[s]);
+            issued = it + 1;
         }
     } else if (warp == 5 && lane == 0) {
         /* ---- MMA issuer ---- */
@@ -395,9 +398,12 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     __syncthreads();
     /* abort path: let copies already in flight land before the shared memory goes away */
     if (warp == 4 && lane == 0 && *(volatile int *)abort_flag) {
-        for (int s = 0; s < Cfg::kStages; s++) {
-            long long t0 = clock64();
-            while (!vb_mbar_try_wait(&full[s], 0u) && !vb_mbar_try_wait(&full[s], 1u)) {
+        /* the last load issued into stage s was iteration `it` with it % kStages == s: wait for
+         * exactly that phase of its barrier */
+        const int first_it = issued > Cfg::kStages ? issued - Cfg::kStages : 0;
+        for (int it = first_it; it < issued; it++) {
+            const long long t0 = clock64();
+            while (!vb_mbar_try_wait(&full[it % Cfg::kStages], (uint32_t)(it / Cfg::kStages) & 1u)) {
                 if (clock64() - t0 > VB_WAIT_CYCLES / 8) break;
             }
         }
@@ -460,15 +466,7 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
     tpa.wait = g.wait;
     tpa.wait.status = g.status;
     switch (a.rows_pad) {
-    case 16: {
-        /* Pipeline depth of the 16-row kernel. Measured on the frame loop: 3 stages 3.74 ms per
-         * frame, 4: 3.46, 5: 3.40, 6: 3.36, 8: 3.39, 10: 3.48. With 6 (136 KB) one CTA fits an SM. */
-        static const int st16 = getenv("VB200_TC_STAGES") ? atoi(getenv("VB200_TC_STAGES")) : 6;
-        if (st16 == 4) return launch_tc<16, 4>(w, a, ka, tpa, st);
-        if (st16 == 5) return launch_tc<16, 5>(w, a, ka, tpa, st);
-        if (st16 == 8) return launch_tc<16, 8>(w, a, ka, tpa, st);
-        return launch_tc<16, 6>(w, a, ka, tpa, st);
-    }
+    case 16: return launch_tc<16, 6>(w, a, ka, tpa, st);
     case 64: return launch_tc<64, 5>(w, a, ka, tpa, st);
     case 256: return launch_tc<256, 2>(w, a, ka, tpa, st);
     default: return -1;
