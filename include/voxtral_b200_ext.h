@@ -97,9 +97,15 @@ int vb200_tp_plan(int rank, int world, int n_sm, int *out9);
  * they run on the streaming frame kernel (VB200_NO_TC=1, or per-layer taps enabled). */
 int vb200_frame_on_tensor_cores(void);
 
+/* 1 when the decoder step of vb200_frame / vb200_utterance_* runs as one launch of the
+ * persistent streaming kernel (the default on one GPU; VB200_NO_STREAM=1 selects the GEMM graph). */
+int vb200_frame_on_stream_kernel(void);
+
 /* Options by name. "ignore_end" (0/1): a device-resident run started after this call
- * treats END as an ordinary code, for fixed-length timing runs. Returns -1 for an
- * unknown name. */
+ * treats END as an ordinary code, for fixed-length timing runs. "wait_limit_us": the limit of
+ * every wait inside the streaming decoder kernel (default about one second); when a wait runs
+ * out the call returns -1 and vb200_last_status() names the wait. Returns -1 for an unknown
+ * name or value. */
 int vb200_set_option(const char *name, int value);
 
 /* Copy rows [pos0, pos0+n) of one layer's K and V cache to / from the host

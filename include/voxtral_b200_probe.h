@@ -26,6 +26,17 @@ int vb200_gemm_sweep(int which, int iters, float *ms, double *bytes_per_sweep, i
  * copy as the frame uses; bit 1: a single copy, which stays in L2 when it fits, instead of
  * rotating through 512 MB of copies). Returns elapsed ms and the split-K factor chosen. */
 int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, float *ms, int *splits);
+/* Measurement aid: the streaming decoder-step kernel (26 layers, semantic head, llm token,
+ * argmax: one launch that reads every decoder weight byte once) launched `iters` times back to
+ * back at cache row `pos` between two CUDA events. Returns the elapsed ms and the algorithmic
+ * bytes of one launch (weights + the cache rows attention reads). Needs all weights uploaded. */
+int vb200_stream_step_ms(int pos, int iters, float *ms, double *bytes_per_launch);
+/* Failure-path self test that is safe on a shared GPU: launches the streaming kernel on an op
+ * that waits for a flag nothing ever sets, with a wait limit of limit_us microseconds. The
+ * kernel gives up by itself, records its status and returns; nothing faults and nothing is
+ * killed. Returns the status word the kernel left (47 = the flag wait ran out, as it should),
+ * or -1 when the launch could not be made. */
+int vb200_selftest_wait_expiry(int limit_us);
 /* How the frame kernel splits a [N,K] matrix product with M activation rows
  * over `n_cta` CTAs (host logic, usable without a GPU). out[0..6] = first row,
  * end row, column passes, columns per pass, rows per chunk, row blocks, chunks of

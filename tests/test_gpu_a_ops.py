@@ -55,6 +55,12 @@ LINEAR_SHAPES = [
     (6, 3072, 6144), (6, 4096, 3072), (6, 9216, 3072), (2, 3072, 36), (3, 3072, 1024), (7, 3072, 3072),
     (8, 512, 96), (5, 264, 10), (1, 8, 3), (4, 5000, 33), (1, 36, 3072), (3, 100, 7), (19, 512, 96),
     (1, 12288, 40),
+    # the row counts of the other tensor-core tiles: 48 (eight utterances' acoustic rows, 64-row
+    # tile), 100 and 256 (prefill, 256-row tile), and 257+ (two row blocks)
+    (48, 3072, 6144), (48, 9216, 3072), (100, 3072, 1024), (256, 3072, 6144), (256, 4096, 3072),
+    (256, 9216, 3072), (300, 3072, 256),
+    # K > 4096 with many rows per CTA on the streaming engine (cross-pass accumulators)
+    (8, 9224, 4000),
 ]
 
 

@@ -181,6 +181,11 @@ int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, fl
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     return tc_probe(M, N, K, swiglu ? TC_EPI_SWIGLU_TERMS : TC_EPI_PARTIAL, tiled, reps, n_sm, ms, splits);
 }
+int vb200_stream_step_ms(int pos, int iters, float *ms, double *bytes_per_launch) {
+    return stream_step_time(pos, iters, ms, bytes_per_launch);
+}
+int vb200_selftest_wait_expiry(int limit_us) { return stream_wait_expiry(limit_us); }
+int vb200_frame_on_stream_kernel(void) { return single_on_stream() ? 1 : 0; }
 int vb200_tp_arena(int rank, int world, void *handle_out64) { return tp_arena(rank, world, handle_out64); }
 int vb200_tp_connect(const void *handles) { return tp_connect(handles); }
 void vb200_tp_close(void) { tp_close(); }
@@ -201,6 +206,11 @@ int vb200_set_option(const char *name, int value) {
             model().ignore_end = v;
             batch_options_changed();
         }
+        return 0;
+    }
+    if (!strcmp(name, "wait_limit_us")) {
+        if (value < 1) return -1;
+        model().wait_cycles = (long long)value * 2000;   /* SM clock, about 2 GHz */
         return 0;
     }
     return -1;

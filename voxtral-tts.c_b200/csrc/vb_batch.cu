@@ -21,6 +21,7 @@
  */
 #include "vb_acoustic_tc.cuh"
 #include "vb_common.cuh"
+#include "vb_stream.cuh"
 #include "vb_umma.cuh"
 
 #include <math.h>
@@ -50,6 +51,18 @@ struct BtWeights {
     int s_qkv = 1, s_wo = 1, s_w2 = 1, s_sem = 1, s_llm = 1;
 };
 static BtWeights g_w;
+
+/* Slab-order copies of the decoder's matrices and of the two M = 1 heads, made once per
+ * weight upload, for a grid of g_sw.n_cta CTAs. */
+struct StreamWeights {
+    bool ready = false;
+    int n_cta = 0;
+    uint16_t *wqkv[VB200_DEC_LAYERS] = {}, *wo[VB200_DEC_LAYERS] = {}, *w13[VB200_DEC_LAYERS] = {}, *w2[VB200_DEC_LAYERS] = {};
+    uint16_t *wsem = nullptr, *wllm = nullptr;
+    std::vector<void *> allocs;
+};
+static StreamWeights g_sw;
+
 
 /* Host <-> device blocks of the single-utterance context: one copy each way per frame. */
 struct OneIn {
@@ -98,6 +111,13 @@ struct Batch {
     float *attn_scratch = nullptr;
     unsigned *tickets = nullptr;
     AcBuffers ac;
+    /* the decoder step as one launch of the persistent streaming kernel (vb_stream.cu) */
+    bool stream = false, s_tap = false;
+    const uint16_t *s_table = nullptr;          /* audio table the op lists were built with */
+    float *s_qkv = nullptr, *s_attn = nullptr, *s_h = nullptr, *s_logits = nullptr, *s_scratch = nullptr;
+    unsigned *s_counters = nullptr;             /* [0] grid barrier, [16] exit counter, [32..40) attention tickets */
+    SOp *s_prog[kVariants] = {};
+    int s_n[kVariants] = {};
     cudaGraphExec_t exec[kVariants] = {};
     int direct_calls[kVariants] = {};
     int graph_cap = 0;                          /* frame cap baked into exec[0] */
@@ -598,6 +618,9 @@ void batch_invalidate() {
     drop_graphs(g_bt);
     drop_graphs(g_one);
     g_w.ready = false;
+    g_sw.ready = false;
+    /* the op lists of an open context point at the old copies */
+    if (g_one.open && g_one.stream) ctx_close(g_one);
 }
 
 /* Called when an option that is baked into captured launches as a kernel argument changes
@@ -691,6 +714,124 @@ void batch_free_all() {
     tp_close();
     bt_free(&g_w.allocs);
     g_w.ready = false;
+    bt_free(&g_sw.allocs);
+    g_sw.ready = false;
+}
+
+/* ---- the streaming decoder step (vb_stream.cu) ---- */
+static bool stream_wanted() {
+    static const bool off = getenv("VB200_NO_STREAM") != nullptr;
+    return !off;
+}
+
+static int stream_weights() {
+    Model &m = model();
+    StreamWeights &w = g_sw;
+    if (w.ready) return 0;
+    bt_free(&w.allocs);
+    w.n_cta = stream_max_ctas(m.device);
+    if (w.n_cta <= 0) return -1;
+    const struct { int N, K, epi; } shp[6] = {{QKV, D, S_EPI_STORE}, {D, QD, S_EPI_ADD}, {2 * HID, D, S_EPI_SWIGLU},
+                                              {D, HID, S_EPI_ADD}, {NSEM, D, S_EPI_STORE}, {D, D, S_EPI_STORE}};
+    for (int i = 0; i < 6; i++)
+        if (stream_validate(shp[i].N, shp[i].K, shp[i].epi, w.n_cta)) return -1;
+    auto slab = [&](uint16_t **dst, const uint16_t *src, int i) -> int {
+        void *p = nullptr;
+        if (bt_alloc(&p, stream_slab_bytes(shp[i].N, shp[i].K), &w.allocs)) return -1;
+        *dst = (uint16_t *)p;
+        return stream_make_slabs(*dst, src, shp[i].N, shp[i].K, shp[i].epi, w.n_cta, m.st);
+    };
+    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+        const LayerDev &L = m.dec[l];
+        if (slab(&w.wqkv[l], L.wqkv, 0) || slab(&w.wo[l], L.wo, 1) || slab(&w.w13[l], L.w13, 2) || slab(&w.w2[l], L.w2, 3))
+            return -1;
+    }
+    if (slab(&w.wsem, m.ac_sem_out, 4) || slab(&w.wllm, m.ac_llm_proj, 5)) return -1;
+    if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+    w.ready = true;
+    return 0;
+}
+
+static SOp sop_zero() {
+    SOp o;
+    memset(&o, 0, sizeof(o));
+    return o;
+}
+
+static SOp sop_gemv(int N, int K, int epi, const uint16_t *W, const float *x, float *y) {
+    SOp o = sop_zero();
+    o.type = S_OP_GEMV; o.N = N; o.K = K; o.epi = epi; o.W = W; o.x = x; o.y = y; o.eps = VB200_NORM_EPS;
+    return o;
+}
+
+/* The op lists of the three frame variants (they differ in how the input row is made). */
+static int stream_programs(Batch &t) {
+    Model &m = model();
+    const StreamWeights &w = g_sw;
+    const float scale = 1.0f / sqrtf((float)kHD);
+    unsigned *tickets = t.s_counters + 32;
+    for (int v = 0; v < kVariants; v++) {
+        std::vector<SOp> ops;
+        if (v != 1) {
+            SOp e = sop_zero();
+            e.type = S_OP_EMBED; e.N = D; e.W = m.audio_table; e.p0 = t.codes; e.y = t.X;
+            e.i0 = VB200_CODES; e.i1 = 8194; e.i2 = 23;
+            if (v == 0) e.flags = S_F_SKIP_FRAME0;
+            ops.push_back(e);
+        }
+        for (int l = 0; l < VB200_DEC_LAYERS; l++) {
+            const LayerDev &L = m.dec[l];
+            SOp o = sop_gemv(QKV, D, S_EPI_STORE, w.wqkv[l], t.X, t.s_qkv);
+            o.gain = L.attn_norm;
+            ops.push_back(o);
+            o = sop_zero();
+            o.type = S_OP_ATTN; o.x = t.s_qkv; o.y = t.s_attn; o.p0 = t.s_scratch; o.p1 = tickets;
+            o.p2 = t.kv_k + (size_t)l * t.kv_max * KVD;
+            o.p3 = t.kv_v + (size_t)l * t.kv_max * KVD;
+            o.i0 = VB200_HEADS; o.i1 = VB200_KV_HEADS; o.f0 = scale; o.f1 = VB200_ROPE_THETA;
+            ops.push_back(o);
+            o = sop_gemv(D, QD, S_EPI_ADD, w.wo[l], t.s_attn, t.X);
+            o.res = t.X;
+            if (m.tap_on) o.tap = m.tap + (size_t)(2 * l) * D;
+            ops.push_back(o);
+            o = sop_gemv(2 * HID, D, S_EPI_SWIGLU, w.w13[l], t.X, t.s_h);
+            o.gain = L.ffn_norm;
+            ops.push_back(o);
+            o = sop_gemv(D, HID, S_EPI_ADD, w.w2[l], t.s_h, t.X);
+            o.res = t.X;
+            if (m.tap_on) o.tap = m.tap + (size_t)(2 * l + 1) * D;
+            ops.push_back(o);
+        }
+        /* final RMSNorm (voxtral_tts_llm.c:267) folded into the two heads that read it; the
+         * hidden row itself goes out through xn_out */
+        SOp o = sop_gemv(NSEM, D, S_EPI_STORE, w.wsem, t.X, t.s_logits);
+        o.gain = m.dec_norm; o.bias = m.ac_sem_bias; o.xn_out = t.hidden; o.flags = S_F_NOSYNC;
+        ops.push_back(o);
+        o = sop_gemv(D, D, S_EPI_STORE, w.wllm, t.X, t.ltok);
+        o.gain = m.dec_norm;
+        ops.push_back(o);
+        o = sop_zero();
+        o.type = S_OP_ARGMAX; o.N = NSEM; o.x = t.s_logits; o.i0 = VB200_SEM_VALID_END; o.p2 = t.codes;
+        ops.push_back(o);
+        if (!t.s_prog[v] && bt_alloc((void **)&t.s_prog[v], sizeof(SOp) * 160, &t.allocs)) return -1;
+        if (ops.size() > 160) return -1;
+        if (cudaMemcpyAsync(t.s_prog[v], ops.data(), sizeof(SOp) * ops.size(), cudaMemcpyHostToDevice, m.st) != cudaSuccess ||
+            cudaStreamSynchronize(m.st) != cudaSuccess)
+            return -1;
+        t.s_n[v] = (int)ops.size();
+    }
+    t.s_tap = m.tap_on;
+    t.s_table = m.audio_table;
+    return 0;
+}
+
+static int stream_step(Batch &t, int variant) {
+    Model &m = model();
+    SArgs a;
+    a.ops = t.s_prog[variant]; a.n_ops = t.s_n[variant]; a.dyn = t.dyn;
+    a.bar_counter = t.s_counters; a.exit_counter = t.s_counters + 16; a.status = t.status;
+    a.wait_cycles = m.wait_cycles;
+    return stream_launch(a, g_sw.n_cta, m.st) == cudaSuccess ? 0 : -1;
 }
 
 /* Buffers of a context. single: one utterance on the library's own cache, with pinned
@@ -698,7 +839,10 @@ void batch_free_all() {
 static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames) {
     Model &m = model();
     ctx_close(t);
-    if (bt_weights()) return -1;
+    /* one utterance on one GPU: the decoder step runs on the streaming kernel and needs the slab
+     * copies; everything else (batches, tensor parallelism) runs the GEMM graph on the tile copies */
+    const bool stream = single && !g_tp.on && stream_wanted() && stream_weights() == 0;
+    if (!stream && bt_weights()) return -1;
     t.single = single;
     t.B = n_utt; t.kv_max = kv_max; t.cap = max_frames; t.alloc_cap = max_frames;
     t.slab = (size_t)VB200_DEC_LAYERS * kv_max * KVD;
@@ -749,6 +893,15 @@ static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames
     rc |= bt_alloc((void **)&t.attn_scratch,
                    sizeof(float) * (size_t)B * VB200_KV_HEADS * kBtKeySplits * kGroup * (kHD + 2), &t.allocs);
     rc |= bt_alloc((void **)&t.tickets, sizeof(unsigned) * B * VB200_KV_HEADS, &t.allocs);
+    if (stream) {
+        rc |= bt_alloc((void **)&t.s_qkv, sizeof(float) * QKV, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_attn, sizeof(float) * QD, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_h, sizeof(float) * HID, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_logits, sizeof(float) * NSEM, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_scratch,
+                       sizeof(float) * (size_t)VB200_KV_HEADS * kSKeySplitsMax * kGroup * (kHD + 2), &t.allocs);
+        rc |= bt_alloc((void **)&t.s_counters, sizeof(unsigned) * 64, &t.allocs);
+    }
     if (rc) { ctx_close(t); return -1; }
     if (tc_acts(&t.aD, t.bD, 16, D) || tc_acts(&t.aQ, t.bQ, 16, QD) || tc_acts(&t.aH, t.bH, 16, HID)) {
         ctx_close(t);
@@ -761,6 +914,8 @@ static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames
     t.ac.sd.lat = VB200_FLOW_STEPS * A; t.ac.sd.vel = 2 * A; t.ac.sd.codes = kCodeStride;
     t.ac.sd.noise = (size_t)max_frames * A; t.ac.sd.codes_all = (size_t)max_frames * VB200_CODES;
     if (cudaEventCreate(&t.e0) != cudaSuccess || cudaEventCreate(&t.e1) != cudaSuccess) { ctx_close(t); return -1; }
+    t.stream = stream;
+    if (stream && stream_programs(t)) { ctx_close(t); return -1; }
     t.open = true;
     return 0;
 }
@@ -774,6 +929,13 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
     const float scale = 1.0f / sqrtf((float)kHD);
     const int chunksD = tc_prepare_chunks(D);
     const size_t psD = (size_t)B * D, psQ = (size_t)B * QKV;
+    if (t.stream) {
+        /* decoder step, semantic head + argmax and llm token: one launch */
+        const int variant = embed_mode == EMBED_CODES_AFTER0 ? 0 : embed_mode == EMBED_HOST ? 1 : 2;
+        if (stream_step(t, variant)) return -1;
+        if (acoustic_tc_enqueue_on(t.ac, noise, codes_log, cap, advance, m.ignore_end)) return -1;
+        return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    }
     if (embed_mode != EMBED_HOST)
         launch_pdl(bt_embed_kernel, dim3((D + 255) / 256, B), dim3(256), 0, st, t.X, (const uint16_t *)m.audio_table,
                    (const int *)t.codes, (const VbDyn *)t.dyn, VB200_CODES, 8194, 23, embed_mode);
@@ -1003,7 +1165,7 @@ int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int
     Model &m = model();
     if (which == 0 && one_ready(0)) return -1;
     Batch &t = which == 0 ? g_one : g_bt;
-    if (!t.open || iters < 1) return -1;
+    if (!t.open || iters < 1 || bt_weights()) return -1;
     const BtWeights &w = g_w;
     const int chunksD = tc_prepare_chunks(D);
     TcGemm g;
@@ -1033,18 +1195,95 @@ int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int
     return 0;
 }
 
+/* The streaming decoder step (26 layers, both heads, argmax: one launch) `iters` times back to
+ * back at cache row `pos`, between two events: the kernel's own launch time. Every launch reads
+ * every decoder weight byte once; the cache row `pos` is rewritten with the same values. */
+static int one_status(Batch &t);
+int stream_step_time(int pos, int iters, float *ms_out, double *bytes_per_launch) {
+    Model &m = model();
+    if (!m.inited || !m.llm_ready || !m.ac_ready || iters < 1 || pos < 0 || pos >= m.kv_max || one_ready(0)) return -1;
+    Batch &t = g_one;
+    if (!t.stream) return -1;
+    t.h_in->dyn.pos = pos; t.h_in->dyn.kv_max = m.kv_max; t.h_in->dyn.frame = 0; t.h_in->dyn.done = 0;
+    if (cudaMemcpyAsync(&t.d_in->dyn, &t.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice, m.st) != cudaSuccess) return -1;
+    for (int i = 0; i < 2; i++)
+        if (stream_step(t, 1)) return -1;
+    cudaEventRecord(t.e0, m.st);
+    for (int i = 0; i < iters; i++)
+        if (stream_step(t, 1)) return -1;
+    cudaEventRecord(t.e1, m.st);
+    if (cudaMemcpyAsync(t.h_out, t.d_out, sizeof(OneOut), cudaMemcpyDeviceToHost, m.st) != cudaSuccess ||
+        cudaStreamSynchronize(m.st) != cudaSuccess)
+        return -1;
+    if (ms_out && cudaEventElapsedTime(ms_out, t.e0, t.e1) != cudaSuccess) return -1;
+    if (bytes_per_launch)
+        *bytes_per_launch = 2.0 * VB200_DEC_LAYERS * ((double)QKV * D + (double)D * QD + 2.0 * HID * D + (double)D * HID) +
+                            2.0 * ((double)NSEM * D + (double)D * D) +
+                            2.0 * VB200_DEC_LAYERS * (double)(pos + 1) * KVD * sizeof(float);
+    return one_status(t);
+}
+
+/* A wait inside the streaming kernel that nothing ever satisfies, with a short limit: the kernel
+ * must record its status, leave through the abort path by itself and leave the library usable.
+ * Host-safe by construction (the kernel returns; nothing faults, nothing is killed). Returns the
+ * status word the kernel left (S_ERR_FLAG_WAIT when all is well), or -1. */
+int stream_wait_expiry(int limit_us) {
+    Model &m = model();
+    if (!m.inited || limit_us < 1 || limit_us > 1000000) return -1;
+    const int n_cta = stream_max_ctas(m.device);
+    if (n_cta <= 0) return -1;
+    std::vector<void *> own;
+    unsigned *words = nullptr;      /* [0] the flag nobody sets, [16] barrier, [32] exit, [48] status, [52..56) dyn */
+    SOp *d_ops = nullptr;
+    if (bt_alloc((void **)&words, sizeof(unsigned) * 64, &own) || bt_alloc((void **)&d_ops, sizeof(SOp) * 2, &own)) {
+        bt_free(&own);
+        return -1;
+    }
+    SOp ops[2];
+    for (SOp &o : ops) {
+        o = sop_zero();
+        o.type = S_OP_WAIT; o.p0 = words; o.i0 = 1;
+    }
+    int st = -1;
+    SArgs a;
+    a.ops = d_ops; a.n_ops = 2; a.dyn = (VbDyn *)(words + 52);
+    a.bar_counter = words + 16; a.exit_counter = words + 32; a.status = (int *)(words + 48);
+    a.wait_cycles = (long long)limit_us * 2000;
+    if (cudaMemcpyAsync(d_ops, ops, sizeof(ops), cudaMemcpyHostToDevice, m.st) == cudaSuccess &&
+        stream_launch(a, n_cta, m.st) == cudaSuccess && cudaStreamSynchronize(m.st) == cudaSuccess)
+        cudaMemcpy(&st, words + 48, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaGetLastError();
+    bt_free(&own);
+    return st;
+}
+
 /* ---- one utterance on the library's own cache ---- */
 bool single_tc_usable() {
     Model &m = model();
     static const bool off = getenv("VB200_NO_TC") != nullptr;
-    return !off && m.inited && m.llm_ready && m.ac_ready && acoustic_tc_ready() && !m.tap_on;
+    if (off || !m.inited || !m.llm_ready || !m.ac_ready || !acoustic_tc_ready()) return false;
+    /* per-layer taps exist on the streaming decoder step (and on the fallback engine), not on
+     * the GEMM graph */
+    if (m.tap_on) return !g_tp.on && stream_wanted();
+    return true;
 }
+
+/* 1 when the single-utterance calls run their decoder step on the streaming kernel. */
+bool single_on_stream() { return single_tc_usable() && !g_tp.on && stream_wanted() && (!g_one.open || g_one.stream); }
 
 /* (Re)creates the single-utterance context when needed; the code / noise arrays grow on demand. */
 static int one_ready(int frames) {
     Model &m = model();
     Batch &t = g_one;
-    if (t.open && t.kv_k == m.kv_k && t.kv_max == m.kv_max && frames <= t.alloc_cap) return bt_weights();
+    if (t.open && t.kv_k == m.kv_k && t.kv_max == m.kv_max && frames <= t.alloc_cap) {
+        if (!t.stream) return bt_weights();
+        if (t.s_tap != m.tap_on || t.s_table != m.audio_table) {   /* both are part of the op lists */
+            if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+            drop_graphs(t);
+            return stream_programs(t);
+        }
+        return 0;
+    }
     const int cap = frames > t.alloc_cap ? frames : t.alloc_cap;
     return ctx_open(t, true, 1, m.kv_max, cap);
 }
@@ -1055,6 +1294,7 @@ static int one_status(Batch &t) {
     if (m.last_status == 0) return 0;
     fprintf(stderr, "voxtral_b200: a frame kernel gave up with status %d\n", m.last_status);
     cudaMemsetAsync(t.tickets, 0, sizeof(unsigned) * VB200_KV_HEADS, m.st);
+    if (t.s_counters) cudaMemsetAsync(t.s_counters, 0, sizeof(unsigned) * 64, m.st);
     cudaMemsetAsync(t.status, 0, sizeof(int) * 4, m.st);
     cudaStreamSynchronize(m.st);
     return -1;

@@ -81,6 +81,7 @@ struct Model {
     bool tap_on = false;
     int prefetch_chunks = kPrefetchChunks;   /* VB200_PREFETCH overrides */
     bool ignore_end = false;      /* timed runs: an END code does not stop a device-resident run */
+    long long wait_cycles = 2000000000LL;   /* limit of the waits inside the streaming decoder kernel (~1 s) */
     Program p_llm, p_ac, p_frame, p_chain, p_pv, p_run_first, p_run_next;
     float *noise_all = nullptr;   /* device-resident run: [frames, 36] */
     int *codes_all = nullptr;     /* [frames, 37] */
@@ -138,6 +139,9 @@ int single_begin(const float *first_embed, int start_pos, const float *noise_all
 int single_run(int n);
 int single_end(int *codes_out, int *frames_done, int *hit_end, float *device_ms);
 int gemm_sweep(int which, int iters, float *ms_out, double *bytes_per_sweep, int *launches_per_sweep);
+int stream_step_time(int pos, int iters, float *ms_out, double *bytes_per_launch);
+int stream_wait_expiry(int limit_us);
+bool single_on_stream();
 int tp_arena(int rank, int world, void *handle_out);
 int tp_connect(const void *handles);
 int tp_plan(int rank, int world, int n_sm, int *out);
