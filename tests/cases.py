@@ -2,7 +2,8 @@
 
 They follow the benchmark configurations: config 1 = one decoder step with a cache
 pre-filled with 64 positions of N(0,1); config 2 = one acoustic frame on a
-N(0,1) hidden state."""
+N(0,1) hidden state; config 3 = a 256-row prompt (224 voice-embedding rows ~N(0,0.5), then 32
+token rows with ids in [1000, 131072)); config 4 = that prompt followed by generated frames."""
 import numpy as np
 
 MODEL_SEED = 1234
@@ -43,3 +44,19 @@ def primitive_inputs(pkg):
         "gate": pkg.synth_f32(1024, s, "prim.gate"),
         "up": pkg.synth_f32(1024, s, "prim.up"),
     }
+
+
+CONFIG4_SEED = 4242
+CONFIG4_FRAMES = 16
+GOLDEN_LAYERS = (0, 12, 25)
+GOLDEN_ROWS = (0, 100, 255)
+
+
+def config3_prompt(pkg, model):
+    voice = pkg.synth_f32((224, 3072), INPUT_SEED, "cfg3.voice", 0.0, 0.5)
+    ids = 1000 + (pkg.synth_bf16(32, INPUT_SEED, "cfg3.ids").astype(np.int64) * 2 % (131072 - 1000))
+    return np.concatenate([voice, model.token_rows(ids)], axis=0)
+
+
+def config4_first_embed(model):
+    return model.token_rows([24])[0]          # embed(AUDIO), voxtral_tts.c:295

@@ -11,6 +11,10 @@ so the fixtures hold outputs only:
   config2_acoustic.npz one acoustic frame, RNG seed 42
   frames3.npz          three chained frames: decode -> acoustic -> re-embed
   primitives.npz       the kernel-level functions on small seeded inputs
+With --full (minutes of CPU; uses the OpenBLAS build, as the reference's `make blas` does):
+  config3_prefill.npz  cache rows after a 256-row prompt: three rows of three layers in full,
+                       and the norm of every row of those layers
+  config4_slice.npz    that prompt followed by 16 generated frames: codes, hidden rows, RNG state
 """
 import os
 import sys
@@ -21,11 +25,45 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 from conftest import load_package  # noqa: E402
 import oracle_bind as ob  # noqa: E402
-from cases import (MODEL_SEED, config1_inputs, config2_inputs, frames_inputs, primitive_inputs)  # noqa: E402
+from cases import (CONFIG4_FRAMES, CONFIG4_SEED, GOLDEN_LAYERS, GOLDEN_ROWS, MODEL_SEED, config1_inputs,  # noqa: E402
+                   config2_inputs, config3_prompt, config4_first_embed, frames_inputs, primitive_inputs)
+
+
+def full_size(pkg, model):
+    """Configurations 3 and 4 at their full size on the reference's OpenBLAS build."""
+    ref = ob.load_ref("blas")
+    if ref is None:
+        raise SystemExit("oracle/_ref/libvoxref_blas.so missing: run oracle/build_oracle.py with the reference present")
+    rows = config3_prompt(pkg, model)
+    M = rows.shape[0]
+    ref.open(model, kv_max=M + CONFIG4_FRAMES + 8)
+    ref.llm_prefill(rows)
+    assert ref.kv_len() == M
+    k, v = ref.kv()
+    L, R = list(GOLDEN_LAYERS), list(GOLDEN_ROWS)
+    np.savez_compressed(os.path.join(HERE, "config3_prefill.npz"),
+                        k_rows=k[L][:, R].copy(), v_rows=v[L][:, R].copy(),
+                        k_norms=np.linalg.norm(k[L, :M].astype(np.float64), axis=-1).astype(np.float32),
+                        v_norms=np.linalg.norm(v[L, :M].astype(np.float64), axis=-1).astype(np.float32))
+    ref.seed(CONFIG4_SEED)
+    e = config4_first_embed(model)
+    codes, hidden = [], []
+    for _ in range(CONFIG4_FRAMES):
+        h = ref.llm_forward(e)
+        c = ref.acoustic_forward(h)
+        codes.append(c)
+        hidden.append(h)
+        e = ref.audio_embed(c)
+    np.savez_compressed(os.path.join(HERE, "config4_slice.npz"), codes=np.stack(codes), hidden=np.stack(hidden),
+                        rng_after=np.uint64(ref.rng_state()))
+    ref.close()
+    print("full-size fixtures written to", HERE)
 
 
 def main():
     pkg = load_package()
+    if "--full" in sys.argv:
+        return full_size(pkg, pkg.SynthModel(seed=MODEL_SEED))
     ref = ob.load_ref("noblas")
     if ref is None:
         raise SystemExit("oracle/_ref/libvoxref_noblas.so missing: run oracle/build_oracle.py with the reference present")

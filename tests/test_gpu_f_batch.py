@@ -104,3 +104,26 @@ def test_rejects_bad_arguments(pkg, engine):
     assert L.vb200_batch_open(2, 64, 4) == 0
     assert L.vb200_batch_prefill(2, None, 4) == -1
     L.vb200_batch_close()
+
+
+def test_eight_utterances_one_frame_against_the_oracle(pkg, engine, oracle, synth_model):
+    """A full batch (8 utterances: M = 8 decoder rows, M = 48 acoustic rows) compared with the CPU
+    oracle directly, not with the single-utterance GPU path: hidden rows within 2e-3, semantic
+    codes identical, acoustic codes identical up to one rounding-boundary slip per utterance."""
+    n = 8
+    first = synth_model.token_rows([24])[0]
+    prompts = [_prompt(pkg, synth_model, 4 + u, 2, 300 + u) for u in range(n)]
+    states = [oracle.seed(1300 + u) for u in range(n)]
+    noise = np.stack([oracle.randn(states[u], 36)[0].reshape(1, 36) for u in range(n)])
+    codes, ends, hidden, _ = engine.batch(prompts, np.stack([first] * n), noise)
+    dec, ac = oracle.decoder(synth_model), oracle.acoustic(synth_model)
+    for u, p in enumerate(prompts):
+        M = p.shape[0]
+        k = np.zeros((26, 32, 1024), dtype=np.float32)
+        v = np.zeros_like(k)
+        oracle.llm_prefill(dec, k, v, 0, p)
+        h_ref = oracle.llm_forward(dec, k, v, M, first)
+        assert rel_l2(hidden[u], h_ref) < 2e-3, u
+        ref_codes, _, _, _ = oracle.acoustic_forward(ac, states[u], h_ref)
+        assert codes[u].shape == (1, 37) and codes[u][0, 0] == ref_codes[0], u
+        assert int(np.sum(codes[u][0] != ref_codes)) <= 1, u

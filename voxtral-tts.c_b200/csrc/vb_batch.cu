@@ -1242,13 +1242,13 @@ int stream_wait_expiry(int limit_us) {
     SOp ops[2];
     for (SOp &o : ops) {
         o = sop_zero();
-        o.type = S_OP_WAIT; o.p0 = words; o.i0 = 1;
+        o.type = S_OP_WAIT; o.p0 = words; o.i0 = 1; o.i1 = limit_us;
     }
     int st = -1;
     SArgs a;
     a.ops = d_ops; a.n_ops = 2; a.dyn = (VbDyn *)(words + 52);
     a.bar_counter = words + 16; a.exit_counter = words + 32; a.status = (int *)(words + 48);
-    a.wait_cycles = (long long)limit_us * 2000;
+    a.wait_cycles = m.wait_cycles;       /* the other waits keep the ordinary limit: the flag wait runs out first */
     if (cudaMemcpyAsync(d_ops, ops, sizeof(ops), cudaMemcpyHostToDevice, m.st) == cudaSuccess &&
         stream_launch(a, n_cta, m.st) == cudaSuccess && cudaStreamSynchronize(m.st) == cudaSuccess)
         cudaMemcpy(&st, words + 48, sizeof(int), cudaMemcpyDeviceToHost);

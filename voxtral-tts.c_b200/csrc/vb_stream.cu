@@ -26,7 +26,9 @@
  * the side, and 1/sqrt(mean + eps) multiplies the finished sums (voxtral_tts_kernels.c:333-349).
  *
  * Every wait (mbarrier, grid barrier, flag) is bounded by SArgs.wait_cycles; on expiry a
- * status code is stored, the CTA raises its abort flag, every role falls through, and the
+ * status code is stored and the CTA raises its abort flag. Threads that have given up keep
+ * taking part in the CTA barriers of the op they are in, the whole CTA leaves the op loop at
+ * the next grid barrier, the other CTAs follow when they see the status word, and the
  * producer waits (bounded) for its copies in flight before the CTA retires.
  */
 #include "vb_stream.cuh"
@@ -44,7 +46,8 @@ struct SSmem {
     float red[kSConsumerWarps];
     uint64_t full[kSSlots];
     uint64_t empty[kSSlots];
-    int abort_flag;
+    int abort_flag;     /* raised by any thread of the CTA, at any time */
+    int abort_seen;     /* the abort flag as sampled inside the last grid barrier: the same for every consumer thread */
     int last_flag;
 };
 
@@ -84,22 +87,29 @@ VB_DEVINL bool s_mbar_wait(SCtx &c, uint64_t *bar, uint32_t parity) {
     }
 }
 
-/* Grid barrier of the consumer warps. */
-__device__ void s_grid_sync(SCtx &c) {
+/* Grid barrier of the consumer warps. Returns true when the kernel is giving up; the answer is
+ * sampled by one thread between the two CTA barriers, so every consumer thread of the CTA gets
+ * the same one and the threads leave the op loop together (a thread that has given up still
+ * takes part in every CTA barrier on its way: nobody is left waiting at a bar.sync). */
+__device__ bool s_grid_sync(SCtx &c) {
     c.barrier_epoch++;
     vb_named_bar(1, kSConsumerThreads);
-    if (c.tid == 0 && !s_aborted(c)) {
-        __threadfence();
-        vb_atomic_add_release_gpu(c.a.bar_counter, 1u);
-        const unsigned target = c.barrier_epoch * gridDim.x;
-        const long long t0 = clock64();
-        while (vb_ld_acquire_gpu(c.a.bar_counter) < target) {
-            if (vb_ld_relaxed_gpu_s32(c.a.status) != 0) { *(volatile int *)&c.s->abort_flag = 1; break; }
-            if (clock64() - t0 > c.a.wait_cycles) { s_raise(c, S_ERR_GRID_BARRIER); break; }
+    if (c.tid == 0) {
+        if (!s_aborted(c)) {
+            __threadfence();
+            vb_atomic_add_release_gpu(c.a.bar_counter, 1u);
+            const unsigned target = c.barrier_epoch * gridDim.x;
+            const long long t0 = clock64();
+            while (vb_ld_acquire_gpu(c.a.bar_counter) < target) {
+                if (vb_ld_relaxed_gpu_s32(c.a.status) != 0) { *(volatile int *)&c.s->abort_flag = 1; break; }
+                if (clock64() - t0 > c.a.wait_cycles) { s_raise(c, S_ERR_GRID_BARRIER); break; }
+            }
+            __threadfence();
         }
-        __threadfence();
+        c.s->abort_seen = s_aborted(c) ? 1 : 0;
     }
     vb_named_bar(1, kSConsumerThreads);
+    return *(volatile int *)&c.s->abort_seen != 0;
 }
 
 /* ------------------------------------------------------------------ producer */
@@ -189,7 +199,7 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
         c.chunk_counter++;
         if (!s_mbar_wait(c, &s->full[slot], use & 1u)) {
             if (!s_aborted(c)) s_raise(c, S_ERR_FULL_WAIT);
-            return;
+            break;      /* carry on to the CTA barriers below; the results no longer matter */
         }
         const int kb0 = ch * p.kbs, kb1 = min(kb0 + p.kbs, p.kblocks);
         int kb = kb0 + ((kres - (kb0 % kmod)) + kmod) % kmod;
@@ -489,14 +499,16 @@ __device__ void s_argmax(SCtx &c, const SOp &op) {
 }
 
 /* Waits until the word at op.p0 reaches i0 (something outside this kernel publishes it).
- * One thread of CTA 0 polls; when the limit passes it records S_ERR_FLAG_WAIT and every CTA
- * leaves through the abort path at its next barrier. */
+ * One thread of CTA 0 polls; its limit is i1 microseconds when i1 > 0, else the kernel's. When
+ * the limit passes it records S_ERR_FLAG_WAIT and every CTA leaves through the abort path at
+ * its next barrier. */
 __device__ void s_wait_flag(SCtx &c, const SOp &op) {
     if (blockIdx.x != 0 || c.tid != 0) return;
     const unsigned *flag = (const unsigned *)op.p0;
+    const long long limit = op.i1 > 0 ? (long long)op.i1 * 2000 : c.a.wait_cycles;
     const long long t0 = clock64();
     while (vb_ld_acquire_gpu(flag) < (unsigned)op.i0) {
-        if (clock64() - t0 > c.a.wait_cycles) { s_raise(c, S_ERR_FLAG_WAIT); break; }
+        if (clock64() - t0 > limit) { s_raise(c, S_ERR_FLAG_WAIT); break; }
     }
 }
 
@@ -519,6 +531,7 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
             vb_mbar_init(&s->empty[i], kSConsumerWarps);
         }
         s->abort_flag = 0;
+        s->abort_seen = 0;
         s->last_flag = 0;
         vb_mbar_init_fence();
     }
@@ -527,7 +540,7 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
     if (c.warp == kSConsumerWarps) {
         if (c.lane == 0) s_produce(c);
     } else {
-        for (int oi = 0; oi < a.n_ops && !s_aborted(c); oi++) {
+        for (int oi = 0; oi < a.n_ops; oi++) {
             const SOp &op = a.ops[oi];
             switch (op.type) {
             case S_OP_GEMV:   s_gemv(c, op); break;
@@ -537,7 +550,7 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
             case S_OP_WAIT:   s_wait_flag(c, op); break;
             default: if (c.tid == 0) s_raise(c, S_ERR_BAD_OP); break;
             }
-            if (!(op.flags & S_F_NOSYNC) && oi + 1 < a.n_ops) s_grid_sync(c);
+            if (!(op.flags & S_F_NOSYNC) && oi + 1 < a.n_ops && s_grid_sync(c)) break;
         }
     }
 
