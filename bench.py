@@ -280,11 +280,32 @@ def micro_gemm(args):
                       "achieved_gbs": gbs, "frac_of_peak": gbs / peak, "peak_source": src}))
 
 
+def micro_stream(args):
+    """The streaming decoder-step kernel alone on `--ops` GEMV ops over generated [n, k] matrices
+    (no model upload; rotating copies so no op finds its weights in L2), with or without a grid
+    barrier after every op. A small case for profiling and the per-shape table."""
+    pkg = load_package()
+    L = pkg.lib()
+    ms, nb = C.c_float(0.0), C.c_double(0.0)
+    rc = L.vb200_stream_probe(args.n, args.k, args.ops, 0 if args.no_sync else 1, args.reps, C.byref(ms), C.byref(nb))
+    if rc != 0:
+        raise SystemExit(f"vb200_stream_probe failed ({rc})")
+    peak, src = measured_hbm_peak()
+    us = ms.value * 1000.0 / args.reps
+    gbs = nb.value / (us * 1e-6) / 1e9
+    print(json.dumps({"micro": "stream", "k": args.k, "n": args.n, "ops_per_launch": args.ops, "launches": args.reps,
+                      "grid_barrier_after_each_op": not args.no_sync, "us_per_launch": us, "us_per_op": us / args.ops,
+                      "weight_bytes_per_launch": nb.value, "achieved_gbs": gbs, "frac_of_peak": gbs / peak,
+                      "peak_source": src}))
+
+
 def micro(args):
     """One GEMV op of the frame kernel through tts_cuda_linear_bf16 on device buffers:
     y[m,n] = x[m,k] . W[n,k]^T. Not the headline metric: a small, self-contained case for profiling."""
     if args.micro == "gemm":
         return micro_gemm(args)
+    if args.micro == "stream":
+        return micro_stream(args)
     pkg = load_package()
     eng = pkg.Engine(kv_cache_max=64)
     L = eng.L
@@ -349,7 +370,9 @@ def main():
     ap.add_argument("--untiled", action="store_true", help="--micro gemm: row-major weights instead of the tiled copy")
     ap.add_argument("--l2-resident", action="store_true",
                     help="--micro gemm: one weight copy (stays in L2 when it fits) instead of rotating copies")
-    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm"],
+    ap.add_argument("--ops", type=int, default=16, help="--micro stream: GEMV ops per launch")
+    ap.add_argument("--no-sync", action="store_true", help="--micro stream: no grid barrier between the ops")
+    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm", "stream"],
                     help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--k", type=int, default=3072)

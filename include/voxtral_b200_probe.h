@@ -31,6 +31,11 @@ int vb200_tc_gemm_probe(int M, int N, int K, int swiglu, int tiled, int reps, fl
  * back at cache row `pos` between two CUDA events. Returns the elapsed ms and the algorithmic
  * bytes of one launch (weights + the cache rows attention reads). Needs all weights uploaded. */
 int vb200_stream_step_ms(int pos, int iters, float *ms, double *bytes_per_launch);
+/* Measurement aid without a model: the streaming kernel on `n_ops` GEMV ops over generated
+ * [N, K] BF16 matrices (rotating copies, so no op finds its weights in L2), with (sync = 1) or
+ * without a grid barrier after every op; `reps` launches between two CUDA events on the default
+ * stream. Returns elapsed ms and the weight bytes of one launch. */
+int vb200_stream_probe(int N, int K, int n_ops, int sync, int reps, float *ms, double *bytes_per_launch);
 /* Failure-path self test that is safe on a shared GPU: launches the streaming kernel on an op
  * that waits for a flag nothing ever sets, with a wait limit of limit_us microseconds. The
  * kernel gives up by itself, records its status and returns; nothing faults and nothing is

@@ -106,6 +106,7 @@ def lib():
         "vb200_set_option": (C.c_int, [C.c_char_p, C.c_int]),
         "vb200_stream_step_ms": (C.c_int, [C.c_int, C.c_int, f32p, C.POINTER(C.c_double)]),
         "vb200_selftest_wait_expiry": (C.c_int, [C.c_int]),
+        "vb200_stream_probe": (C.c_int, [C.c_int] * 5 + [f32p, C.POINTER(C.c_double)]),
         "vb200_frame_on_stream_kernel": (C.c_int, []),
         "vb200_utterance_engine_ms": (C.c_double, [i32p]),
         "vb200_utterance_end": (C.c_int, [C.c_void_p, i32p, i32p, f32p]),

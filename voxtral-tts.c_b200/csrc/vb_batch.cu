@@ -114,10 +114,14 @@ struct Batch {
     /* the decoder step as one launch of the persistent streaming kernel (vb_stream.cu) */
     bool stream = false, s_tap = false;
     const uint16_t *s_table = nullptr;          /* audio table the op lists were built with */
-    float *s_qkv = nullptr, *s_attn = nullptr, *s_h = nullptr, *s_logits = nullptr, *s_scratch = nullptr;
-    unsigned *s_counters = nullptr;             /* [0] grid barrier, [16] exit counter, [32..40) attention tickets */
+    float *s_qkv = nullptr, *s_attn = nullptr, *s_h = nullptr, *s_logits = nullptr;
+    unsigned *s_counters = nullptr;             /* [0] grid barrier, [16] exit counter */
     SOp *s_prog[kVariants] = {};
-    int s_n[kVariants] = {};
+    SWeights *s_wl[kVariants] = {};             /* the producer's view of each op list: its GEMV weights in order */
+    int s_n[kVariants] = {}, s_nw[kVariants] = {};
+    std::vector<SOp> s_host;                    /* host copy of variant 1's op list (measurement aid) */
+    SOp *s_prog_dbg = nullptr;
+    SWeights *s_wl_dbg = nullptr;
     cudaGraphExec_t exec[kVariants] = {};
     int direct_calls[kVariants] = {};
     int graph_cap = 0;                          /* frame cap baked into exec[0] */
@@ -764,12 +768,18 @@ static SOp sop_gemv(int N, int K, int epi, const uint16_t *W, const float *x, fl
     return o;
 }
 
+static std::vector<SWeights> stream_weight_list(const std::vector<SOp> &ops) {
+    std::vector<SWeights> wl;
+    for (const SOp &o : ops)
+        if (o.type == S_OP_GEMV) wl.push_back(SWeights{o.W, o.N, o.K, o.epi, 0});
+    return wl;
+}
+
 /* The op lists of the three frame variants (they differ in how the input row is made). */
 static int stream_programs(Batch &t) {
     Model &m = model();
     const StreamWeights &w = g_sw;
     const float scale = 1.0f / sqrtf((float)kHD);
-    unsigned *tickets = t.s_counters + 32;
     for (int v = 0; v < kVariants; v++) {
         std::vector<SOp> ops;
         if (v != 1) {
@@ -785,7 +795,7 @@ static int stream_programs(Batch &t) {
             o.gain = L.attn_norm;
             ops.push_back(o);
             o = sop_zero();
-            o.type = S_OP_ATTN; o.x = t.s_qkv; o.y = t.s_attn; o.p0 = t.s_scratch; o.p1 = tickets;
+            o.type = S_OP_ATTN; o.x = t.s_qkv; o.y = t.s_attn;
             o.p2 = t.kv_k + (size_t)l * t.kv_max * KVD;
             o.p3 = t.kv_v + (size_t)l * t.kv_max * KVD;
             o.i0 = VB200_HEADS; o.i1 = VB200_KV_HEADS; o.f0 = scale; o.f1 = VB200_ROPE_THETA;
@@ -813,12 +823,18 @@ static int stream_programs(Batch &t) {
         o = sop_zero();
         o.type = S_OP_ARGMAX; o.N = NSEM; o.x = t.s_logits; o.i0 = VB200_SEM_VALID_END; o.p2 = t.codes;
         ops.push_back(o);
-        if (!t.s_prog[v] && bt_alloc((void **)&t.s_prog[v], sizeof(SOp) * 160, &t.allocs)) return -1;
+        if (!t.s_prog[v] && (bt_alloc((void **)&t.s_prog[v], sizeof(SOp) * 160, &t.allocs) ||
+                             bt_alloc((void **)&t.s_wl[v], sizeof(SWeights) * 160, &t.allocs)))
+            return -1;
         if (ops.size() > 160) return -1;
+        const std::vector<SWeights> wl = stream_weight_list(ops);
         if (cudaMemcpyAsync(t.s_prog[v], ops.data(), sizeof(SOp) * ops.size(), cudaMemcpyHostToDevice, m.st) != cudaSuccess ||
+            cudaMemcpyAsync(t.s_wl[v], wl.data(), sizeof(SWeights) * wl.size(), cudaMemcpyHostToDevice, m.st) != cudaSuccess ||
             cudaStreamSynchronize(m.st) != cudaSuccess)
             return -1;
         t.s_n[v] = (int)ops.size();
+        t.s_nw[v] = (int)wl.size();
+        if (v == 1) t.s_host = ops;
     }
     t.s_tap = m.tap_on;
     t.s_table = m.audio_table;
@@ -829,8 +845,12 @@ static int stream_step(Batch &t, int variant) {
     Model &m = model();
     SArgs a;
     a.ops = t.s_prog[variant]; a.n_ops = t.s_n[variant]; a.dyn = t.dyn;
+    a.wl = t.s_wl[variant]; a.n_wl = t.s_nw[variant];
     a.bar_counter = t.s_counters; a.exit_counter = t.s_counters + 16; a.status = t.status;
     a.wait_cycles = m.wait_cycles;
+    a.dbg = getenv("VB200_STREAM_DBG") ? atoi(getenv("VB200_STREAM_DBG")) : 0;
+    a.pf_bytes = getenv("VB200_STREAM_PF") ? atoi(getenv("VB200_STREAM_PF")) : kSPrefetchBytes;
+    a.timeline = nullptr;
     return stream_launch(a, g_sw.n_cta, m.st) == cudaSuccess ? 0 : -1;
 }
 
@@ -898,8 +918,6 @@ static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames
         rc |= bt_alloc((void **)&t.s_attn, sizeof(float) * QD, &t.allocs);
         rc |= bt_alloc((void **)&t.s_h, sizeof(float) * HID, &t.allocs);
         rc |= bt_alloc((void **)&t.s_logits, sizeof(float) * NSEM, &t.allocs);
-        rc |= bt_alloc((void **)&t.s_scratch,
-                       sizeof(float) * (size_t)VB200_KV_HEADS * kSKeySplitsMax * kGroup * (kHD + 2), &t.allocs);
         rc |= bt_alloc((void **)&t.s_counters, sizeof(unsigned) * 64, &t.allocs);
     }
     if (rc) { ctx_close(t); return -1; }
@@ -1204,6 +1222,38 @@ int stream_step_time(int pos, int iters, float *ms_out, double *bytes_per_launch
     if (!m.inited || !m.llm_ready || !m.ac_ready || iters < 1 || pos < 0 || pos >= m.kv_max || one_ready(0)) return -1;
     Batch &t = g_one;
     if (!t.stream) return -1;
+    /* VB200_STREAM_DISSECT (measurement only; results are meaningless): 1 = no grid barriers,
+     * 2 = no attention ops, 3 = barriers only (every op replaced by an empty one) */
+    const int mode = getenv("VB200_STREAM_DISSECT") ? atoi(getenv("VB200_STREAM_DISSECT")) : 0;
+    SOp *prog = t.s_prog[1];
+    int n_prog = t.s_n[1];
+    SWeights *wlp = t.s_wl[1];
+    int n_wl = t.s_nw[1];
+    if (mode > 0) {
+        std::vector<SOp> ops;
+        for (SOp o : t.s_host) {
+            if (mode == 1) o.flags |= S_F_NOSYNC;
+            if (mode == 2 && o.type == S_OP_ATTN) continue;
+            if (mode == 3) { const int f = o.flags; o = sop_zero(); o.type = S_OP_WAIT; o.p0 = t.s_counters + 48; o.i0 = 0; o.flags = f; }
+            ops.push_back(o);
+        }
+        if (!t.s_prog_dbg && (bt_alloc((void **)&t.s_prog_dbg, sizeof(SOp) * 160, &t.allocs) ||
+                              bt_alloc((void **)&t.s_wl_dbg, sizeof(SWeights) * 160, &t.allocs)))
+            return -1;
+        const std::vector<SWeights> wl = stream_weight_list(ops);
+        if (cudaMemcpy(t.s_prog_dbg, ops.data(), sizeof(SOp) * ops.size(), cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(t.s_wl_dbg, wl.data(), sizeof(SWeights) * wl.size(), cudaMemcpyHostToDevice) != cudaSuccess)
+            return -1;
+        prog = t.s_prog_dbg;
+        n_prog = (int)ops.size();
+        wlp = t.s_wl_dbg;
+        n_wl = (int)wl.size();
+    }
+    struct Restore {
+        Batch &t; SOp *p; int n; SWeights *w; int nw;
+        ~Restore() { t.s_prog[1] = p; t.s_n[1] = n; t.s_wl[1] = w; t.s_nw[1] = nw; }
+    } restore{t, t.s_prog[1], t.s_n[1], t.s_wl[1], t.s_nw[1]};
+    t.s_prog[1] = prog; t.s_n[1] = n_prog; t.s_wl[1] = wlp; t.s_nw[1] = n_wl;
     t.h_in->dyn.pos = pos; t.h_in->dyn.kv_max = m.kv_max; t.h_in->dyn.frame = 0; t.h_in->dyn.done = 0;
     if (cudaMemcpyAsync(&t.d_in->dyn, &t.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice, m.st) != cudaSuccess) return -1;
     for (int i = 0; i < 2; i++)
@@ -1247,8 +1297,12 @@ int stream_wait_expiry(int limit_us) {
     int st = -1;
     SArgs a;
     a.ops = d_ops; a.n_ops = 2; a.dyn = (VbDyn *)(words + 52);
+    a.wl = nullptr; a.n_wl = 0;
     a.bar_counter = words + 16; a.exit_counter = words + 32; a.status = (int *)(words + 48);
     a.wait_cycles = m.wait_cycles;       /* the other waits keep the ordinary limit: the flag wait runs out first */
+    a.dbg = 0;
+    a.pf_bytes = 0;
+    a.timeline = nullptr;
     if (cudaMemcpyAsync(d_ops, ops, sizeof(ops), cudaMemcpyHostToDevice, m.st) == cudaSuccess &&
         stream_launch(a, n_cta, m.st) == cudaSuccess && cudaStreamSynchronize(m.st) == cudaSuccess)
         cudaMemcpy(&st, words + 48, sizeof(int), cudaMemcpyDeviceToHost);

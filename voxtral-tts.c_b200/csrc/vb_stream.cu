@@ -9,19 +9,20 @@
  * thing, keeping HBM busy from the first byte to the last.
  *
  * Roles inside a CTA (one CTA per SM, cooperative launch):
- *   warp 16, lane 0   producer. Walks the op list ahead of everyone and copies this CTA's
- *                     slab of every matrix, 16 KB at a time, into an 11-slot ring with 1-D
- *                     bulk copies (cp.async.bulk, completion on an mbarrier, no multicast).
- *                     It never waits for an op's input, only for a free slot: while the
- *                     other warps sit at a grid barrier the ring fills up with the next
- *                     matrix.
- *   warps 0..15       consumers. The slab order makes a warp load 512 contiguous bytes
- *                     (4 rows x 8 chunks of 8 BF16): lane = (row r, chunk c). A lane keeps
- *                     its 8 activations of the k-block in registers and one accumulator per
- *                     row step, so nothing is reduced per chunk: the 8 lanes of a row and
- *                     the warps that share a row range are summed once per op, in fixed
- *                     order (bit-reproducible; BF16 -> fp32 is an exact shift and all
- *                     products are fp32, as in voxtral_tts_kernels.c:152-185).
+ *   warp 12, lane 0   producer. Walks the list of weight matrices ahead of everyone and copies
+ *                     this CTA's slab of every matrix, 16 KB at a time, into an 11-slot ring
+ *                     with 1-D bulk copies (cp.async.bulk, completion on an mbarrier, no
+ *                     multicast). It never waits for an op's input, only for a free slot:
+ *                     while the other warps sit at a grid barrier the ring fills up with the
+ *                     next matrix.
+ *   warps 0..11       consumers. Warp s owns ring slot s: it waits for the slot alone and
+ *                     hands it back alone (warp 11 owns none). The slab order makes a warp
+ *                     load 512 contiguous bytes (4 rows x 8 chunks of 8 BF16): lane = (row r,
+ *                     chunk c). A lane keeps its 8 activations of the k-block in registers and
+ *                     one accumulator per row step, so nothing is reduced per slot: the 8
+ *                     lanes of a row and the warps are summed once per op, in fixed order
+ *                     (bit-reproducible; BF16 -> fp32 is an exact shift and all products are
+ *                     fp32, as in voxtral_tts_kernels.c:152-185).
  * RMSNorm is folded in: the input row is staged as x * gain, the sum of squares is taken on
  * the side, and 1/sqrt(mean + eps) multiplies the finished sums (voxtral_tts_kernels.c:333-349).
  *
@@ -35,6 +36,9 @@
 #include "vb_common.cuh"
 
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <vector>
 
 namespace vb {
 
@@ -42,25 +46,29 @@ struct SSmem {
     alignas(128) unsigned char ring[kSSlots][kSSlotBytes];
     /* the staged input row (permuted, see s_gemv); the attention op uses the same bytes */
     alignas(16) float xs[kSMaxK];
-    float part[kSConsumerWarps][kSMaxRowSteps * 4];
+    float part[kSConsumerWarps][kSMaxRows];     /* per-warp partial sums of the CTA's rows */
     float red[kSConsumerWarps];
+    alignas(16) SOp opbuf[2];                   /* the current and the next op descriptor */
     uint64_t full[kSSlots];
     uint64_t empty[kSSlots];
     int abort_flag;     /* raised by any thread of the CTA, at any time */
     int abort_seen;     /* the abort flag as sampled inside the last grid barrier: the same for every consumer thread */
-    int last_flag;
 };
 
 /* Attention scratch, overlaid on SSmem::xs. */
 struct SAttnSmem {
-    alignas(16) float qs[4][kSHeadDim];
-    alignas(16) float attn_o[kSAttnSubsets][4][kSHeadDim];
-    float attn_ml[kSAttnSubsets][4][2];
+    alignas(16) float q[kSHeadDim];
+    alignas(16) float kn[kSHeadDim];
+    alignas(16) float vn[kSHeadDim];
     float cs[kSHeadDim];
-    float cmb_m[kSKeySplitsMax * 4], cmb_l[kSKeySplitsMax * 4];
+    alignas(16) float wo[kSConsumerWarps][kSHeadDim];
+    float wml[kSConsumerWarps][2];
 };
 static_assert(sizeof(SAttnSmem) <= sizeof(float) * kSMaxK, "attention scratch must fit the row buffer");
 static_assert(sizeof(SSmem) <= 232448, "over the 227 KB a CTA may use");
+static_assert(sizeof(SOp) % 16 == 0, "op descriptors are copied in 16-byte pieces");
+static_assert(kSSlots <= kSConsumerWarps, "every ring slot needs an owner warp");
+static_assert(kSConsumerThreads >= 2 * kSHeadDim, "the attention op rotates q and k and copies v with one thread each");
 
 struct SCtx {
     SSmem *s;
@@ -68,6 +76,7 @@ struct SCtx {
     int tid, warp, lane;
     unsigned chunk_counter;
     unsigned barrier_epoch;
+    int tl_op;
 };
 
 VB_DEVINL bool s_aborted(const SCtx &c) { return *(volatile int *)&c.s->abort_flag != 0; }
@@ -77,6 +86,8 @@ VB_DEVINL void s_raise(SCtx &c, int code) {
     *(volatile int *)&c.s->abort_flag = 1;
 }
 
+/* Bounded mbarrier wait. try_wait suspends the thread for a while by itself; between tries the
+ * thread sleeps a little more so that waiting warps leave the issue slots to the working ones. */
 VB_DEVINL bool s_mbar_wait(SCtx &c, uint64_t *bar, uint32_t parity) {
     if (vb_mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -84,6 +95,7 @@ VB_DEVINL bool s_mbar_wait(SCtx &c, uint64_t *bar, uint32_t parity) {
         if (vb_mbar_try_wait(bar, parity)) return true;
         if (s_aborted(c)) return false;
         if (clock64() - t0 > c.a.wait_cycles) return false;
+        __nanosleep(32);
     }
 }
 
@@ -96,15 +108,17 @@ __device__ bool s_grid_sync(SCtx &c) {
     vb_named_bar(1, kSConsumerThreads);
     if (c.tid == 0) {
         if (!s_aborted(c)) {
-            __threadfence();
-            vb_atomic_add_release_gpu(c.a.bar_counter, 1u);
+            /* release: everything this CTA wrote before the CTA barrier above is visible to
+             * whoever acquires the counter; no return value, so the arrival costs no round trip */
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.a.bar_counter) : "memory");
             const unsigned target = c.barrier_epoch * gridDim.x;
             const long long t0 = clock64();
-            while (vb_ld_acquire_gpu(c.a.bar_counter) < target) {
+            /* relaxed polls (no fence per try), one acquire fence once the count is there */
+            while ((unsigned)vb_ld_relaxed_gpu_s32((const int *)c.a.bar_counter) < target) {
                 if (vb_ld_relaxed_gpu_s32(c.a.status) != 0) { *(volatile int *)&c.s->abort_flag = 1; break; }
                 if (clock64() - t0 > c.a.wait_cycles) { s_raise(c, S_ERR_GRID_BARRIER); break; }
             }
-            __threadfence();
+            asm volatile("fence.acq_rel.gpu;" ::: "memory");
         }
         c.s->abort_seen = s_aborted(c) ? 1 : 0;
     }
@@ -113,14 +127,65 @@ __device__ bool s_grid_sync(SCtx &c) {
 }
 
 /* ------------------------------------------------------------------ producer */
+/* One thread. The weight list is read one entry ahead, so an op switch costs no memory round
+ * trip: the only thing this thread ever waits for is a free ring slot.
+ *
+ * Second level: a cursor runs `pf_bytes` ahead of the ring through the same byte sequence and
+ * asks L2 for it (cp.async.bulk.prefetch.L2). The ring alone holds 4 us of this SM's share of
+ * HBM; the dependent chain between two ops (epilogue, grid barrier, staging of the next input)
+ * is about as long, so without the second level HBM idles at every op boundary. With it HBM
+ * keeps filling L2 through the stall, and the ring then refills from L2, faster than HBM could. */
+struct SCursor {
+    const SWeights *wl;
+    int n, i;
+    const unsigned char *ptr;
+    size_t left;
+};
+
+__device__ void s_cursor_open(SCursor &k, int i) {
+    k.i = i;
+    k.left = 0;
+    k.ptr = nullptr;
+    if (i >= k.n) return;
+    const SWeights w = k.wl[i];
+    const SPlan p = stream_plan(w.N, w.K, w.epi, blockIdx.x, gridDim.x);
+    k.ptr = (const unsigned char *)w.W + (size_t)p.r0 * w.K * 2;
+    k.left = (size_t)p.n_rows * w.K * 2;
+}
+
+/* Prefetches the next `bytes` of the sequence (crossing into following matrices as needed). */
+__device__ void s_cursor_prefetch(SCursor &k, size_t bytes) {
+    while (bytes > 0 && k.i < k.n) {
+        if (k.left == 0) { s_cursor_open(k, k.i + 1); continue; }
+        const uint32_t n = (uint32_t)(k.left < bytes ? k.left : bytes);
+        vb_prefetch_l2(k.ptr, n);
+        k.ptr += n;
+        k.left -= n;
+        bytes -= n;
+    }
+}
+
 __device__ void s_produce(SCtx &c) {
     SSmem *s = c.s;
-    for (int oi = 0; oi < c.a.n_ops; oi++) {
-        const SOp &op = c.a.ops[oi];
-        if (op.type != S_OP_GEMV) continue;
-        const SPlan p = stream_plan(op.N, op.K, op.epi, blockIdx.x, gridDim.x);
-        if (p.n_chunks == 0) continue;
-        const unsigned char *src = (const unsigned char *)op.W + (size_t)p.r0 * op.K * 2;
+    if (c.a.n_wl <= 0) return;
+    SCursor pf;
+    pf.wl = c.a.wl; pf.n = c.a.pf_bytes > 0 ? c.a.n_wl : 0;
+    s_cursor_open(pf, 0);
+    /* the ring's own first fill needs no prefetch: start the cursor one ring ahead */
+    {
+        size_t skip = (size_t)kSSlots * kSSlotBytes;
+        while (skip > 0 && pf.i < pf.n) {
+            if (pf.left == 0) { s_cursor_open(pf, pf.i + 1); continue; }
+            const size_t n = pf.left < skip ? pf.left : skip;
+            pf.ptr += n; pf.left -= n; skip -= n;
+        }
+        for (int b = 0; b < c.a.pf_bytes; b += kSSlotBytes) s_cursor_prefetch(pf, kSSlotBytes);
+    }
+    SWeights cur = c.a.wl[0];
+    for (int i = 0; i < c.a.n_wl; i++) {
+        const SWeights nxt = c.a.wl[i + 1 < c.a.n_wl ? i + 1 : i];
+        const SPlan p = stream_plan(cur.N, cur.K, cur.epi, blockIdx.x, gridDim.x);
+        const unsigned char *src = (const unsigned char *)cur.W + (size_t)p.r0 * cur.K * 2;
         const uint32_t kb_bytes = (uint32_t)p.n_rows * (kSBlockK * 2);
         for (int ch = 0; ch < p.n_chunks; ch++) {
             const int nkb = min(p.kbs, p.kblocks - ch * p.kbs);
@@ -134,22 +199,29 @@ __device__ void s_produce(SCtx &c) {
             vb_mbar_arrive_expect_tx(&s->full[slot], bytes);
             vb_bulk_g2s(s->ring[slot], src, bytes, &s->full[slot]);
             src += bytes;
+            s_cursor_prefetch(pf, bytes);       /* the cursor keeps its distance */
         }
+        cur = nxt;
     }
 }
+
+#define S_TL(k) do { if (c.a.timeline && blockIdx.x == 0 && c.tid == 0) c.a.timeline[c.tl_op * 8 + (k)] = clock64(); } while (0)
 
 /* ------------------------------------------------------------------ GEMV */
 __device__ void s_gemv(SCtx &c, const SOp &op) {
     SSmem *s = c.s;
-    const int N = op.N, K = op.K, epi = op.epi;
-    (void)N;
+    const int K = op.K, epi = op.epi;
     const SPlan p = stream_plan(op.N, K, epi, blockIdx.x, gridDim.x);
     const int tid = c.tid, warp = c.warp, lane = c.lane;
     float *const y = op.y;
     float *const tap = op.tap;
     const float *const bias = op.bias;
     const float *const gain = op.gain;
+    const float *const x = op.x;
+    const float eps = op.eps;
+    float *const xn_out = op.xn_out;
 
+    S_TL(0);
     /* this thread's residual value, requested before anything else needs L2 */
     float resv = 0.0f;
     if (epi == S_EPI_ADD && tid < p.n_rows) resv = __ldcg(op.res + p.r0 + tid);
@@ -159,7 +231,7 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
      * 128 contiguous bytes per load (no bank conflicts), the 4 row groups broadcast. */
     float ss = 0.0f;
     for (int i = tid; i < K / 4; i += kSConsumerThreads) {
-        float4 v = __ldcg(reinterpret_cast<const float4 *>(op.x) + i);
+        float4 v = __ldcg(reinterpret_cast<const float4 *>(x) + i);
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         if (gain) {
             const float4 g = __ldg(reinterpret_cast<const float4 *>(gain) + i);
@@ -178,70 +250,95 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
         float t = 0.0f;
 #pragma unroll
         for (int w = 0; w < kSConsumerWarps; w++) t += s->red[w];
-        rscale = 1.0f / sqrtf(t / (float)K + op.eps);
-        if (op.xn_out && blockIdx.x == 0) {
-            for (int k = tid; k < K; k += kSConsumerThreads)
-                op.xn_out[k] = __ldcg(op.x + k) * rscale * __ldg(gain + k);
+        rscale = 1.0f / sqrtf(t / (float)K + eps);
+        if (xn_out && blockIdx.x == 0) {
+            for (int k = tid; k < K; k += kSConsumerThreads) xn_out[k] = __ldcg(x + k) * rscale * __ldg(gain + k);
         }
     }
 
+    S_TL(1);
     const int c8 = lane & 7, rg = lane >> 3;
-    const int R = p.R, jr = p.jr;
-    const int rr = warp & (R - 1), kmod = kSConsumerWarps / R, kres = warp / R;
+    const int J = p.J;
     const int kb_bytes = p.n_rows * (kSBlockK * 2);
-    const int row0 = rr * jr * 4 + rg;          /* this lane's row in row step 0 */
     float acc[kSMaxRowSteps];
 #pragma unroll
     for (int j = 0; j < kSMaxRowSteps; j++) acc[j] = 0.0f;
 
+    /* Ring slot s belongs to warp s: it alone waits for the slot's fills (and so sees every
+     * phase of that mbarrier in order) and hands the slot back. The owner walks every row step
+     * of every k-block in the slot. */
     for (int ch = 0; ch < p.n_chunks; ch++) {
-        const unsigned slot = c.chunk_counter % kSSlots, use = c.chunk_counter / kSSlots;
-        c.chunk_counter++;
+        const unsigned g = c.chunk_counter++;
+        const unsigned slot = g % kSSlots, use = g / kSSlots;
+        if (slot != (unsigned)warp) continue;
         if (!s_mbar_wait(c, &s->full[slot], use & 1u)) {
             if (!s_aborted(c)) s_raise(c, S_ERR_FULL_WAIT);
             break;      /* carry on to the CTA barriers below; the results no longer matter */
         }
+        S_TL(6);
         const int kb0 = ch * p.kbs, kb1 = min(kb0 + p.kbs, p.kblocks);
-        int kb = kb0 + ((kres - (kb0 % kmod)) + kmod) % kmod;
-        for (; kb < kb1; kb += kmod) {
+        const unsigned char *base = s->ring[slot] + lane * 16;
+        for (int kb = (c.a.dbg & 1) ? kb1 : kb0; kb < kb1; kb++, base += kb_bytes) {
             const float4 xa = *reinterpret_cast<const float4 *>(&s->xs[kb * 64 + c8 * 4]);
             const float4 xb = *reinterpret_cast<const float4 *>(&s->xs[kb * 64 + 32 + c8 * 4]);
-            const unsigned char *base = s->ring[slot] + (size_t)(kb - kb0) * kb_bytes + rr * jr * 512 + lane * 16;
+            /* Row steps in groups of eight: the eight 16-byte loads of a group are issued
+             * together and feed eight independent accumulator chains. A row past the CTA's last
+             * one (the group is padded, and the last row step may be ragged) loads zeros. */
 #pragma unroll
-            for (int j = 0; j < kSMaxRowSteps; j++) {
-                if (j < jr && row0 + 4 * j < p.n_rows) {
-                    const uint4 w = *reinterpret_cast<const uint4 *>(base + j * 512);
-                    float a = acc[j];
-                    a = fmaf(vb_bf16_lo(w.x), xa.x, a); a = fmaf(vb_bf16_hi(w.x), xa.y, a);
-                    a = fmaf(vb_bf16_lo(w.y), xa.z, a); a = fmaf(vb_bf16_hi(w.y), xa.w, a);
-                    a = fmaf(vb_bf16_lo(w.z), xb.x, a); a = fmaf(vb_bf16_hi(w.z), xb.y, a);
-                    a = fmaf(vb_bf16_lo(w.w), xb.z, a); a = fmaf(vb_bf16_hi(w.w), xb.w, a);
-                    acc[j] = a;
+            for (int g8 = 0; g8 < kSMaxRowSteps / 8; g8++) {
+                if (g8 * 8 < J) {
+                    uint4 w[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int j = g8 * 8 + u;
+                        w[u] = make_uint4(0u, 0u, 0u, 0u);
+                        if (4 * j + rg < p.n_rows) w[u] = *reinterpret_cast<const uint4 *>(base + j * 512);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        float a = acc[g8 * 8 + u];
+                        a = fmaf(vb_bf16_lo(w[u].x), xa.x, a); a = fmaf(vb_bf16_hi(w[u].x), xa.y, a);
+                        a = fmaf(vb_bf16_lo(w[u].y), xa.z, a); a = fmaf(vb_bf16_hi(w[u].y), xa.w, a);
+                        a = fmaf(vb_bf16_lo(w[u].z), xb.x, a); a = fmaf(vb_bf16_hi(w[u].z), xb.y, a);
+                        a = fmaf(vb_bf16_lo(w[u].w), xb.z, a); a = fmaf(vb_bf16_hi(w[u].w), xb.w, a);
+                        acc[g8 * 8 + u] = a;
+                    }
                 }
             }
         }
-        /* the slot's bytes this warp needs are in registers */
+        /* the slot's bytes are in registers */
         __syncwarp();
         if (lane == 0) vb_mbar_arrive(&s->empty[slot]);
     }
 
-    /* once per op: the 8 column chunks of a row (lanes), then the warps of a row range */
+    S_TL(2);
+    /* once per op: the 8 column chunks of a row (lanes), then the warps, in fixed order */
 #pragma unroll
-    for (int j = 0; j < kSMaxRowSteps; j++) {
-        float v = acc[j];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        if (c8 == 0) s->part[warp][j * 4 + rg] = v;
+    for (int g8 = 0; g8 < kSMaxRowSteps / 8; g8++) {
+        if (g8 * 8 < J) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = acc[g8 * 8 + u];
+#pragma unroll
+            for (int off = 1; off < 8; off <<= 1) {
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] += __shfl_xor_sync(0xffffffffu, v[u], off);
+            }
+            if (c8 == 0) {
+#pragma unroll
+                for (int u = 0; u < 8; u++) s->part[warp][(g8 * 8 + u) * 4 + rg] = v[u];
+            }
+        }
     }
     vb_named_bar(2, kSConsumerThreads);
+    S_TL(3);
     if (warp * 32 < p.n_rows) {
         const int t = tid;
         const bool valid = t < p.n_rows;
         float sum = 0.0f;
         if (valid) {
-            const int js = t >> 2, rt = js / jr, j = js - rt * jr, rl = j * 4 + (t & 3);
-            for (int w = rt; w < kSConsumerWarps; w += R) sum += s->part[w][rl];
+#pragma unroll
+            for (int w = 0; w < kSConsumerWarps; w++) sum += s->part[w][t];
         }
         sum *= rscale;
         if (epi == S_EPI_SWIGLU) {
@@ -265,14 +362,15 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
 
 /* ------------------------------------------------------------------ decode attention */
 /* op.x = [q | k | v] of the new token (6144 floats); op.y = attention output (4096);
- * op.p2 / op.p3 = this layer's K and V cache [kv_max, 1024]; op.p0 = float scratch for the
- * key-split partials; op.p1 = one ticket per KV head; i0 = query heads, i1 = KV heads;
+ * op.p2 / op.p3 = this layer's K and V cache [kv_max, 1024]; i0 = query heads, i1 = KV heads;
  * f0 = softmax scale, f1 = RoPE theta. Restates voxtral_tts_llm.c:221-238 with tts_apply_rope
- * and tts_causal_attention (voxtral_tts_kernels.c:403-465, 602-634): interleaved pairs,
- * the score is scaled after the dot product, the running maximum starts at -1e30. A CTA
- * serves the four query heads of one KV head on one slice of the keys; four warp subsets
- * split the slice; slices are merged with log-sum-exp weights in slice order by the last
- * CTA of the KV head to finish (a ticket, no spin). */
+ * and tts_causal_attention (voxtral_tts_kernels.c:403-465, 602-634): interleaved pairs, the
+ * score is scaled after the dot product, the running maximum starts at -1e30.
+ * One CTA per query head (32 of the grid's CTAs work, no exchange between CTAs): warp w takes
+ * the keys w, w + 12, ... with the reference's running-maximum update, eight keys per pass so
+ * that their sixteen loads are in flight together; the warps are merged with log-sum-exp
+ * weights in warp order. The new token's key and value are used from shared memory; the first
+ * query head of each group also appends them to the cache. */
 __device__ void s_attn(SCtx &c, const SOp &op) {
     SAttnSmem *s = reinterpret_cast<SAttnSmem *>(c.s->xs);
     const int tid = c.tid, warp = c.warp, lane = c.lane;
@@ -282,66 +380,58 @@ __device__ void s_attn(SCtx &c, const SOp &op) {
         return;
     }
     const int H = op.i0, G = op.i1, group = H / G;      /* 32, 8, 4 */
+    const int h = blockIdx.x;
+    if (h >= H) return;
+    const int g = h / group;
     const int kv_dim = G * kSHeadDim, q_dim = H * kSHeadDim;
-    const int nk = pos + 1;
-    int max_s = (int)gridDim.x / G;
-    if (max_s > kSKeySplitsMax) max_s = kSKeySplitsMax;
-    if (max_s < 1) max_s = 1;
-    int S = (nk + 31) / 32;
-    if (S > max_s) S = max_s;
-    const int item = blockIdx.x;
-    if (item >= G * S) return;
-    const int g = item / S, sp = item % S;
-    const int j0 = (int)((long long)nk * sp / S), j1 = (int)((long long)nk * (sp + 1) / S);
-    float *Kc = (float *)op.p2, *Vc = (float *)op.p3;
-    const float *q = op.x, *kn = op.x + q_dim, *vn = op.x + q_dim + kv_dim;
-    const bool writer = sp == S - 1;    /* its key range ends with the new token */
+    const float scale = op.f0;
+    const float *Kc = (const float *)op.p2 + g * kSHeadDim, *Vc = (const float *)op.p3 + g * kSHeadDim;
+    const float *qg = op.x + (size_t)h * kSHeadDim, *kg = op.x + q_dim + g * kSHeadDim,
+                *vg = op.x + q_dim + kv_dim + g * kSHeadDim;
+    const bool writer = (h % group) == 0;
+    constexpr int half = kSHeadDim / 2;
 
-    if (tid < kSHeadDim / 2) {
-        const float freq = 1.0f / powf(op.f1, (float)(2 * tid) / (float)kSHeadDim);
+    /* raw values first (three loads in flight per thread group), then the rotation */
+    float ra = 0.0f, rb = 0.0f;
+    if (tid < half) { ra = __ldcg(qg + 2 * tid); rb = __ldcg(qg + 2 * tid + 1); }
+    else if (tid < 2 * half) { ra = __ldcg(kg + 2 * (tid - half)); rb = __ldcg(kg + 2 * (tid - half) + 1); }
+    else if (tid < 2 * half + kSHeadDim) { ra = __ldcg(vg + (tid - 2 * half)); }
+    if (tid < 2 * half) {
+        const int d = tid < half ? tid : tid - half;
+        const float freq = 1.0f / powf(op.f1, (float)(2 * d) / (float)kSHeadDim);
         const float ang = (float)pos * freq;
-        s->cs[2 * tid] = cosf(ang);
-        s->cs[2 * tid + 1] = sinf(ang);
-    }
-    vb_named_bar(2, kSConsumerThreads);
-    const int half = kSHeadDim / 2;
-    if (tid < group * half) {
-        const int hh = tid / half, d = tid % half;
-        const float *src = q + (size_t)(g * group + hh) * kSHeadDim;
-        const float a = __ldcg(src + 2 * d), b = __ldcg(src + 2 * d + 1);
-        const float cv = s->cs[2 * d], sv = s->cs[2 * d + 1];
-        s->qs[hh][2 * d] = a * cv - b * sv;
-        s->qs[hh][2 * d + 1] = a * sv + b * cv;
-    } else if (writer && tid < group * half + half) {
-        const int d = tid - group * half;
-        const float a = __ldcg(kn + g * kSHeadDim + 2 * d), b = __ldcg(kn + g * kSHeadDim + 2 * d + 1);
-        const float cv = s->cs[2 * d], sv = s->cs[2 * d + 1];
-        float *dst = Kc + (size_t)pos * kv_dim + g * kSHeadDim;
-        dst[2 * d] = a * cv - b * sv;
-        dst[2 * d + 1] = a * sv + b * cv;
-        __threadfence();
-    } else if (writer && tid >= 384 && tid < 384 + kSHeadDim) {
-        const int d = tid - 384;
-        Vc[(size_t)pos * kv_dim + g * kSHeadDim + d] = __ldcg(vn + g * kSHeadDim + d);
-        __threadfence();
+        const float cv = cosf(ang), sv = sinf(ang);
+        const float o0 = ra * cv - rb * sv, o1 = ra * sv + rb * cv;
+        if (tid < half) { s->q[2 * d] = o0; s->q[2 * d + 1] = o1; }
+        else {
+            s->kn[2 * d] = o0; s->kn[2 * d + 1] = o1;
+            if (writer) {
+                float *dst = (float *)op.p2 + (size_t)pos * kv_dim + g * kSHeadDim;
+                dst[2 * d] = o0; dst[2 * d + 1] = o1;
+            }
+        }
+    } else if (tid < 2 * half + kSHeadDim) {
+        const int d = tid - 2 * half;
+        s->vn[d] = ra;
+        if (writer) ((float *)op.p3)[(size_t)pos * kv_dim + g * kSHeadDim + d] = ra;
     }
     vb_named_bar(2, kSConsumerThreads);
 
-    const int hh = warp & 3, ss = warp >> 2;
-    const float4 q4 = *reinterpret_cast<const float4 *>(&s->qs[hh][4 * lane]);
+    const float4 q4 = *reinterpret_cast<const float4 *>(&s->q[4 * lane]);
     float mx = -1e30f, den = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    /* four keys per pass: their eight loads are in flight together, the running-maximum update
-     * then takes them in key order as the reference does */
-    constexpr int kKeysPerPass = 4;
-    for (int jb = j0 + ss; jb < j1; jb += kKeysPerPass * kSAttnSubsets) {
+    constexpr int kKeysPerPass = 8;
+    for (int jb = warp; jb <= pos; jb += kKeysPerPass * kSConsumerWarps) {
         float4 kq[kKeysPerPass], vq[kKeysPerPass];
 #pragma unroll
         for (int u = 0; u < kKeysPerPass; u++) {
-            const int j = jb + u * kSAttnSubsets;
-            if (j < j1) {
-                kq[u] = vb_ldcg4(Kc + (size_t)j * kv_dim + g * kSHeadDim + 4 * lane);
-                vq[u] = vb_ldcg4(Vc + (size_t)j * kv_dim + g * kSHeadDim + 4 * lane);
+            const int j = jb + u * kSConsumerWarps;
+            if (j < pos) {
+                kq[u] = vb_ldcg4(Kc + (size_t)j * kv_dim + 4 * lane);
+                vq[u] = vb_ldcg4(Vc + (size_t)j * kv_dim + 4 * lane);
+            } else if (j == pos) {
+                kq[u] = *reinterpret_cast<const float4 *>(&s->kn[4 * lane]);
+                vq[u] = *reinterpret_cast<const float4 *>(&s->vn[4 * lane]);
             } else {
                 kq[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 vq[u] = kq[u];
@@ -358,8 +448,8 @@ __device__ void s_attn(SCtx &c, const SOp &op) {
         }
 #pragma unroll
         for (int u = 0; u < kKeysPerPass; u++) {
-            if (jb + u * kSAttnSubsets >= j1) break;
-            const float d = dq[u] * op.f0;
+            if (jb + u * kSConsumerWarps > pos) break;
+            const float d = dq[u] * scale;
             const float4 vv = vq[u];
             if (d > mx) {
                 const float corr = expf(mx - d);
@@ -374,67 +464,23 @@ __device__ void s_attn(SCtx &c, const SOp &op) {
             }
         }
     }
-    *reinterpret_cast<float4 *>(&s->attn_o[ss][hh][4 * lane]) = o;
-    if (lane == 0) { s->attn_ml[ss][hh][0] = mx; s->attn_ml[ss][hh][1] = den; }
+    *reinterpret_cast<float4 *>(&s->wo[warp][4 * lane]) = o;
+    if (lane == 0) { s->wml[warp][0] = mx; s->wml[warp][1] = den; }
     vb_named_bar(2, kSConsumerThreads);
-
-    /* merge the four key subsets: thread = (head, dim) */
-    const int th = tid / kSHeadDim, td = tid % kSHeadDim;
-    float M0 = -1e30f;
+    if (tid < kSHeadDim) {
+        float M0 = -1e30f;
 #pragma unroll
-    for (int u = 0; u < kSAttnSubsets; u++) M0 = fmaxf(M0, s->attn_ml[u][th][0]);
-    float L = 0.0f, O = 0.0f;
+        for (int w = 0; w < kSConsumerWarps; w++) M0 = fmaxf(M0, s->wml[w][0]);
+        float L = 0.0f, O = 0.0f;
 #pragma unroll
-    for (int u = 0; u < kSAttnSubsets; u++) {
-        const float w = (s->attn_ml[u][th][1] > 0.0f) ? expf(s->attn_ml[u][th][0] - M0) : 0.0f;
-        L += s->attn_ml[u][th][1] * w;
-        O += s->attn_o[u][th][td] * w;
-    }
-    float *out = op.y + (size_t)(g * group + th) * kSHeadDim + td;
-    if (S == 1) {
-        *out = (L > 0.0f) ? O * (1.0f / L) : 0.0f;
-        return;
-    }
-    /* several CTAs share this KV head: publish the slice, the last arrival merges */
-    const int stride = kSHeadDim + 2;
-    float *po = (float *)op.p0 + (size_t)g * kSKeySplitsMax * group * stride;   /* [slice][head][128 + 2] */
-    float *mine = po + ((size_t)sp * group + th) * stride;
-    mine[td] = O;
-    if (td == 0) { mine[kSHeadDim] = M0; mine[kSHeadDim + 1] = L; }
-    __threadfence();
-    vb_named_bar(2, kSConsumerThreads);
-    unsigned *tickets = (unsigned *)op.p1;
-    if (tid == 0) {
-        const unsigned t = atomicAdd(&tickets[g], 1u);
-        c.s->last_flag = (t == (unsigned)(S - 1));
-        if (c.s->last_flag) tickets[g] = 0u;
-    }
-    vb_named_bar(2, kSConsumerThreads);
-    if (!c.s->last_flag) return;
-    __threadfence();
-    if (tid < S * group) {
-        const float *pu = po + (size_t)tid * stride;     /* (slice, head) = tid / group, tid % group */
-        s->cmb_m[tid] = __ldcg(pu + kSHeadDim);
-        s->cmb_l[tid] = __ldcg(pu + kSHeadDim + 1);
-    }
-    float ov[kSKeySplitsMax];
-#pragma unroll
-    for (int u = 0; u < kSKeySplitsMax; u++)
-        ov[u] = u < S ? __ldcg(po + ((size_t)u * group + th) * stride + td) : 0.0f;
-    vb_named_bar(2, kSConsumerThreads);
-    float Mg = -1e30f;
-    for (int u = 0; u < S; u++) Mg = fmaxf(Mg, s->cmb_m[u * group + th]);
-    float Lg = 0.0f, Og = 0.0f;
-#pragma unroll
-    for (int u = 0; u < kSKeySplitsMax; u++) {
-        if (u < S) {
-            const float lu = s->cmb_l[u * group + th];
-            const float w = (lu > 0.0f) ? expf(s->cmb_m[u * group + th] - Mg) : 0.0f;
-            Lg += lu * w;
-            Og += ov[u] * w;
+        for (int w = 0; w < kSConsumerWarps; w++) {
+            const float lw = s->wml[w][1];
+            const float e = lw > 0.0f ? expf(s->wml[w][0] - M0) : 0.0f;
+            L += lw * e;
+            O += s->wo[w][tid] * e;
         }
+        op.y[(size_t)h * kSHeadDim + tid] = L > 0.0f ? O * (1.0f / L) : 0.0f;
     }
-    *out = (Lg > 0.0f) ? Og * (1.0f / Lg) : 0.0f;
 }
 
 /* ------------------------------------------------------------------ small ops */
@@ -513,35 +559,52 @@ __device__ void s_wait_flag(SCtx &c, const SOp &op) {
 }
 
 /* ------------------------------------------------------------------ the kernel */
+VB_DEVINL void s_cp_async16(void *smem_dst, const void *gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(vb_smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+VB_DEVINL void s_cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
     extern __shared__ __align__(128) unsigned char s_smem_raw[];
     SSmem *s = reinterpret_cast<SSmem *>(s_smem_raw);
     SCtx c;
     c.s = s; c.a = a;
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
-    c.chunk_counter = 0; c.barrier_epoch = 0;
+    c.chunk_counter = 0; c.barrier_epoch = 0; c.tl_op = 0;
 
     /* a device-resident run that has ended: its remaining queued launches do nothing (the flag
      * was written by an earlier launch, so the whole grid agrees) */
     if (a.dyn->done) return;
 
+    constexpr int kOpVecs = (int)(sizeof(SOp) / 16);
     if (c.tid == 0) {
         for (int i = 0; i < kSSlots; i++) {
             vb_mbar_init(&s->full[i], 1);
-            vb_mbar_init(&s->empty[i], kSConsumerWarps);
+            vb_mbar_init(&s->empty[i], 1);
         }
         s->abort_flag = 0;
         s->abort_seen = 0;
-        s->last_flag = 0;
         vb_mbar_init_fence();
     }
+    if (c.tid < kOpVecs && a.n_ops > 0)
+        reinterpret_cast<uint4 *>(&s->opbuf[0])[c.tid] = __ldg(reinterpret_cast<const uint4 *>(a.ops) + c.tid);
     __syncthreads();
 
     if (c.warp == kSConsumerWarps) {
         if (c.lane == 0) s_produce(c);
     } else {
         for (int oi = 0; oi < a.n_ops; oi++) {
-            const SOp &op = a.ops[oi];
+            /* Descriptors reach shared memory one op ahead (asynchronous copies issued by a few
+             * threads during the previous op), so no op starts with a round trip to L2 for its
+             * own parameters. The CTA barrier makes op oi's copy visible to every thread and
+             * tells the copying threads that nobody reads op oi-1's buffer any more. */
+            if (c.tid < kOpVecs) s_cp_async_wait_all();
+            vb_named_bar(3, kSConsumerThreads);
+            if (c.tid < kOpVecs && oi + 1 < a.n_ops)
+                s_cp_async16(reinterpret_cast<uint4 *>(&s->opbuf[(oi + 1) & 1]) + c.tid,
+                             reinterpret_cast<const uint4 *>(a.ops + oi + 1) + c.tid);
+            const SOp &op = s->opbuf[oi & 1];
+            const int flags = op.flags;
             switch (op.type) {
             case S_OP_GEMV:   s_gemv(c, op); break;
             case S_OP_ATTN:   s_attn(c, op); break;
@@ -550,8 +613,13 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
             case S_OP_WAIT:   s_wait_flag(c, op); break;
             default: if (c.tid == 0) s_raise(c, S_ERR_BAD_OP); break;
             }
-            if (!(op.flags & S_F_NOSYNC) && oi + 1 < a.n_ops && s_grid_sync(c)) break;
+            S_TL(4);
+            const bool stop = !(flags & S_F_NOSYNC) && oi + 1 < a.n_ops && s_grid_sync(c);
+            S_TL(5);
+            c.tl_op++;
+            if (stop) break;
         }
+        if (c.tid < kOpVecs) s_cp_async_wait_all();
     }
 
     __syncthreads();
@@ -645,6 +713,103 @@ cudaError_t stream_launch(const SArgs &args, int n_cta, cudaStream_t st) {
     cfg.attrs = at;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, vb_stream_kernel, a);
+}
+
+/* ---------------------------------------------------------------- stand-alone probe */
+__global__ void vb_stream_fill_kernel(uint16_t *p, size_t n, uint32_t seed) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t h = (uint32_t)i * 2654435761u + seed;
+    h ^= h >> 15;
+    p[i] = (uint16_t)(0x3c00u | (h & 0x3fu) | ((h & 0x40u) << 9));   /* small BF16 values of both signs */
+}
+
+/* The kernel alone, without a model: `n_ops` GEMV ops on generated [N, K] matrices (enough
+ * copies that no op finds its weights in L2), `reps` launches between two events on the default
+ * stream. sync = 1: a grid barrier after every op (as in a decoder step); 0: none. A measurement
+ * and profiling aid with a small memory footprint. */
+int stream_probe(int N, int K, int n_ops, int sync, int reps, int dbg, float *ms_out, double *bytes_per_launch) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    const int n_cta = stream_max_ctas(dev);
+    if (n_cta <= 0 || n_ops < 1 || n_ops > 128 || reps < 1 || stream_validate(N, K, S_EPI_STORE, n_cta)) return -1;
+    const size_t wn = (size_t)N * K;
+    int copies = (int)((size_t)400 * 1024 * 1024 / (wn * 2)) + 1;
+    if (copies > n_ops) copies = n_ops;
+    std::vector<uint16_t *> W(copies, nullptr);
+    float *x = nullptr, *y = nullptr;
+    unsigned *words = nullptr;
+    SOp *d_ops = nullptr;
+    SWeights *d_wl = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = -1;
+    do {
+        bool ok = true;
+        for (int c = 0; c < copies && ok; c++) {
+            ok = cudaMalloc(&W[c], wn * 2) == cudaSuccess;
+            if (ok) vb_stream_fill_kernel<<<(unsigned)((wn + 255) / 256), 256>>>(W[c], wn, 1u + c);
+        }
+        if (!ok || cudaMalloc(&x, sizeof(float) * K) != cudaSuccess || cudaMalloc(&y, sizeof(float) * N) != cudaSuccess ||
+            cudaMalloc(&words, sizeof(unsigned) * 64) != cudaSuccess || cudaMalloc(&d_ops, sizeof(SOp) * n_ops) != cudaSuccess)
+            break;
+        cudaMemset(x, 0, sizeof(float) * K);
+        cudaMemset(words, 0, sizeof(unsigned) * 64);
+        std::vector<SOp> ops(n_ops);
+        for (int i = 0; i < n_ops; i++) {
+            SOp &o = ops[i];
+            memset(&o, 0, sizeof(o));
+            o.type = S_OP_GEMV; o.N = N; o.K = K; o.epi = S_EPI_STORE; o.W = W[i % copies]; o.x = x; o.y = y;
+            o.flags = sync ? 0 : S_F_NOSYNC;
+        }
+        std::vector<SWeights> wl(n_ops);
+        for (int i = 0; i < n_ops; i++) wl[i] = SWeights{ops[i].W, N, K, S_EPI_STORE, 0};
+        if (cudaMalloc(&d_wl, sizeof(SWeights) * n_ops) != cudaSuccess ||
+            cudaMemcpy(d_wl, wl.data(), sizeof(SWeights) * n_ops, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(d_ops, ops.data(), sizeof(SOp) * n_ops, cudaMemcpyHostToDevice) != cudaSuccess)
+            break;
+        SArgs a;
+        a.ops = d_ops; a.n_ops = n_ops; a.dyn = (VbDyn *)(words + 52);
+        a.wl = d_wl; a.n_wl = n_ops;
+        a.bar_counter = words; a.exit_counter = words + 16; a.status = (int *)(words + 32);
+        a.wait_cycles = 2000000000LL; a.dbg = dbg; a.timeline = nullptr;
+        a.pf_bytes = getenv("VB200_STREAM_PF") ? atoi(getenv("VB200_STREAM_PF")) : kSPrefetchBytes;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
+        for (int i = 0; i < 2 && ok; i++) ok = stream_launch(a, n_cta, 0) == cudaSuccess;
+        cudaEventRecord(e0, 0);
+        for (int i = 0; i < reps && ok; i++) ok = stream_launch(a, n_cta, 0) == cudaSuccess;
+        cudaEventRecord(e1, 0);
+        if (!ok || cudaDeviceSynchronize() != cudaSuccess) break;
+        int st = 0;
+        cudaMemcpy(&st, words + 32, sizeof(int), cudaMemcpyDeviceToHost);
+        if (st) break;
+        if (getenv("VB200_STREAM_TL")) {
+            long long *tl = nullptr;
+            if (cudaMalloc(&tl, sizeof(long long) * 8 * n_ops) == cudaSuccess) {
+                cudaMemset(tl, 0, sizeof(long long) * 8 * n_ops);
+                a.timeline = tl;
+                stream_launch(a, n_cta, 0);
+                cudaDeviceSynchronize();
+                std::vector<long long> h(8 * n_ops);
+                cudaMemcpy(h.data(), tl, sizeof(long long) * 8 * n_ops, cudaMemcpyDeviceToHost);
+                for (int i = 0; i < n_ops; i++) {
+                    fprintf(stderr, "op %2d:", i);
+                    for (int k = 0; k < 7; k++) fprintf(stderr, " %8.2f", (double)(h[8 * i + k] - h[0]) / 1965.0);
+                    fprintf(stderr, "\n");
+                }
+                cudaFree(tl);
+                a.timeline = nullptr;
+            }
+        }
+        if (ms_out) cudaEventElapsedTime(ms_out, e0, e1);
+        if (bytes_per_launch) *bytes_per_launch = 2.0 * (double)wn * n_ops;
+        rc = 0;
+    } while (0);
+    cudaGetLastError();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    for (uint16_t *p : W) cudaFree(p);
+    cudaFree(x); cudaFree(y); cudaFree(words); cudaFree(d_ops); cudaFree(d_wl);
+    return rc;
 }
 
 } // namespace vb

@@ -22,18 +22,17 @@
 
 namespace vb {
 
-constexpr int kSConsumerWarps = 16;
+constexpr int kSConsumerWarps = 12;
 constexpr int kSConsumerThreads = kSConsumerWarps * 32;
 constexpr int kSThreads = kSConsumerThreads + 32;      /* + the producer warp */
 constexpr int kSSlotBytes = 16384;                     /* one ring slot: whole k-blocks of the CTA's rows */
 constexpr int kSSlots = 11;
 constexpr int kSBlockK = 64;                           /* columns per k-block: 128 bytes per row */
-constexpr int kSMaxRowSteps = 8;                       /* row steps (4 rows each) a warp accumulates at once */
-constexpr int kSMaxRows = kSSlotBytes / (kSBlockK * 2);/* 128 rows per CTA per op */
+constexpr int kSMaxRows = kSSlotBytes / (kSBlockK * 2);/* 128 rows per CTA per op: one k-block fits a slot */
+constexpr int kSMaxRowSteps = kSMaxRows / 4;           /* row steps (4 rows each) = accumulators per lane */
 constexpr int kSMaxK = 9216;
 constexpr int kSHeadDim = 128;
-constexpr int kSAttnSubsets = 4;
-constexpr int kSKeySplitsMax = 20;
+constexpr int kSPrefetchBytes = 0;            /* default L2 prefetch distance per CTA */
 
 enum SOpType {
     S_OP_GEMV = 1,      /* y[N] = epi(W[N,K] . pro(x[K])) */
@@ -70,15 +69,16 @@ struct SOp {
 
 /* How one GEMV op is cut for one CTA. Rows are dealt out in units (1 row, or a
  * (gate, up) pair); the first `rem` CTAs take one unit more. A CTA's rows are walked in
- * row steps of 4 rows x 8 column chunks = one 512-byte warp load; J row steps are divided
- * into R row ranges of jr <= 8 steps, and warp w serves row range w % R on the k-blocks
- * kb with kb % (16 / R) == w / R. */
+ * row steps of 4 rows x 8 column chunks = one 512-byte warp load. A ring slot holds `kbs`
+ * whole k-blocks of the CTA's rows; slot s belongs to consumer warp s for the whole launch (one
+ * waiter per mbarrier, which therefore sees every phase of it in order), and the owner walks
+ * all J row steps of every k-block in its slot. */
 struct SPlan {
     int r0, n_rows;     /* this CTA's rows */
     int kblocks;        /* K / 64 */
     int kbs;            /* k-blocks per ring slot */
     int n_chunks;       /* ring slots this op takes */
-    int J, R, jr;
+    int J;              /* row steps: ceil(n_rows / 4) */
 };
 
 __host__ __device__ inline SPlan stream_plan(int N, int K, int epi, int cta, int n_cta) {
@@ -93,9 +93,6 @@ __host__ __device__ inline SPlan stream_plan(int N, int K, int epi, int cta, int
     if (p.kbs > p.kblocks) p.kbs = p.kblocks;
     p.n_chunks = p.kbs > 0 ? (p.kblocks + p.kbs - 1) / p.kbs : 0;
     p.J = (p.n_rows + 3) / 4;
-    p.R = 1;
-    while ((p.J + p.R - 1) / p.R > kSMaxRowSteps && p.R < kSConsumerWarps) p.R *= 2;
-    p.jr = (p.J + p.R - 1) / p.R;
     return p;
 }
 
@@ -104,8 +101,7 @@ inline int stream_validate(int N, int K, int epi, int n_cta) {
     if (N <= 0 || K <= 0 || (K % kSBlockK) != 0 || K > kSMaxK) return -1;
     if (epi == S_EPI_SWIGLU && (N & 1)) return -2;
     const SPlan p = stream_plan(N, K, epi, 0, n_cta);   /* CTA 0 has the most rows */
-    if (p.n_rows > kSMaxRows || p.n_rows > kSConsumerThreads) return -3;
-    if (p.jr > kSMaxRowSteps) return -4;
+    if (p.n_rows > kSMaxRows) return -3;
     return 0;
 }
 
@@ -114,14 +110,25 @@ inline size_t stream_slab_bytes(int N, int K) { return (size_t)N * K * 2; }
 /* Re-lays a row-major [N, K] BF16 matrix out in slab order for n_cta CTAs. */
 int stream_make_slabs(uint16_t *d_dst, const uint16_t *d_src, int N, int K, int epi, int n_cta, cudaStream_t st);
 
+/* What the producer thread needs to know about a GEMV op, in program order. */
+struct SWeights {
+    const uint16_t *W;
+    int N, K, epi, pad;
+};
+
 struct SArgs {
     const SOp *ops;
     int n_ops;
+    const SWeights *wl;         /* the GEMV ops' weights, in the order the ops appear */
+    int n_wl;
     VbDyn *dyn;
     unsigned *bar_counter;      /* grid barrier arrivals; zero between launches */
     unsigned *exit_counter;     /* CTAs that finished; the last one re-zeroes both */
     int *status;                /* 0, or the code of the wait that ran out */
     long long wait_cycles;      /* limit of every wait inside the kernel */
+    int dbg;                    /* TEMP measurement: 1 = consumers skip the arithmetic */
+    int pf_bytes;               /* L2 prefetch distance ahead of the ring, per CTA (0 = off) */
+    long long *timeline;        /* TEMP measurement: per-op timestamps of CTA 0 */
 };
 
 /* Status codes of this kernel (distinct from the other kernels' codes). */
@@ -133,6 +140,7 @@ enum SStatus {
 /* CTAs of a launch on `device` (one per SM), or 0 when the kernel does not fit. */
 int stream_max_ctas(int device);
 cudaError_t stream_launch(const SArgs &args, int n_cta, cudaStream_t st);
+int stream_probe(int N, int K, int n_ops, int sync, int reps, int dbg, float *ms_out, double *bytes_per_launch);
 
 } // namespace vb
 
