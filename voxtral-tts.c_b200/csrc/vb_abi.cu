@@ -186,7 +186,7 @@ int vb200_stream_step_ms(int pos, int iters, float *ms, double *bytes_per_launch
     return stream_step_time(pos, iters, ms, bytes_per_launch);
 }
 int vb200_stream_probe(int N, int K, int n_ops, int sync, int reps, float *ms, double *bytes_per_launch) {
-    return stream_probe(N, K, n_ops, sync, reps, getenv("VB200_STREAM_DBG") ? atoi(getenv("VB200_STREAM_DBG")) : 0, ms, bytes_per_launch);
+    return stream_probe(N, K, n_ops, sync, reps, ms, bytes_per_launch);
 }
 int vb200_selftest_wait_expiry(int limit_us) { return stream_wait_expiry(limit_us); }
 int vb200_frame_on_stream_kernel(void) { return single_on_stream() ? 1 : 0; }

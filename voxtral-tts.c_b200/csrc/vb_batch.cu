@@ -114,14 +114,14 @@ struct Batch {
     /* the decoder step as one launch of the persistent streaming kernel (vb_stream.cu) */
     bool stream = false, s_tap = false;
     const uint16_t *s_table = nullptr;          /* audio table the op lists were built with */
-    float *s_qkv = nullptr, *s_attn = nullptr, *s_h = nullptr, *s_logits = nullptr;
+    stag_t *s_qkv = nullptr, *s_attn = nullptr, *s_h = nullptr, *s_xa = nullptr, *s_xb = nullptr;   /* tagged vectors */
+    stag_t *s_scratch = nullptr;                /* attention key-slice partials, tagged */
+    float *s_logits = nullptr;
     unsigned *s_counters = nullptr;             /* [0] grid barrier, [16] exit counter */
+    unsigned *s_seq = nullptr;                  /* launch sequence number (never reset: tags must not repeat) */
     SOp *s_prog[kVariants] = {};
     SWeights *s_wl[kVariants] = {};             /* the producer's view of each op list: its GEMV weights in order */
     int s_n[kVariants] = {}, s_nw[kVariants] = {};
-    std::vector<SOp> s_host;                    /* host copy of variant 1's op list (measurement aid) */
-    SOp *s_prog_dbg = nullptr;
-    SWeights *s_wl_dbg = nullptr;
     cudaGraphExec_t exec[kVariants] = {};
     int direct_calls[kVariants] = {};
     int graph_cap = 0;                          /* frame cap baked into exec[0] */
@@ -789,44 +789,76 @@ static int stream_programs(Batch &t) {
             if (v == 0) e.flags = S_F_SKIP_FRAME0;
             ops.push_back(e);
         }
+        /* The residual stream alternates between two tagged vectors: the O projection writes
+         * xb = x + ..., the down projection writes xa = xb + ... (the input row itself stays
+         * plain: the host or the embed op wrote it). Every vector a GEMV or attention op hands on
+         * is tagged with (launch, producing op), so these ops need no grid barrier between them. */
+        int tag = 0;
+        const float *x_cur = t.X;               /* the layer's input: plain for layer 0, then xa */
+        int x_cur_tag = 0;
         for (int l = 0; l < VB200_DEC_LAYERS; l++) {
             const LayerDev &L = m.dec[l];
-            SOp o = sop_gemv(QKV, D, S_EPI_STORE, w.wqkv[l], t.X, t.s_qkv);
+            const int in_flag = x_cur_tag ? S_F_X_TAGGED : 0;
+            SOp o = sop_gemv(QKV, D, S_EPI_STORE, w.wqkv[l], x_cur, (float *)t.s_qkv);
             o.gain = L.attn_norm;
+            o.flags = S_F_NOSYNC | S_F_Y_TAGGED | in_flag; o.x_tag = x_cur_tag; o.y_tag = ++tag;
+            const int qkv_tag = tag;
             ops.push_back(o);
             o = sop_zero();
-            o.type = S_OP_ATTN; o.x = t.s_qkv; o.y = t.s_attn;
+            o.type = S_OP_ATTN; o.x = (const float *)t.s_qkv; o.y = (float *)t.s_attn;
             o.p2 = t.kv_k + (size_t)l * t.kv_max * KVD;
             o.p3 = t.kv_v + (size_t)l * t.kv_max * KVD;
             o.i0 = VB200_HEADS; o.i1 = VB200_KV_HEADS; o.f0 = scale; o.f1 = VB200_ROPE_THETA;
+            o.p0 = t.s_scratch;
+            o.flags = S_F_NOSYNC | S_F_X_TAGGED | S_F_Y_TAGGED; o.x_tag = qkv_tag; o.y_tag = ++tag;
+            const int part_tag = tag;
+            o.i2 = part_tag + 1;            /* with a single key slice it writes the final output itself */
             ops.push_back(o);
-            o = sop_gemv(D, QD, S_EPI_ADD, w.wo[l], t.s_attn, t.X);
-            o.res = t.X;
+            o = sop_zero();
+            o.type = S_OP_ATTN_MERGE; o.p0 = t.s_scratch; o.y = (float *)t.s_attn;
+            o.i0 = VB200_HEADS; o.i1 = VB200_KV_HEADS;
+            o.flags = S_F_NOSYNC | S_F_X_TAGGED | S_F_Y_TAGGED; o.x_tag = part_tag; o.y_tag = ++tag;
+            const int attn_tag = tag;
+            ops.push_back(o);
+            o = sop_gemv(D, QD, S_EPI_ADD, w.wo[l], (const float *)t.s_attn, (float *)t.s_xb);
+            o.res = x_cur;
+            o.flags = S_F_NOSYNC | S_F_X_TAGGED | S_F_Y_TAGGED | (x_cur_tag ? S_F_RES_TAGGED : 0);
+            o.x_tag = attn_tag; o.y_tag = ++tag;
+            const int xb_tag = tag;
             if (m.tap_on) o.tap = m.tap + (size_t)(2 * l) * D;
             ops.push_back(o);
-            o = sop_gemv(2 * HID, D, S_EPI_SWIGLU, w.w13[l], t.X, t.s_h);
+            o = sop_gemv(2 * HID, D, S_EPI_SWIGLU, w.w13[l], (const float *)t.s_xb, (float *)t.s_h);
             o.gain = L.ffn_norm;
+            o.flags = S_F_NOSYNC | S_F_X_TAGGED | S_F_Y_TAGGED; o.x_tag = xb_tag; o.y_tag = ++tag;
+            const int h_tag = tag;
             ops.push_back(o);
-            o = sop_gemv(D, HID, S_EPI_ADD, w.w2[l], t.s_h, t.X);
-            o.res = t.X;
+            o = sop_gemv(D, HID, S_EPI_ADD, w.w2[l], (const float *)t.s_h, (float *)t.s_xa);
+            o.res = (const float *)t.s_xb;
+            o.flags = S_F_NOSYNC | S_F_X_TAGGED | S_F_Y_TAGGED | S_F_RES_TAGGED; o.x_tag = h_tag; o.y_tag = ++tag;
             if (m.tap_on) o.tap = m.tap + (size_t)(2 * l + 1) * D;
             ops.push_back(o);
+            x_cur = (const float *)t.s_xa;
+            x_cur_tag = tag;
         }
         /* final RMSNorm (voxtral_tts_llm.c:267) folded into the two heads that read it; the
-         * hidden row itself goes out through xn_out */
-        SOp o = sop_gemv(NSEM, D, S_EPI_STORE, w.wsem, t.X, t.s_logits);
-        o.gain = m.dec_norm; o.bias = m.ac_sem_bias; o.xn_out = t.hidden; o.flags = S_F_NOSYNC;
+         * hidden row itself goes out through xn_out. Their outputs are plain vectors: a grid
+         * barrier separates them from the argmax. */
+        SOp o = sop_gemv(NSEM, D, S_EPI_STORE, w.wsem, x_cur, t.s_logits);
+        o.gain = m.dec_norm; o.bias = m.ac_sem_bias; o.xn_out = t.hidden;
+        o.flags = S_F_NOSYNC | S_F_X_TAGGED; o.x_tag = x_cur_tag;
         ops.push_back(o);
-        o = sop_gemv(D, D, S_EPI_STORE, w.wllm, t.X, t.ltok);
+        o = sop_gemv(D, D, S_EPI_STORE, w.wllm, x_cur, t.ltok);
         o.gain = m.dec_norm;
+        o.flags = S_F_X_TAGGED; o.x_tag = x_cur_tag;
         ops.push_back(o);
         o = sop_zero();
         o.type = S_OP_ARGMAX; o.N = NSEM; o.x = t.s_logits; o.i0 = VB200_SEM_VALID_END; o.p2 = t.codes;
         ops.push_back(o);
-        if (!t.s_prog[v] && (bt_alloc((void **)&t.s_prog[v], sizeof(SOp) * 160, &t.allocs) ||
-                             bt_alloc((void **)&t.s_wl[v], sizeof(SWeights) * 160, &t.allocs)))
+        if (tag > 255) return -1;
+        if (!t.s_prog[v] && (bt_alloc((void **)&t.s_prog[v], sizeof(SOp) * 200, &t.allocs) ||
+                             bt_alloc((void **)&t.s_wl[v], sizeof(SWeights) * 200, &t.allocs)))
             return -1;
-        if (ops.size() > 160) return -1;
+        if (ops.size() > 200) return -1;
         const std::vector<SWeights> wl = stream_weight_list(ops);
         if (cudaMemcpyAsync(t.s_prog[v], ops.data(), sizeof(SOp) * ops.size(), cudaMemcpyHostToDevice, m.st) != cudaSuccess ||
             cudaMemcpyAsync(t.s_wl[v], wl.data(), sizeof(SWeights) * wl.size(), cudaMemcpyHostToDevice, m.st) != cudaSuccess ||
@@ -834,7 +866,6 @@ static int stream_programs(Batch &t) {
             return -1;
         t.s_n[v] = (int)ops.size();
         t.s_nw[v] = (int)wl.size();
-        if (v == 1) t.s_host = ops;
     }
     t.s_tap = m.tap_on;
     t.s_table = m.audio_table;
@@ -847,10 +878,8 @@ static int stream_step(Batch &t, int variant) {
     a.ops = t.s_prog[variant]; a.n_ops = t.s_n[variant]; a.dyn = t.dyn;
     a.wl = t.s_wl[variant]; a.n_wl = t.s_nw[variant];
     a.bar_counter = t.s_counters; a.exit_counter = t.s_counters + 16; a.status = t.status;
+    a.seq = t.s_seq;
     a.wait_cycles = m.wait_cycles;
-    a.dbg = getenv("VB200_STREAM_DBG") ? atoi(getenv("VB200_STREAM_DBG")) : 0;
-    a.pf_bytes = getenv("VB200_STREAM_PF") ? atoi(getenv("VB200_STREAM_PF")) : kSPrefetchBytes;
-    a.timeline = nullptr;
     return stream_launch(a, g_sw.n_cta, m.st) == cudaSuccess ? 0 : -1;
 }
 
@@ -914,9 +943,13 @@ static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames
                    sizeof(float) * (size_t)B * VB200_KV_HEADS * kBtKeySplits * kGroup * (kHD + 2), &t.allocs);
     rc |= bt_alloc((void **)&t.tickets, sizeof(unsigned) * B * VB200_KV_HEADS, &t.allocs);
     if (stream) {
-        rc |= bt_alloc((void **)&t.s_qkv, sizeof(float) * QKV, &t.allocs);
-        rc |= bt_alloc((void **)&t.s_attn, sizeof(float) * QD, &t.allocs);
-        rc |= bt_alloc((void **)&t.s_h, sizeof(float) * HID, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_qkv, sizeof(stag_t) * QKV, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_attn, sizeof(stag_t) * QD, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_h, sizeof(stag_t) * HID, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_xa, sizeof(stag_t) * D, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_xb, sizeof(stag_t) * D, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_seq, sizeof(unsigned) * 16, &t.allocs);
+        rc |= bt_alloc((void **)&t.s_scratch, sizeof(stag_t) * (size_t)VB200_KV_HEADS * 16 * kGroup * (kHD + 2), &t.allocs);
         rc |= bt_alloc((void **)&t.s_logits, sizeof(float) * NSEM, &t.allocs);
         rc |= bt_alloc((void **)&t.s_counters, sizeof(unsigned) * 64, &t.allocs);
     }
@@ -1222,38 +1255,6 @@ int stream_step_time(int pos, int iters, float *ms_out, double *bytes_per_launch
     if (!m.inited || !m.llm_ready || !m.ac_ready || iters < 1 || pos < 0 || pos >= m.kv_max || one_ready(0)) return -1;
     Batch &t = g_one;
     if (!t.stream) return -1;
-    /* VB200_STREAM_DISSECT (measurement only; results are meaningless): 1 = no grid barriers,
-     * 2 = no attention ops, 3 = barriers only (every op replaced by an empty one) */
-    const int mode = getenv("VB200_STREAM_DISSECT") ? atoi(getenv("VB200_STREAM_DISSECT")) : 0;
-    SOp *prog = t.s_prog[1];
-    int n_prog = t.s_n[1];
-    SWeights *wlp = t.s_wl[1];
-    int n_wl = t.s_nw[1];
-    if (mode > 0) {
-        std::vector<SOp> ops;
-        for (SOp o : t.s_host) {
-            if (mode == 1) o.flags |= S_F_NOSYNC;
-            if (mode == 2 && o.type == S_OP_ATTN) continue;
-            if (mode == 3) { const int f = o.flags; o = sop_zero(); o.type = S_OP_WAIT; o.p0 = t.s_counters + 48; o.i0 = 0; o.flags = f; }
-            ops.push_back(o);
-        }
-        if (!t.s_prog_dbg && (bt_alloc((void **)&t.s_prog_dbg, sizeof(SOp) * 160, &t.allocs) ||
-                              bt_alloc((void **)&t.s_wl_dbg, sizeof(SWeights) * 160, &t.allocs)))
-            return -1;
-        const std::vector<SWeights> wl = stream_weight_list(ops);
-        if (cudaMemcpy(t.s_prog_dbg, ops.data(), sizeof(SOp) * ops.size(), cudaMemcpyHostToDevice) != cudaSuccess ||
-            cudaMemcpy(t.s_wl_dbg, wl.data(), sizeof(SWeights) * wl.size(), cudaMemcpyHostToDevice) != cudaSuccess)
-            return -1;
-        prog = t.s_prog_dbg;
-        n_prog = (int)ops.size();
-        wlp = t.s_wl_dbg;
-        n_wl = (int)wl.size();
-    }
-    struct Restore {
-        Batch &t; SOp *p; int n; SWeights *w; int nw;
-        ~Restore() { t.s_prog[1] = p; t.s_n[1] = n; t.s_wl[1] = w; t.s_nw[1] = nw; }
-    } restore{t, t.s_prog[1], t.s_n[1], t.s_wl[1], t.s_nw[1]};
-    t.s_prog[1] = prog; t.s_n[1] = n_prog; t.s_wl[1] = wlp; t.s_nw[1] = n_wl;
     t.h_in->dyn.pos = pos; t.h_in->dyn.kv_max = m.kv_max; t.h_in->dyn.frame = 0; t.h_in->dyn.done = 0;
     if (cudaMemcpyAsync(&t.d_in->dyn, &t.h_in->dyn, sizeof(VbDyn), cudaMemcpyHostToDevice, m.st) != cudaSuccess) return -1;
     for (int i = 0; i < 2; i++)
@@ -1299,10 +1300,8 @@ int stream_wait_expiry(int limit_us) {
     a.ops = d_ops; a.n_ops = 2; a.dyn = (VbDyn *)(words + 52);
     a.wl = nullptr; a.n_wl = 0;
     a.bar_counter = words + 16; a.exit_counter = words + 32; a.status = (int *)(words + 48);
+    a.seq = words + 60;
     a.wait_cycles = m.wait_cycles;       /* the other waits keep the ordinary limit: the flag wait runs out first */
-    a.dbg = 0;
-    a.pf_bytes = 0;
-    a.timeline = nullptr;
     if (cudaMemcpyAsync(d_ops, ops, sizeof(ops), cudaMemcpyHostToDevice, m.st) == cudaSuccess &&
         stream_launch(a, n_cta, m.st) == cudaSuccess && cudaStreamSynchronize(m.st) == cudaSuccess)
         cudaMemcpy(&st, words + 48, sizeof(int), cudaMemcpyDeviceToHost);

@@ -15,14 +15,13 @@
  *                     multicast). It never waits for an op's input, only for a free slot:
  *                     while the other warps sit at a grid barrier the ring fills up with the
  *                     next matrix.
- *   warps 0..11       consumers. Warp s owns ring slot s: it waits for the slot alone and
- *                     hands it back alone (warp 11 owns none). The slab order makes a warp
- *                     load 512 contiguous bytes (4 rows x 8 chunks of 8 BF16): lane = (row r,
- *                     chunk c). A lane keeps its 8 activations of the k-block in registers and
- *                     one accumulator per row step, so nothing is reduced per slot: the 8
- *                     lanes of a row and the warps are summed once per op, in fixed order
- *                     (bit-reproducible; BF16 -> fp32 is an exact shift and all products are
- *                     fp32, as in voxtral_tts_kernels.c:152-185).
+ *   warps 0..11       consumers. Warp s owns ring slot s (warps 10 and 11 own none): it waits
+ *                     for the slot alone and hands it back alone. The weights never pass
+ *                     through the CUDA cores: ldmatrix moves a 16 x 16 tile from the slot into
+ *                     registers and one mma.sync (m16n8k16, BF16 in, fp32 out) multiplies it
+ *                     by the input row, which is held as three BF16 terms (three B columns).
+ *                     Partial sums stay in registers for the whole op; the three columns and
+ *                     the warps are summed once per op, in fixed order (bit-reproducible).
  * RMSNorm is folded in: the input row is staged as x * gain, the sum of squares is taken on
  * the side, and 1/sqrt(mean + eps) multiplies the finished sums (voxtral_tts_kernels.c:333-349).
  *
@@ -44,8 +43,9 @@ namespace vb {
 
 struct SSmem {
     alignas(128) unsigned char ring[kSSlots][kSSlotBytes];
-    /* the staged input row (permuted, see s_gemv); the attention op uses the same bytes */
-    alignas(16) float xs[kSMaxK];
+    /* the staged input row as three BF16 terms in B-fragment order (see s_gemv); the attention
+     * op uses the same bytes */
+    alignas(16) uint16_t xs[3][kSMaxK];
     float part[kSConsumerWarps][kSMaxRows];     /* per-warp partial sums of the CTA's rows */
     float red[kSConsumerWarps];
     alignas(16) SOp opbuf[2];                   /* the current and the next op descriptor */
@@ -55,20 +55,10 @@ struct SSmem {
     int abort_seen;     /* the abort flag as sampled inside the last grid barrier: the same for every consumer thread */
 };
 
-/* Attention scratch, overlaid on SSmem::xs. */
-struct SAttnSmem {
-    alignas(16) float q[kSHeadDim];
-    alignas(16) float kn[kSHeadDim];
-    alignas(16) float vn[kSHeadDim];
-    float cs[kSHeadDim];
-    alignas(16) float wo[kSConsumerWarps][kSHeadDim];
-    float wml[kSConsumerWarps][2];
-};
-static_assert(sizeof(SAttnSmem) <= sizeof(float) * kSMaxK, "attention scratch must fit the row buffer");
 static_assert(sizeof(SSmem) <= 232448, "over the 227 KB a CTA may use");
 static_assert(sizeof(SOp) % 16 == 0, "op descriptors are copied in 16-byte pieces");
 static_assert(kSSlots <= kSConsumerWarps, "every ring slot needs an owner warp");
-static_assert(kSConsumerThreads >= 2 * kSHeadDim, "the attention op rotates q and k and copies v with one thread each");
+static_assert(kSConsumerThreads == 3 * kSHeadDim, "the attention op gives one pair of q, k or v values to every thread");
 
 struct SCtx {
     SSmem *s;
@@ -76,7 +66,7 @@ struct SCtx {
     int tid, warp, lane;
     unsigned chunk_counter;
     unsigned barrier_epoch;
-    int tl_op;
+    unsigned tag_base;      /* launch sequence number << 8 */
 };
 
 VB_DEVINL bool s_aborted(const SCtx &c) { return *(volatile int *)&c.s->abort_flag != 0; }
@@ -96,6 +86,38 @@ VB_DEVINL bool s_mbar_wait(SCtx &c, uint64_t *bar, uint32_t parity) {
         if (s_aborted(c)) return false;
         if (clock64() - t0 > c.a.wait_cycles) return false;
         __nanosleep(32);
+    }
+}
+
+/* ---- tagged vectors ---- */
+VB_DEVINL void s_st_tagged(stag_t *p, float v, unsigned tag) {
+    const stag_t w = ((stag_t)tag << 32) | (stag_t)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+VB_DEVINL stag_t s_ld_tagged(const stag_t *p) {
+    stag_t w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+VB_DEVINL void s_ld_tagged2(const stag_t *p, stag_t &a, stag_t &b) {
+    asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+VB_DEVINL float s_tag_value(stag_t w) { return __uint_as_float((unsigned)(w & 0xffffffffull)); }
+VB_DEVINL unsigned s_tag_of(stag_t w) { return (unsigned)(w >> 32); }
+
+/* Polls one element until it carries `tag`. Bounded; on expiry (or when another CTA has given
+ * up) the CTA's abort flag is raised and whatever was read last is returned. */
+__device__ stag_t s_poll_tagged(SCtx &c, const stag_t *p, unsigned tag) {
+    const long long t0 = clock64();
+    int spins = 0;
+    while (true) {
+        const stag_t w = s_ld_tagged(p);
+        if (s_tag_of(w) == tag) return w;
+        if (s_aborted(c)) return w;
+        if ((++spins & 63) == 0) {
+            if (vb_ld_relaxed_gpu_s32(c.a.status) != 0) { *(volatile int *)&c.s->abort_flag = 1; return w; }
+            if (clock64() - t0 > c.a.wait_cycles) { s_raise(c, S_ERR_DATA_WAIT); return w; }
+        }
     }
 }
 
@@ -129,58 +151,10 @@ __device__ bool s_grid_sync(SCtx &c) {
 /* ------------------------------------------------------------------ producer */
 /* One thread. The weight list is read one entry ahead, so an op switch costs no memory round
  * trip: the only thing this thread ever waits for is a free ring slot.
- *
- * Second level: a cursor runs `pf_bytes` ahead of the ring through the same byte sequence and
- * asks L2 for it (cp.async.bulk.prefetch.L2). The ring alone holds 4 us of this SM's share of
- * HBM; the dependent chain between two ops (epilogue, grid barrier, staging of the next input)
- * is about as long, so without the second level HBM idles at every op boundary. With it HBM
- * keeps filling L2 through the stall, and the ring then refills from L2, faster than HBM could. */
-struct SCursor {
-    const SWeights *wl;
-    int n, i;
-    const unsigned char *ptr;
-    size_t left;
-};
-
-__device__ void s_cursor_open(SCursor &k, int i) {
-    k.i = i;
-    k.left = 0;
-    k.ptr = nullptr;
-    if (i >= k.n) return;
-    const SWeights w = k.wl[i];
-    const SPlan p = stream_plan(w.N, w.K, w.epi, blockIdx.x, gridDim.x);
-    k.ptr = (const unsigned char *)w.W + (size_t)p.r0 * w.K * 2;
-    k.left = (size_t)p.n_rows * w.K * 2;
-}
-
-/* Prefetches the next `bytes` of the sequence (crossing into following matrices as needed). */
-__device__ void s_cursor_prefetch(SCursor &k, size_t bytes) {
-    while (bytes > 0 && k.i < k.n) {
-        if (k.left == 0) { s_cursor_open(k, k.i + 1); continue; }
-        const uint32_t n = (uint32_t)(k.left < bytes ? k.left : bytes);
-        vb_prefetch_l2(k.ptr, n);
-        k.ptr += n;
-        k.left -= n;
-        bytes -= n;
-    }
-}
-
+ */
 __device__ void s_produce(SCtx &c) {
     SSmem *s = c.s;
     if (c.a.n_wl <= 0) return;
-    SCursor pf;
-    pf.wl = c.a.wl; pf.n = c.a.pf_bytes > 0 ? c.a.n_wl : 0;
-    s_cursor_open(pf, 0);
-    /* the ring's own first fill needs no prefetch: start the cursor one ring ahead */
-    {
-        size_t skip = (size_t)kSSlots * kSSlotBytes;
-        while (skip > 0 && pf.i < pf.n) {
-            if (pf.left == 0) { s_cursor_open(pf, pf.i + 1); continue; }
-            const size_t n = pf.left < skip ? pf.left : skip;
-            pf.ptr += n; pf.left -= n; skip -= n;
-        }
-        for (int b = 0; b < c.a.pf_bytes; b += kSSlotBytes) s_cursor_prefetch(pf, kSSlotBytes);
-    }
     SWeights cur = c.a.wl[0];
     for (int i = 0; i < c.a.n_wl; i++) {
         const SWeights nxt = c.a.wl[i + 1 < c.a.n_wl ? i + 1 : i];
@@ -199,15 +173,110 @@ __device__ void s_produce(SCtx &c) {
             vb_mbar_arrive_expect_tx(&s->full[slot], bytes);
             vb_bulk_g2s(s->ring[slot], src, bytes, &s->full[slot]);
             src += bytes;
-            s_cursor_prefetch(pf, bytes);       /* the cursor keeps its distance */
         }
         cur = nxt;
     }
 }
 
-#define S_TL(k) do { if (c.a.timeline && blockIdx.x == 0 && c.tid == 0) c.a.timeline[c.tl_op * 8 + (k)] = clock64(); } while (0)
-
 /* ------------------------------------------------------------------ GEMV */
+/* The weight side of a GEMV op for one warp: every ring slot this warp owns, through the tensor
+ * cores, into per-warp partial sums of the CTA's rows (SSmem::part).
+ *
+ * Tensor cores as the reduction engine: one mma.sync m16n8k16 multiplies a 16-row x 16-column
+ * weight tile (A, fetched with ldmatrix from the swizzled slab rows) by the three term columns of
+ * the input (B: column t = term t, the other five columns zero) and adds into a 16 x 8 fp32
+ * fragment. Two instructions per 512 weight bytes instead of the twenty a CUDA-core dot product
+ * needs: the SM drains a full ring in a fraction of the time HBM needs to fill it.
+ * TMAX = row tiles the instantiation handles (2, 4 or 8). The eight accumulator fragments a lane
+ * holds are used as TMAX tiles x (8 / TMAX) independent sets taken in turn by the k-steps, so that
+ * a CTA with few rows does not serialise on the latency of one accumulator chain. */
+template <int TMAX>
+__device__ void s_gemv_slots(SCtx &c, const SPlan &p) {
+    SSmem *s = c.s;
+    constexpr int NSETS = 8 / TMAX;
+    const int warp = c.warp, lane = c.lane;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int T = p.T;
+    const int kb_bytes = p.n_rows * (kSBlockK * 2);
+    float acc[NSETS][TMAX][4];
+#pragma unroll
+    for (int a = 0; a < NSETS; a++)
+#pragma unroll
+        for (int t = 0; t < TMAX; t++) { acc[a][t][0] = acc[a][t][1] = acc[a][t][2] = acc[a][t][3] = 0.0f; }
+    /* ldmatrix: lane l addresses row (l & 7) + 8 * ((l >> 3) & 1) of the tile, chunk 2 * ks + (l >> 4) */
+    const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_half = lane >> 4;
+    const uint16_t *xt = gid < 3 ? &s->xs[gid][0] : nullptr;      /* this lane's term (B column), if any */
+
+    /* Ring slot s belongs to warp s: it alone waits for the slot's fills (and so sees every
+     * phase of that mbarrier in order) and hands the slot back. */
+    for (int ch = 0; ch < p.n_chunks; ch++) {
+        const unsigned g = c.chunk_counter++;
+        const unsigned slot = g % kSSlots, use = g / kSSlots;
+        if (slot != (unsigned)warp) continue;
+        if (!s_mbar_wait(c, &s->full[slot], use & 1u)) {
+            if (!s_aborted(c)) s_raise(c, S_ERR_FULL_WAIT);
+            break;      /* carry on to the CTA barriers; the results no longer matter */
+        }
+        const int kb0 = ch * p.kbs, kb1 = min(kb0 + p.kbs, p.kblocks);
+        uint32_t kb_addr = vb_smem_u32(s->ring[slot]);
+        for (int kb = kb0; kb < kb1; kb++, kb_addr += kb_bytes) {
+            uint32_t bf[4][2];
+            if (xt) {
+                const uint4 lo = *reinterpret_cast<const uint4 *>(xt + ((kb * 4 + tig) * 4) * 4);
+                const uint4 hi = *reinterpret_cast<const uint4 *>(xt + ((kb * 4 + tig) * 4 + 2) * 4);
+                bf[0][0] = lo.x; bf[0][1] = lo.y; bf[1][0] = lo.z; bf[1][1] = lo.w;
+                bf[2][0] = hi.x; bf[2][1] = hi.y; bf[3][0] = hi.z; bf[3][1] = hi.w;
+            } else {
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) bf[ks][0] = bf[ks][1] = 0u;
+            }
+#pragma unroll
+            for (int t = 0; t < TMAX; t++) {
+                if (t < T) {
+                    const int row = t * 16 + lm_row;
+                    const uint32_t row_addr = kb_addr + row * 128;
+                    uint32_t a[4][4];
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        const uint32_t addr = row_addr + (((2 * ks + lm_half) ^ (row & 7)) << 4);
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(a[ks][0]), "=r"(a[ks][1]), "=r"(a[ks][2]), "=r"(a[ks][3])
+                                     : "r"(addr));
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        float *d = acc[ks % NSETS][t];
+                        asm volatile(
+                            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                            : "r"(a[ks][0]), "r"(a[ks][1]), "r"(a[ks][2]), "r"(a[ks][3]), "r"(bf[ks][0]), "r"(bf[ks][1]));
+                    }
+                }
+            }
+        }
+        /* the slot's bytes have been read */
+        __syncwarp();
+        if (lane == 0) vb_mbar_arrive(&s->empty[slot]);
+    }
+
+    /* once per op: the accumulator sets in order, then the three term columns of a row (hi + lo
+     * in quad lane 0, lo2 in quad lane 1); the warps are summed by the caller, in fixed order */
+#pragma unroll
+    for (int t = 0; t < TMAX; t++) {
+        if (t < T) {
+            float v[4] = {acc[0][t][0], acc[0][t][1], acc[0][t][2], acc[0][t][3]};
+#pragma unroll
+            for (int a = 1; a < NSETS; a++) { v[0] += acc[a][t][0]; v[1] += acc[a][t][1]; v[2] += acc[a][t][2]; v[3] += acc[a][t][3]; }
+            const float n0 = __shfl_down_sync(0xffffffffu, v[0], 1);
+            const float n2 = __shfl_down_sync(0xffffffffu, v[2], 1);
+            if (tig == 0) {
+                s->part[warp][t * 16 + gid] = (v[0] + v[1]) + n0;
+                s->part[warp][t * 16 + gid + 8] = (v[2] + v[3]) + n2;
+            }
+        }
+    }
+}
+
 __device__ void s_gemv(SCtx &c, const SOp &op) {
     SSmem *s = c.s;
     const int K = op.K, epi = op.epi;
@@ -221,24 +290,68 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
     const float eps = op.eps;
     float *const xn_out = op.xn_out;
 
-    S_TL(0);
-    /* this thread's residual value, requested before anything else needs L2 */
-    float resv = 0.0f;
-    if (epi == S_EPI_ADD && tid < p.n_rows) resv = __ldcg(op.res + p.r0 + tid);
+    const int flags = op.flags;
+    const unsigned x_tag = c.tag_base | (unsigned)op.x_tag, y_tag = c.tag_base | (unsigned)op.y_tag;
 
-    /* Stage the input row. Inside a k-block of 64 columns, column chunk cc (8 floats) is
-     * stored as two 16-byte halves at [cc*4] and [32 + cc*4]: the 8 lanes of a row then read
-     * 128 contiguous bytes per load (no bank conflicts), the 4 row groups broadcast. */
+    /* this thread's residual value, requested before anything else needs L2. A tagged residual
+     * was written by this very thread in an earlier op (same rows, same thread), so it needs no
+     * check. */
+    float resv = 0.0f;
+    if (epi == S_EPI_ADD && tid < p.n_rows) {
+        if (flags & S_F_RES_TAGGED) resv = s_tag_value(s_ld_tagged((const stag_t *)op.res + p.r0 + tid));
+        else resv = __ldcg(op.res + p.r0 + tid);
+    }
+
+    /* Stage the input row as three BF16 terms, x * gain = hi + lo + lo2 (24 mantissa bits;
+     * BF16 x BF16 products are exact in fp32, so the tensor core multiplies what the reference
+     * multiplies and only the summation order differs). Inside a k-block the terms are stored in
+     * the order the MMA's B fragment wants them: [quad q][k-step][4] with the four values of
+     * (q, k-step) = columns 2q, 2q+1, 2q+8, 2q+9 of that 16-column step, so a lane fetches the
+     * fragments of two k-steps with one 16-byte load. */
     float ss = 0.0f;
-    for (int i = tid; i < K / 4; i += kSConsumerThreads) {
-        float4 v = __ldcg(reinterpret_cast<const float4 *>(x) + i);
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    auto stage2 = [&](int k, float va, float vb) {       /* columns k (even) and k + 1 */
+        ss += va * va + vb * vb;
         if (gain) {
-            const float4 g = __ldg(reinterpret_cast<const float4 *>(gain) + i);
-            v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
+            const float2 g = __ldg(reinterpret_cast<const float2 *>(gain + k));
+            va *= g.x; vb *= g.y;
         }
-        const int k = 4 * i, kb = k >> 6, e = k & 63;
-        *reinterpret_cast<float4 *>(&s->xs[kb * 64 + ((e >> 2) & 1) * 32 + (e >> 3) * 4]) = v;
+        const int kb = k >> 6, ks = (k >> 4) & 3, w16 = k & 15;
+        const int pos = ((kb * 4 + ((w16 & 7) >> 1)) * 4 + ks) * 4 + ((w16 >> 3) << 1);
+        uint16_t a0, a1, a2, b0, b1, b2;
+        vb_split3(va, a0, a1, a2);
+        vb_split3(vb, b0, b1, b2);
+        *reinterpret_cast<uint32_t *>(&s->xs[0][pos]) = a0 | ((uint32_t)b0 << 16);
+        *reinterpret_cast<uint32_t *>(&s->xs[1][pos]) = a1 | ((uint32_t)b1 << 16);
+        *reinterpret_cast<uint32_t *>(&s->xs[2][pos]) = a2 | ((uint32_t)b2 << 16);
+    };
+    if (flags & S_F_X_TAGGED) {
+        /* Exchange and readiness in one trip: all of this thread's 16-byte loads (two tagged
+         * elements each) go out together; an element whose tag is not there yet is polled. */
+        const stag_t *xt = (const stag_t *)x;
+        constexpr int kBatch = 6;       /* 16-byte loads in flight per thread */
+        for (int i0 = tid; i0 < K / 2; i0 += kBatch * kSConsumerThreads) {
+            stag_t wa[kBatch], wb[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) {
+                const int i = i0 + u * kSConsumerThreads;
+                if (i < K / 2) s_ld_tagged2(xt + 2 * i, wa[u], wb[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) {
+                const int i = i0 + u * kSConsumerThreads;
+                if (i < K / 2) {
+                    if (s_tag_of(wa[u]) != x_tag) wa[u] = s_poll_tagged(c, xt + 2 * i, x_tag);
+                    if (s_tag_of(wb[u]) != x_tag) wb[u] = s_poll_tagged(c, xt + 2 * i + 1, x_tag);
+                    stage2(2 * i, s_tag_value(wa[u]), s_tag_value(wb[u]));
+                }
+            }
+        }
+    } else {
+        for (int i = tid; i < K / 4; i += kSConsumerThreads) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(x) + i);
+            stage2(4 * i, v.x, v.y);
+            stage2(4 * i + 2, v.z, v.w);
+        }
     }
     if (gain) {
         ss = vb_warp_sum(ss);
@@ -252,93 +365,25 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
         for (int w = 0; w < kSConsumerWarps; w++) t += s->red[w];
         rscale = 1.0f / sqrtf(t / (float)K + eps);
         if (xn_out && blockIdx.x == 0) {
-            for (int k = tid; k < K; k += kSConsumerThreads) xn_out[k] = __ldcg(x + k) * rscale * __ldg(gain + k);
-        }
-    }
-
-    S_TL(1);
-    const int c8 = lane & 7, rg = lane >> 3;
-    const int J = p.J;
-    const int kb_bytes = p.n_rows * (kSBlockK * 2);
-    float acc[kSMaxRowSteps];
-#pragma unroll
-    for (int j = 0; j < kSMaxRowSteps; j++) acc[j] = 0.0f;
-
-    /* Ring slot s belongs to warp s: it alone waits for the slot's fills (and so sees every
-     * phase of that mbarrier in order) and hands the slot back. The owner walks every row step
-     * of every k-block in the slot. */
-    for (int ch = 0; ch < p.n_chunks; ch++) {
-        const unsigned g = c.chunk_counter++;
-        const unsigned slot = g % kSSlots, use = g / kSSlots;
-        if (slot != (unsigned)warp) continue;
-        if (!s_mbar_wait(c, &s->full[slot], use & 1u)) {
-            if (!s_aborted(c)) s_raise(c, S_ERR_FULL_WAIT);
-            break;      /* carry on to the CTA barriers below; the results no longer matter */
-        }
-        S_TL(6);
-        const int kb0 = ch * p.kbs, kb1 = min(kb0 + p.kbs, p.kblocks);
-        const unsigned char *base = s->ring[slot] + lane * 16;
-        for (int kb = (c.a.dbg & 1) ? kb1 : kb0; kb < kb1; kb++, base += kb_bytes) {
-            const float4 xa = *reinterpret_cast<const float4 *>(&s->xs[kb * 64 + c8 * 4]);
-            const float4 xb = *reinterpret_cast<const float4 *>(&s->xs[kb * 64 + 32 + c8 * 4]);
-            /* Row steps in groups of eight: the eight 16-byte loads of a group are issued
-             * together and feed eight independent accumulator chains. A row past the CTA's last
-             * one (the group is padded, and the last row step may be ragged) loads zeros. */
-#pragma unroll
-            for (int g8 = 0; g8 < kSMaxRowSteps / 8; g8++) {
-                if (g8 * 8 < J) {
-                    uint4 w[8];
-#pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        const int j = g8 * 8 + u;
-                        w[u] = make_uint4(0u, 0u, 0u, 0u);
-                        if (4 * j + rg < p.n_rows) w[u] = *reinterpret_cast<const uint4 *>(base + j * 512);
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        float a = acc[g8 * 8 + u];
-                        a = fmaf(vb_bf16_lo(w[u].x), xa.x, a); a = fmaf(vb_bf16_hi(w[u].x), xa.y, a);
-                        a = fmaf(vb_bf16_lo(w[u].y), xa.z, a); a = fmaf(vb_bf16_hi(w[u].y), xa.w, a);
-                        a = fmaf(vb_bf16_lo(w[u].z), xb.x, a); a = fmaf(vb_bf16_hi(w[u].z), xb.y, a);
-                        a = fmaf(vb_bf16_lo(w[u].w), xb.z, a); a = fmaf(vb_bf16_hi(w[u].w), xb.w, a);
-                        acc[g8 * 8 + u] = a;
-                    }
-                }
-            }
-        }
-        /* the slot's bytes are in registers */
-        __syncwarp();
-        if (lane == 0) vb_mbar_arrive(&s->empty[slot]);
-    }
-
-    S_TL(2);
-    /* once per op: the 8 column chunks of a row (lanes), then the warps, in fixed order */
-#pragma unroll
-    for (int g8 = 0; g8 < kSMaxRowSteps / 8; g8++) {
-        if (g8 * 8 < J) {
-            float v[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) v[u] = acc[g8 * 8 + u];
-#pragma unroll
-            for (int off = 1; off < 8; off <<= 1) {
-#pragma unroll
-                for (int u = 0; u < 8; u++) v[u] += __shfl_xor_sync(0xffffffffu, v[u], off);
-            }
-            if (c8 == 0) {
-#pragma unroll
-                for (int u = 0; u < 8; u++) s->part[warp][(g8 * 8 + u) * 4 + rg] = v[u];
+            for (int k = tid; k < K; k += kSConsumerThreads) {
+                const float xv = (flags & S_F_X_TAGGED) ? s_tag_value(s_ld_tagged((const stag_t *)x + k)) : __ldcg(x + k);
+                xn_out[k] = xv * rscale * __ldg(gain + k);
             }
         }
     }
+
+    /* the weights: ring slots -> tensor cores -> per-warp partial sums in shared memory */
+    if (p.T <= 2) s_gemv_slots<2>(c, p);
+    else if (p.T <= 4) s_gemv_slots<4>(c, p);
+    else s_gemv_slots<8>(c, p);
     vb_named_bar(2, kSConsumerThreads);
-    S_TL(3);
     if (warp * 32 < p.n_rows) {
         const int t = tid;
         const bool valid = t < p.n_rows;
         float sum = 0.0f;
         if (valid) {
 #pragma unroll
-            for (int w = 0; w < kSConsumerWarps; w++) sum += s->part[w][t];
+            for (int w = 0; w < kSSlots; w++) sum += s->part[w][t];
         }
         sum *= rscale;
         if (epi == S_EPI_SWIGLU) {
@@ -347,32 +392,61 @@ __device__ void s_gemv(SCtx &c, const SOp &op) {
             if (valid && (t & 1) == 0) {
                 const float r = (sum / (1.0f + expf(-sum))) * up;
                 const int o = (p.r0 + t) >> 1;
-                y[o] = r;
+                if (flags & S_F_Y_TAGGED) s_st_tagged((stag_t *)y + o, r, y_tag);
+                else y[o] = r;
                 if (tap) tap[o] = r;
             }
         } else if (valid) {
             float r = sum;
             if (bias) r += __ldg(bias + p.r0 + t);
             if (epi == S_EPI_ADD) r = resv + r;
-            y[p.r0 + t] = r;
+            if (flags & S_F_Y_TAGGED) s_st_tagged((stag_t *)y + p.r0 + t, r, y_tag);
+            else y[p.r0 + t] = r;
             if (tap) tap[p.r0 + t] = r;
         }
     }
 }
 
 /* ------------------------------------------------------------------ decode attention */
-/* op.x = [q | k | v] of the new token (6144 floats); op.y = attention output (4096);
- * op.p2 / op.p3 = this layer's K and V cache [kv_max, 1024]; i0 = query heads, i1 = KV heads;
- * f0 = softmax scale, f1 = RoPE theta. Restates voxtral_tts_llm.c:221-238 with tts_apply_rope
- * and tts_causal_attention (voxtral_tts_kernels.c:403-465, 602-634): interleaved pairs, the
- * score is scaled after the dot product, the running maximum starts at -1e30.
- * One CTA per query head (32 of the grid's CTAs work, no exchange between CTAs): warp w takes
- * the keys w, w + 12, ... with the reference's running-maximum update, eight keys per pass so
- * that their sixteen loads are in flight together; the warps are merged with log-sum-exp
- * weights in warp order. The new token's key and value are used from shared memory; the first
- * query head of each group also appends them to the cache. */
+/* Two ops. S_OP_ATTN: CTA (g, sp) serves the four query heads of KV head g on slice sp of the
+ * keys (S = ceil(keys / 32) slices, at most 16: 128 of the grid's CTAs work and every K/V row is
+ * fetched once per group, not once per head). S_OP_ATTN_MERGE: CTA h merges the S slices of
+ * query head h with log-sum-exp weights in slice order. With one slice the first op writes the
+ * result itself and the second has nothing to do.
+ *
+ * op.x = [q | k | v] of the new token (6144 elements); op.y = attention output (4096);
+ * op.p2 / op.p3 = this layer's K and V cache [kv_max, 1024]; op.p0 = the slices' partial
+ * results, tagged, [G][16][4][128 + 2]; i0 = query heads, i1 = KV heads, i2 = the tag of the
+ * final output; f0 = softmax scale, f1 = RoPE theta. Restates voxtral_tts_llm.c:221-238 with
+ * tts_apply_rope and tts_causal_attention (voxtral_tts_kernels.c:403-465, 602-634): interleaved
+ * pairs, the score is scaled after the dot product, the running maximum starts at -1e30. Inside
+ * a CTA warp w serves head w & 3 on every third key of the slice, eight keys per pass so that
+ * their sixteen loads are in flight together, with the reference's running-maximum update. The
+ * new token's key and value are used from shared memory; the CTA of the last slice also appends
+ * them to the cache. */
+constexpr int kSAttnSplits = 16;
+constexpr int kSAttnSubsets = kSConsumerWarps / 4;
+
+struct SAttnSmem {
+    alignas(16) float q[4][kSHeadDim];
+    alignas(16) float kn[kSHeadDim];
+    alignas(16) float vn[kSHeadDim];
+    alignas(16) float wo[kSConsumerWarps][kSHeadDim];
+    float wml[kSConsumerWarps][2];
+    float cm[kSAttnSplits], cl[kSAttnSplits];
+};
+static_assert(sizeof(SAttnSmem) <= sizeof(uint16_t) * 3 * kSMaxK, "attention scratch must fit the row buffer");
+
+VB_DEVINL int s_attn_slices(int nk, int grid, int G) {
+    int max_s = grid / G;
+    if (max_s > kSAttnSplits) max_s = kSAttnSplits;
+    if (max_s < 1) max_s = 1;
+    int S = (nk + 31) / 32;
+    return S > max_s ? max_s : S;
+}
+
 __device__ void s_attn(SCtx &c, const SOp &op) {
-    SAttnSmem *s = reinterpret_cast<SAttnSmem *>(c.s->xs);
+    SAttnSmem *s = reinterpret_cast<SAttnSmem *>(&c.s->xs[0][0]);
     const int tid = c.tid, warp = c.warp, lane = c.lane;
     const int pos = c.a.dyn->pos, kv_max = c.a.dyn->kv_max;
     if (pos < 0 || pos >= kv_max) {
@@ -380,53 +454,74 @@ __device__ void s_attn(SCtx &c, const SOp &op) {
         return;
     }
     const int H = op.i0, G = op.i1, group = H / G;      /* 32, 8, 4 */
-    const int h = blockIdx.x;
-    if (h >= H) return;
-    const int g = h / group;
+    const int nk = pos + 1;
+    const int S = s_attn_slices(nk, (int)gridDim.x, G);
+    const int item = blockIdx.x;
+    if (item >= G * S) return;
+    const int g = item / S, sp = item % S;
+    const int j0 = (int)((long long)nk * sp / S), j1 = (int)((long long)nk * (sp + 1) / S);
     const int kv_dim = G * kSHeadDim, q_dim = H * kSHeadDim;
     const float scale = op.f0;
     const float *Kc = (const float *)op.p2 + g * kSHeadDim, *Vc = (const float *)op.p3 + g * kSHeadDim;
-    const float *qg = op.x + (size_t)h * kSHeadDim, *kg = op.x + q_dim + g * kSHeadDim,
-                *vg = op.x + q_dim + kv_dim + g * kSHeadDim;
-    const bool writer = (h % group) == 0;
+    const bool writer = sp == S - 1;        /* its slice ends with the new token */
     constexpr int half = kSHeadDim / 2;
+    const bool tagged = (op.flags & S_F_X_TAGGED) != 0;
+    const unsigned x_tag = c.tag_base | (unsigned)op.x_tag;
 
-    /* raw values first (three loads in flight per thread group), then the rotation */
-    float ra = 0.0f, rb = 0.0f;
-    if (tid < half) { ra = __ldcg(qg + 2 * tid); rb = __ldcg(qg + 2 * tid + 1); }
-    else if (tid < 2 * half) { ra = __ldcg(kg + 2 * (tid - half)); rb = __ldcg(kg + 2 * (tid - half) + 1); }
-    else if (tid < 2 * half + kSHeadDim) { ra = __ldcg(vg + (tid - 2 * half)); }
-    if (tid < 2 * half) {
-        const int d = tid < half ? tid : tid - half;
-        const float freq = 1.0f / powf(op.f1, (float)(2 * d) / (float)kSHeadDim);
-        const float ang = (float)pos * freq;
-        const float cv = cosf(ang), sv = sinf(ang);
-        const float o0 = ra * cv - rb * sv, o1 = ra * sv + rb * cv;
-        if (tid < half) { s->q[2 * d] = o0; s->q[2 * d + 1] = o1; }
-        else {
-            s->kn[2 * d] = o0; s->kn[2 * d + 1] = o1;
+    /* one pair of raw values per thread (q: 4 heads x 64 pairs, k: 64 pairs, v: 64 pairs), then
+     * the rotation of q and k */
+    {
+        size_t e;
+        if (tid < group * half) e = (size_t)(g * group + tid / half) * kSHeadDim + 2 * (tid % half);
+        else if (tid < group * half + half) e = (size_t)q_dim + g * kSHeadDim + 2 * (tid - group * half);
+        else e = (size_t)q_dim + kv_dim + g * kSHeadDim + 2 * (tid - group * half - half);
+        float ra, rb;
+        if (tagged) {
+            const stag_t *xt = (const stag_t *)op.x;
+            stag_t wa, wb;
+            s_ld_tagged2(xt + e, wa, wb);
+            if (s_tag_of(wa) != x_tag) wa = s_poll_tagged(c, xt + e, x_tag);
+            if (s_tag_of(wb) != x_tag) wb = s_poll_tagged(c, xt + e + 1, x_tag);
+            ra = s_tag_value(wa); rb = s_tag_value(wb);
+        } else {
+            ra = __ldcg(op.x + e); rb = __ldcg(op.x + e + 1);
+        }
+        if (tid < group * half + half) {
+            const int d = tid < group * half ? tid % half : tid - group * half;
+            const float freq = 1.0f / powf(op.f1, (float)(2 * d) / (float)kSHeadDim);
+            const float ang = (float)pos * freq;
+            const float cv = cosf(ang), sv = sinf(ang);
+            const float o0 = ra * cv - rb * sv, o1 = ra * sv + rb * cv;
+            if (tid < group * half) { s->q[tid / half][2 * d] = o0; s->q[tid / half][2 * d + 1] = o1; }
+            else {
+                s->kn[2 * d] = o0; s->kn[2 * d + 1] = o1;
+                if (writer) {
+                    float *dst = (float *)op.p2 + (size_t)pos * kv_dim + g * kSHeadDim;
+                    dst[2 * d] = o0; dst[2 * d + 1] = o1;
+                }
+            }
+        } else {
+            const int d = 2 * (tid - group * half - half);
+            s->vn[d] = ra; s->vn[d + 1] = rb;
             if (writer) {
-                float *dst = (float *)op.p2 + (size_t)pos * kv_dim + g * kSHeadDim;
-                dst[2 * d] = o0; dst[2 * d + 1] = o1;
+                float *dst = (float *)op.p3 + (size_t)pos * kv_dim + g * kSHeadDim;
+                dst[d] = ra; dst[d + 1] = rb;
             }
         }
-    } else if (tid < 2 * half + kSHeadDim) {
-        const int d = tid - 2 * half;
-        s->vn[d] = ra;
-        if (writer) ((float *)op.p3)[(size_t)pos * kv_dim + g * kSHeadDim + d] = ra;
     }
     vb_named_bar(2, kSConsumerThreads);
 
-    const float4 q4 = *reinterpret_cast<const float4 *>(&s->q[4 * lane]);
+    const int hh = warp & 3, ss = warp >> 2;
+    const float4 q4 = *reinterpret_cast<const float4 *>(&s->q[hh][4 * lane]);
     float mx = -1e30f, den = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     constexpr int kKeysPerPass = 8;
-    for (int jb = warp; jb <= pos; jb += kKeysPerPass * kSConsumerWarps) {
+    for (int jb = j0 + ss; jb < j1; jb += kKeysPerPass * kSAttnSubsets) {
         float4 kq[kKeysPerPass], vq[kKeysPerPass];
 #pragma unroll
         for (int u = 0; u < kKeysPerPass; u++) {
-            const int j = jb + u * kSConsumerWarps;
-            if (j < pos) {
+            const int j = jb + u * kSAttnSubsets;
+            if (j < j1 && j < pos) {
                 kq[u] = vb_ldcg4(Kc + (size_t)j * kv_dim + 4 * lane);
                 vq[u] = vb_ldcg4(Vc + (size_t)j * kv_dim + 4 * lane);
             } else if (j == pos) {
@@ -448,7 +543,7 @@ __device__ void s_attn(SCtx &c, const SOp &op) {
         }
 #pragma unroll
         for (int u = 0; u < kKeysPerPass; u++) {
-            if (jb + u * kSConsumerWarps > pos) break;
+            if (jb + u * kSAttnSubsets >= j1) break;
             const float d = dq[u] * scale;
             const float4 vv = vq[u];
             if (d > mx) {
@@ -467,19 +562,80 @@ __device__ void s_attn(SCtx &c, const SOp &op) {
     *reinterpret_cast<float4 *>(&s->wo[warp][4 * lane]) = o;
     if (lane == 0) { s->wml[warp][0] = mx; s->wml[warp][1] = den; }
     vb_named_bar(2, kSConsumerThreads);
-    if (tid < kSHeadDim) {
+
+    /* merge the key subsets of each head: element = (head, dim) */
+    const unsigned out_tag = c.tag_base | (unsigned)(S == 1 ? op.i2 : op.y_tag);
+    for (int e = tid; e < group * kSHeadDim; e += kSConsumerThreads) {
+        const int th = e / kSHeadDim, td = e % kSHeadDim;
         float M0 = -1e30f;
 #pragma unroll
-        for (int w = 0; w < kSConsumerWarps; w++) M0 = fmaxf(M0, s->wml[w][0]);
+        for (int u = 0; u < kSAttnSubsets; u++) M0 = fmaxf(M0, s->wml[u * 4 + th][0]);
         float L = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kSConsumerWarps; w++) {
-            const float lw = s->wml[w][1];
-            const float e = lw > 0.0f ? expf(s->wml[w][0] - M0) : 0.0f;
-            L += lw * e;
-            O += s->wo[w][tid] * e;
+        for (int u = 0; u < kSAttnSubsets; u++) {
+            const float lw = s->wml[u * 4 + th][1];
+            const float w = lw > 0.0f ? expf(s->wml[u * 4 + th][0] - M0) : 0.0f;
+            L += lw * w;
+            O += s->wo[u * 4 + th][td] * w;
         }
-        op.y[(size_t)h * kSHeadDim + tid] = L > 0.0f ? O * (1.0f / L) : 0.0f;
+        if (S == 1) {
+            const float r = L > 0.0f ? O * (1.0f / L) : 0.0f;
+            const size_t oi = (size_t)(g * group + th) * kSHeadDim + td;
+            if (op.flags & S_F_Y_TAGGED) s_st_tagged((stag_t *)op.y + oi, r, out_tag);
+            else op.y[oi] = r;
+        } else {
+            stag_t *mine = (stag_t *)op.p0 + ((size_t)(g * kSAttnSplits + sp) * group + th) * (kSHeadDim + 2);
+            s_st_tagged(mine + td, O, out_tag);
+            if (td == 0) { s_st_tagged(mine + kSHeadDim, M0, out_tag); s_st_tagged(mine + kSHeadDim + 1, L, out_tag); }
+        }
+    }
+}
+
+/* op.p0 = the slices' partial results (written by the S_OP_ATTN op before, tag x_tag);
+ * op.y = attention output, written with y_tag; i0, i1 as above. One CTA per query head. */
+__device__ void s_attn_merge(SCtx &c, const SOp &op) {
+    SAttnSmem *s = reinterpret_cast<SAttnSmem *>(&c.s->xs[0][0]);
+    const int tid = c.tid;
+    const int pos = c.a.dyn->pos, kv_max = c.a.dyn->kv_max;
+    if (pos < 0 || pos >= kv_max) return;       /* reported by the op before */
+    const int H = op.i0, G = op.i1, group = H / G;
+    const int S = s_attn_slices(pos + 1, (int)gridDim.x, G);
+    const int h = blockIdx.x;
+    if (S == 1 || h >= H) return;
+    const int g = h / group, th = h % group;
+    const unsigned x_tag = c.tag_base | (unsigned)op.x_tag;
+    const stag_t *base = (const stag_t *)op.p0 + ((size_t)(g * kSAttnSplits) * group + th) * (kSHeadDim + 2);
+    const size_t slice_stride = (size_t)group * (kSHeadDim + 2);
+    if (tid < 2 * S) {
+        const int u = tid >> 1;
+        const stag_t w = s_poll_tagged(c, base + u * slice_stride + kSHeadDim + (tid & 1), x_tag);
+        if (tid & 1) s->cl[u] = s_tag_value(w);
+        else s->cm[u] = s_tag_value(w);
+    }
+    float ov[kSAttnSplits];
+    if (tid < kSHeadDim) {
+#pragma unroll
+        for (int u = 0; u < kSAttnSplits; u++)
+            ov[u] = u < S ? s_tag_value(s_poll_tagged(c, base + u * slice_stride + tid, x_tag)) : 0.0f;
+    }
+    vb_named_bar(2, kSConsumerThreads);
+    if (tid < kSHeadDim) {
+        float Mg = -1e30f;
+        for (int u = 0; u < S; u++) Mg = fmaxf(Mg, s->cm[u]);
+        float Lg = 0.0f, Og = 0.0f;
+#pragma unroll
+        for (int u = 0; u < kSAttnSplits; u++) {
+            if (u < S) {
+                const float lu = s->cl[u];
+                const float w = lu > 0.0f ? expf(s->cm[u] - Mg) : 0.0f;
+                Lg += lu * w;
+                Og += ov[u] * w;
+            }
+        }
+        const float r = Lg > 0.0f ? Og * (1.0f / Lg) : 0.0f;
+        const size_t oi = (size_t)h * kSHeadDim + tid;
+        if (op.flags & S_F_Y_TAGGED) s_st_tagged((stag_t *)op.y + oi, r, c.tag_base | (unsigned)op.y_tag);
+        else op.y[oi] = r;
     }
 }
 
@@ -570,11 +726,12 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
     SCtx c;
     c.s = s; c.a = a;
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
-    c.chunk_counter = 0; c.barrier_epoch = 0; c.tl_op = 0;
+    c.chunk_counter = 0; c.barrier_epoch = 0;
 
     /* a device-resident run that has ended: its remaining queued launches do nothing (the flag
      * was written by an earlier launch, so the whole grid agrees) */
     if (a.dyn->done) return;
+    c.tag_base = *(volatile const unsigned *)a.seq << 8;     /* written by the previous launch's last CTA */
 
     constexpr int kOpVecs = (int)(sizeof(SOp) / 16);
     if (c.tid == 0) {
@@ -599,7 +756,20 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
              * own parameters. The CTA barrier makes op oi's copy visible to every thread and
              * tells the copying threads that nobody reads op oi-1's buffer any more. */
             if (c.tid < kOpVecs) s_cp_async_wait_all();
-            vb_named_bar(3, kSConsumerThreads);
+            /* the same barrier tells every thread whether any thread of the CTA has given up
+             * (ops that exchange tagged data have no grid barrier between them to learn it at) */
+            {
+                int any;
+                asm volatile(
+                    "{\n\t.reg .pred p, q;\n\t"
+                    "setp.ne.b32 p, %1, 0;\n\t"
+                    "barrier.cta.red.or.pred q, 3, %2, p;\n\t"
+                    "selp.b32 %0, 1, 0, q;\n\t}"
+                    : "=r"(any)
+                    : "r"(s_aborted(c) ? 1 : 0), "r"(kSConsumerThreads)
+                    : "memory");
+                if (any) break;
+            }
             if (c.tid < kOpVecs && oi + 1 < a.n_ops)
                 s_cp_async16(reinterpret_cast<uint4 *>(&s->opbuf[(oi + 1) & 1]) + c.tid,
                              reinterpret_cast<const uint4 *>(a.ops + oi + 1) + c.tid);
@@ -608,16 +778,13 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
             switch (op.type) {
             case S_OP_GEMV:   s_gemv(c, op); break;
             case S_OP_ATTN:   s_attn(c, op); break;
+            case S_OP_ATTN_MERGE: s_attn_merge(c, op); break;
             case S_OP_EMBED:  s_embed(c, op); break;
             case S_OP_ARGMAX: s_argmax(c, op); break;
             case S_OP_WAIT:   s_wait_flag(c, op); break;
             default: if (c.tid == 0) s_raise(c, S_ERR_BAD_OP); break;
             }
-            S_TL(4);
-            const bool stop = !(flags & S_F_NOSYNC) && oi + 1 < a.n_ops && s_grid_sync(c);
-            S_TL(5);
-            c.tl_op++;
-            if (stop) break;
+            if (!(flags & S_F_NOSYNC) && oi + 1 < a.n_ops && s_grid_sync(c)) break;
         }
         if (c.tid < kOpVecs) s_cp_async_wait_all();
     }
@@ -641,6 +808,7 @@ __global__ void __launch_bounds__(kSThreads, 1) vb_stream_kernel(SArgs a) {
         if (t == gridDim.x - 1) {
             *a.bar_counter = 0u;
             *a.exit_counter = 0u;
+            *a.seq = (c.tag_base >> 8) + 1u;        /* the next launch's tags differ from this one's */
             __threadfence();
         }
     }
@@ -663,7 +831,8 @@ __global__ void vb_stream_slab_kernel(uint4 *dst, const uint4 *src, int N, int K
     const size_t li = i - (size_t)r0 * vec_per_row;              /* vector index inside the slab */
     const unsigned kb = (unsigned)(li / ((size_t)n_rows * 8)), within = (unsigned)(li % ((size_t)n_rows * 8));
     const unsigned r = within / 8, v = within % 8;
-    dst[i] = src[((size_t)(r0 + r) * K + (size_t)kb * kSBlockK) / 8 + v];
+    /* physical 16-byte chunk v of slab row r holds the row's chunk v ^ (r & 7) */
+    dst[i] = src[((size_t)(r0 + r) * K + (size_t)kb * kSBlockK) / 8 + (v ^ (r & 7))];
 }
 
 int stream_make_slabs(uint16_t *d_dst, const uint16_t *d_src, int N, int K, int epi, int n_cta, cudaStream_t st) {
@@ -728,7 +897,7 @@ __global__ void vb_stream_fill_kernel(uint16_t *p, size_t n, uint32_t seed) {
  * copies that no op finds its weights in L2), `reps` launches between two events on the default
  * stream. sync = 1: a grid barrier after every op (as in a decoder step); 0: none. A measurement
  * and profiling aid with a small memory footprint. */
-int stream_probe(int N, int K, int n_ops, int sync, int reps, int dbg, float *ms_out, double *bytes_per_launch) {
+int stream_probe(int N, int K, int n_ops, int sync, int reps, float *ms_out, double *bytes_per_launch) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return -1;
     const int n_cta = stream_max_ctas(dev);
@@ -770,9 +939,8 @@ int stream_probe(int N, int K, int n_ops, int sync, int reps, int dbg, float *ms
         SArgs a;
         a.ops = d_ops; a.n_ops = n_ops; a.dyn = (VbDyn *)(words + 52);
         a.wl = d_wl; a.n_wl = n_ops;
-        a.bar_counter = words; a.exit_counter = words + 16; a.status = (int *)(words + 32);
-        a.wait_cycles = 2000000000LL; a.dbg = dbg; a.timeline = nullptr;
-        a.pf_bytes = getenv("VB200_STREAM_PF") ? atoi(getenv("VB200_STREAM_PF")) : kSPrefetchBytes;
+        a.bar_counter = words; a.exit_counter = words + 16; a.status = (int *)(words + 32); a.seq = words + 40;
+        a.wait_cycles = 2000000000LL;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
         for (int i = 0; i < 2 && ok; i++) ok = stream_launch(a, n_cta, 0) == cudaSuccess;
         cudaEventRecord(e0, 0);
@@ -782,24 +950,6 @@ int stream_probe(int N, int K, int n_ops, int sync, int reps, int dbg, float *ms
         int st = 0;
         cudaMemcpy(&st, words + 32, sizeof(int), cudaMemcpyDeviceToHost);
         if (st) break;
-        if (getenv("VB200_STREAM_TL")) {
-            long long *tl = nullptr;
-            if (cudaMalloc(&tl, sizeof(long long) * 8 * n_ops) == cudaSuccess) {
-                cudaMemset(tl, 0, sizeof(long long) * 8 * n_ops);
-                a.timeline = tl;
-                stream_launch(a, n_cta, 0);
-                cudaDeviceSynchronize();
-                std::vector<long long> h(8 * n_ops);
-                cudaMemcpy(h.data(), tl, sizeof(long long) * 8 * n_ops, cudaMemcpyDeviceToHost);
-                for (int i = 0; i < n_ops; i++) {
-                    fprintf(stderr, "op %2d:", i);
-                    for (int k = 0; k < 7; k++) fprintf(stderr, " %8.2f", (double)(h[8 * i + k] - h[0]) / 1965.0);
-                    fprintf(stderr, "\n");
-                }
-                cudaFree(tl);
-                a.timeline = nullptr;
-            }
-        }
         if (ms_out) cudaEventElapsedTime(ms_out, e0, e1);
         if (bytes_per_launch) *bytes_per_launch = 2.0 * (double)wn * n_ops;
         rc = 0;
