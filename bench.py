@@ -364,6 +364,8 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="with N > 1 ranks: ONE utterance, the decoder tensor-parallel over the N GPUs (strong scaling) "
                          "instead of one utterance per GPU")
+    ap.add_argument("--no-streaming-leg", action="store_true",
+                    help="skip the extra measurement with the decoder step on the persistent streaming kernel")
     ap.add_argument("--utterances", type=int, default=8,
                     help="utterances per GPU of the additional lock-step measurement (1 = skip it)")
     ap.add_argument("--swiglu", action="store_true", help="--micro gemm: SwiGLU epilogue instead of split-K partials")
@@ -606,6 +608,34 @@ def main():
                    "hbm_frac": step_bytes / (bmax / Kb / 1000.0) / 1e9 / peak,
                    "workload": "config 5 per GPU: 8 utterances, 256-row prompts, lock-step frames"}
 
+    # ---- the other decoder-step kernel: one launch of the persistent streaming kernel per frame ----
+    streaming = None
+    if on_tc and not tp and not args.no_streaming_leg:
+        Ks, Ws = min(K, 64), min(W, 5)
+        assert Lb.vb200_set_option(b"decoder_kernel", 1) == 0
+        try:
+            eng.prefill(rows, 0)
+            assert Lb.vb200_utterance_begin(first.ctypes.data, PROMPT_ROWS, noise.ctypes.data, Ws + Ks) == 0
+            assert Lb.vb200_utterance_run(Ws) == 0
+            torch.cuda.synchronize()
+            barrier()
+            assert Lb.vb200_utterance_run(Ks) == 0
+            sdone, send, sms = C.c_int(0), C.c_int(0), C.c_float(0.0)
+            assert Lb.vb200_utterance_end(None, C.byref(sdone), C.byref(send), C.byref(sms)) == 0
+            sval, smax = aggregate(sms.value, Ks, dist)
+            stms, stb = C.c_float(0.0), C.c_double(0.0)
+            mid = PROMPT_ROWS + (W + K) // 2
+            assert Lb.vb200_stream_step_ms(mid, 10, C.byref(stms), C.byref(stb)) == 0
+            step_ms = stms.value / 10
+            streaming = {"decoder_kernel": "vb_stream_kernel (26 layers + semantic head + llm token + argmax: one launch)",
+                         "value": sval, "unit": "frames/s", "steps": Ks, "ms_per_step": smax / Ks,
+                         "launches_per_frame": 1 + (pkg.FLOW_STEPS - 1) * (2 + pkg.AC_LAYERS * 7) + 1,
+                         "step_launch_ms": step_ms, "step_cache_row": mid, "step_algorithmic_bytes": stb.value,
+                         "step_achieved_gbs": stb.value / (step_ms / 1000.0) / 1e9,
+                         "step_frac": stb.value / (step_ms / 1000.0) / 1e9 / peak}
+        finally:
+            Lb.vb200_set_option(b"decoder_kernel", 0)
+
     if tp:
         barrier()                                            # nobody unmaps an arena a peer may still write to
     if rank != 0:
@@ -629,7 +659,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": "frames/s", "steps": Ke,
                     "h2d_bytes_per_step": 16 + 3072 * 4 + 36 * 4, "d2h_bytes_per_step": 176 + 3072 * 4},
             "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu,
-            "batched": batched,
+            "batched": batched, "streaming_decoder": streaming,
             "utterance": {"prefill_rows": PROMPT_ROWS, "prefill_ms": min(prefill_ms),
                           "first_frame_after_ms": min(prefill_ms) + 1000.0 / e2e_value,
                           "frames": 212,

@@ -98,11 +98,15 @@ int vb200_tp_plan(int rank, int world, int n_sm, int *out9);
 int vb200_frame_on_tensor_cores(void);
 
 /* 1 when the decoder step of vb200_frame / vb200_utterance_* runs as one launch of the
- * persistent streaming kernel (the default on one GPU; VB200_NO_STREAM=1 selects the GEMM graph). */
+ * persistent streaming kernel (option "decoder_kernel" = 1), 0 when it runs as GEMM launches of the
+ * frame graph (the default). */
 int vb200_frame_on_stream_kernel(void);
 
 /* Options by name. "ignore_end" (0/1): a device-resident run started after this call
- * treats END as an ordinary code, for fixed-length timing runs. "wait_limit_us": the limit of
+ * treats END as an ordinary code, for fixed-length timing runs. "decoder_kernel" (0/1): the
+ * decoder step of vb200_frame / vb200_utterance_* runs as GEMM launches inside the frame graph
+ * (0, default) or as one launch of the persistent streaming kernel (1; one GPU only). Both give
+ * the same results within the summation-order tolerance. "wait_limit_us": the limit of
  * every wait inside the streaming decoder kernel (default about one second); when a wait runs
  * out the call returns -1 and vb200_last_status() names the wait. Returns -1 for an unknown
  * name or value. */

@@ -212,6 +212,15 @@ int vb200_set_option(const char *name, int value) {
         }
         return 0;
     }
+    if (!strcmp(name, "decoder_kernel")) {
+        if (value != 0 && value != 1) return -1;
+        if ((value != 0) != model().decoder_stream) {
+            if (model().st) cudaStreamSynchronize(model().st);
+            model().decoder_stream = value != 0;
+            single_path_changed();
+        }
+        return 0;
+    }
     if (!strcmp(name, "wait_limit_us")) {
         if (value < 1) return -1;
         model().wait_cycles = (long long)value * 2000;   /* SM clock, about 2 GHz */

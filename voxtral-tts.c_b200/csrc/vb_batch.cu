@@ -466,7 +466,7 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
 template <bool TP>
 __global__ void __launch_bounds__(1024)
 bt_final_kernel(float *hidden, uint16_t *terms, int rows_pad, const float *X, const float *part, int n_part,
-                size_t part_stride, const float *gain, float eps, const typename TcWaitSel<TP>::type wait) {
+                size_t part_stride, const float *gain, float eps, float *tap, const typename TcWaitSel<TP>::type wait) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -493,6 +493,7 @@ bt_final_kernel(float *hidden, uint16_t *terms, int rows_pad, const float *X, co
 #pragma unroll
             for (int p = 0; p < kTcMaxSplits; p++) s += pp[i][p];     /* split order; unused splits add 0 */
             v[i] = xv[i] + s;
+            if (tap) tap[(size_t)b * D + tid + i * 1024] = v[i];       /* residual stream after the last layer */
             ss += v[i] * v[i];
         }
     }
@@ -639,6 +640,12 @@ void batch_options_changed() {
 static void ctx_close(Batch &t);
 void batch_close() { ctx_close(g_bt); }
 
+/* The decoder-step kernel of the single-utterance calls was switched: reopen that context on
+ * its next use. */
+void single_path_changed() {
+    if (g_one.open) ctx_close(g_one);
+}
+
 /* ---- tensor parallelism: set-up ---- */
 void tp_close() {
     Tp &t = g_tp;
@@ -723,10 +730,9 @@ void batch_free_all() {
 }
 
 /* ---- the streaming decoder step (vb_stream.cu) ---- */
-static bool stream_wanted() {
-    static const bool off = getenv("VB200_NO_STREAM") != nullptr;
-    return !off;
-}
+/* Which kernel runs the decoder step of the single-utterance calls: the GEMM graph (default) or
+ * the persistent streaming kernel (vb200_set_option("decoder_kernel", 1), or VB200_STREAM=1). */
+static bool stream_wanted() { return model().decoder_stream; }
 
 static int stream_weights() {
     Model &m = model();
@@ -966,6 +972,7 @@ static int ctx_open(Batch &t, bool single, int n_utt, int kv_max, int max_frames
     t.ac.sd.noise = (size_t)max_frames * A; t.ac.sd.codes_all = (size_t)max_frames * VB200_CODES;
     if (cudaEventCreate(&t.e0) != cudaSuccess || cudaEventCreate(&t.e1) != cudaSuccess) { ctx_close(t); return -1; }
     t.stream = stream;
+    t.s_tap = m.tap_on;
     if (stream && stream_programs(t)) { ctx_close(t); return -1; }
     t.open = true;
     return 0;
@@ -1006,9 +1013,12 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
     for (int l = 0; l < VB200_DEC_LAYERS; l++) {
         const LayerDev &L = m.dec[l];
         const int NL = VB200_DEC_LAYERS;      /* every exchanged buffer is filled once per layer */
+        /* residual-stream taps (single utterance only): after the attention half and after the
+         * FFN half of every layer, as the parity tests read them (voxtral_tts_llm.c:245,263) */
+        float *const tap_base = (t.single && m.tap_on) ? m.tap : nullptr;
         if (l == 0) tc_prepare(t.aD, t.X, D, B, nullptr, 0, 0, nullptr, nullptr, L.attn_norm, t.ssq, st);
         else tc_prepare(t.aD, nullptr, D, B, t.part_w2, s_w2, psD, t.X, t.X, L.attn_norm, t.ssq, st,
-                        tp_wait_for(0, TP_W2, NL, l, t.status));
+                        tp_wait_for(0, TP_W2, NL, l, t.status), tap_base ? tap_base + (size_t)(2 * l - 1) * D : nullptr);
         TcGemm g;
         g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
         g.epi = TC_EPI_PARTIAL; g.out = t.part_qkv; g.splits = s_qkv; g.ld_out = QKV;
@@ -1030,7 +1040,7 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
         if (tp) { g.tile0 = o0; g.n_tiles = on; g.push = tp_push(0, TP_WO, NL, l + 1); }
         if (tc_gemm(w.wo[l], t.aQ, g, st)) return -1;
         tc_prepare(t.aD, nullptr, D, B, t.part_wo, s_wo, psD, t.X, t.X, L.ffn_norm, t.ssq, st,
-                   tp_wait_for(0, TP_WO, NL, l + 1, t.status));
+                   tp_wait_for(0, TP_WO, NL, l + 1, t.status), tap_base ? tap_base + (size_t)(2 * l) * D : nullptr);
         g = TcGemm();
         g.M = B; g.status = t.status; g.eps = VB200_NORM_EPS;
         g.epi = TC_EPI_SWIGLU_TERMS; g.out_terms = t.bH; g.out_rows_pad = 16;
@@ -1046,13 +1056,14 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
         }
         if (tc_gemm(w.w2[l], t.aH, g, st)) return -1;
     }
+    float *const last_tap = (t.single && m.tap_on) ? m.tap + (size_t)(2 * VB200_DEC_LAYERS - 1) * D : nullptr;
     if (tp)
         launch_pdl(bt_final_kernel<true>, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
-                   (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS,
+                   (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS, last_tap,
                    tp_wait_for(0, TP_W2, VB200_DEC_LAYERS, VB200_DEC_LAYERS, t.status));
     else
         launch_pdl(bt_final_kernel<false>, dim3(B), dim3(1024), 0, st, t.hidden, t.bD, 16, (const float *)t.X,
-                   (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS, TcNoWait());
+                   (const float *)t.part_w2, s_w2, psD, (const float *)m.dec_norm, VB200_NORM_EPS, last_tap, TcNoWait());
     TcGemm g;
     g.M = B; g.status = t.status;
     /* semantic head + argmax (voxtral_tts_acoustic.c:283-309), llm token (:204) */
@@ -1315,10 +1326,7 @@ bool single_tc_usable() {
     Model &m = model();
     static const bool off = getenv("VB200_NO_TC") != nullptr;
     if (off || !m.inited || !m.llm_ready || !m.ac_ready || !acoustic_tc_ready()) return false;
-    /* per-layer taps exist on the streaming decoder step (and on the fallback engine), not on
-     * the GEMM graph */
-    if (m.tap_on) return !g_tp.on && stream_wanted();
-    return true;
+    return true;     /* per-layer taps exist on both decoder-step paths */
 }
 
 /* 1 when the single-utterance calls run their decoder step on the streaming kernel. */
@@ -1329,7 +1337,14 @@ static int one_ready(int frames) {
     Model &m = model();
     Batch &t = g_one;
     if (t.open && t.kv_k == m.kv_k && t.kv_max == m.kv_max && frames <= t.alloc_cap) {
-        if (!t.stream) return bt_weights();
+        if (!t.stream) {
+            if (t.s_tap != m.tap_on) {          /* the tap pointers are arguments of the captured launches */
+                if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
+                drop_graphs(t);
+                t.s_tap = m.tap_on;
+            }
+            return bt_weights();
+        }
         if (t.s_tap != m.tap_on || t.s_table != m.audio_table) {   /* both are part of the op lists */
             if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
             drop_graphs(t);

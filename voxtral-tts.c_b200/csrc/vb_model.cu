@@ -92,6 +92,7 @@ int model_init(int kv_cache_max) {
         return -1;
     }
     if (getenv("VB200_PREFETCH")) m.prefetch_chunks = atoi(getenv("VB200_PREFETCH"));
+    if (getenv("VB200_STREAM")) m.decoder_stream = atoi(getenv("VB200_STREAM")) != 0;
     const char *cta_env = getenv("VB200_CTAS");
     if (cta_env && atoi(cta_env) > 0 && atoi(cta_env) < m.n_cta) m.n_cta = atoi(cta_env);
 

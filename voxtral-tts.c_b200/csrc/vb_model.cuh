@@ -81,6 +81,7 @@ struct Model {
     bool tap_on = false;
     int prefetch_chunks = kPrefetchChunks;   /* VB200_PREFETCH overrides */
     bool ignore_end = false;      /* timed runs: an END code does not stop a device-resident run */
+    bool decoder_stream = false;  /* decoder step of the single-utterance calls on the persistent streaming kernel */
     long long wait_cycles = 2000000000LL;   /* limit of the waits inside the streaming decoder kernel (~1 s) */
     Program p_llm, p_ac, p_frame, p_chain, p_pv, p_run_first, p_run_next;
     float *noise_all = nullptr;   /* device-resident run: [frames, 36] */
@@ -149,6 +150,7 @@ void tp_close();
 void batch_close();
 void batch_invalidate();
 void batch_options_changed();
+void single_path_changed();
 void batch_free_all();
 
 int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);

@@ -484,7 +484,7 @@ template <bool TP>
 __global__ void vb_tc_prepare_kernel(uint16_t *buf, int rows_pad, int K, const float *x, int ldx,
                                      const float *partials, int n_part, size_t part_stride,
                                      const float *residual, float *x_out, const float *gain, float *ssq,
-                                     const typename TcWaitSel<TP>::type wait) {
+                                     float *tap, const typename TcWaitSel<TP>::type wait) {
     __shared__ float red[8];
     pdl_launch_dependents();
     pdl_wait();
@@ -517,6 +517,7 @@ __global__ void vb_tc_prepare_kernel(uint16_t *buf, int rows_pad, int K, const f
             v = *reinterpret_cast<const float4 *>(x + (size_t)m * ldx + c);
         }
         if (x_out) *reinterpret_cast<float4 *>(x_out + (size_t)m * ldx + c) = v;
+        if (tap) *reinterpret_cast<float4 *>(tap + (size_t)m * ldx + c) = v;     /* residual-stream tap for parity checks */
         ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         if (gain) {
             const float4 g = __ldg(reinterpret_cast<const float4 *>(gain + c));
@@ -547,14 +548,15 @@ int tc_prepare_chunks(int K) { return (K + 1023) / 1024; }
 
 void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float *partials, int n_part,
                 size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
-                cudaStream_t st, const TcWait &wait) {
+                cudaStream_t st, const TcWait &wait, float *tap) {
     if (M <= 0) return;
     if (wait.n > 0)
         launch_pdl(vb_tc_prepare_kernel<true>, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf,
-                   acts.rows_pad, acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, wait);
+                   acts.rows_pad, acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, tap, wait);
     else
         launch_pdl(vb_tc_prepare_kernel<false>, dim3(tc_prepare_chunks(acts.K), M), dim3(256), 0, st, acts.buf,
-                   acts.rows_pad, acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, TcNoWait());
+                   acts.rows_pad, acts.K, x, ldx, partials, n_part, part_stride, residual, x_out, gain, ssq, tap,
+                   TcNoWait());
 }
 
 /* y[i] = sum over the split-K partials in fixed order (+ bias[i % N]). */

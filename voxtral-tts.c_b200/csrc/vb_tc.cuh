@@ -117,7 +117,7 @@ int tc_prepare_chunks(int K);                      /* column chunks (and ssq ent
  * (RMSNorm's scalar is applied by the consuming GEMM). */
 void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float *partials, int n_part,
                 size_t part_stride, const float *residual, float *x_out, const float *gain, float *ssq,
-                cudaStream_t st, const TcWait &wait = TcWait());
+                cudaStream_t st, const TcWait &wait = TcWait(), float *tap = nullptr);
 
 int tc_gemm(const TcWeight &w, const TcActs &acts, const TcGemm &g, cudaStream_t st);
 
