@@ -25,9 +25,8 @@
 #include "voxtral_tts.h"
 #include "voxtral_tts_kernels.h"
 #include "voxtral_tts_safetensors.h"
-#ifdef USE_CUDA
-#include "voxtral_b200.h"      /* the library's copy of the reference's voxtral_tts_cuda.h surface */
-#endif
+/* with -DUSE_CUDA voxtral_tts_kernels.h pulls in the reference's voxtral_tts_cuda.h, whose
+ * entry points libvoxtral_b200.so exports under the same names */
 
 #include <inttypes.h>
 #include <stdio.h>

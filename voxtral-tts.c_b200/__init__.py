@@ -273,6 +273,41 @@ class SynthModel:
     def audio_table(self):
         return self.t["mm_audio_embeddings.audio_codebook_embeddings.embeddings.weight"]
 
+    def write_safetensors(self, path, token_table=True):
+        """Writes the tensors as a safetensors file the reference's reader accepts
+        (voxtral_tts_safetensors.c:71-283: 8-byte little-endian header length, JSON with dtype /
+        shape / data_offsets per tensor, then the raw data; matrices BF16, gains F32), so that
+        tts_llm_load / tts_acoustic_load / tts_audio_embed_load can be run on the synthetic
+        checkpoint. The 131072-row token table (0.8 GB) is generated on the way out."""
+        import json
+        import struct
+        items = [(k, v) for k, v in self.t.items()]
+        header, off = {}, 0
+        tok_name = "mm_audio_embeddings.tok_embeddings.weight"
+        sizes = []
+        for name, a in items:
+            dt = "BF16" if a.dtype == np.uint16 else "F32"
+            n = a.size * a.dtype.itemsize
+            header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + n]}
+            sizes.append(n)
+            off += n
+        if token_table:
+            n = VOCAB * DIM * 2
+            header[tok_name] = {"dtype": "BF16", "shape": [VOCAB, DIM], "data_offsets": [off, off + n]}
+            off += n
+        blob = json.dumps(header, separators=(",", ":")).encode()
+        blob += b" " * ((8 - len(blob) % 8) % 8)
+        with open(path, "wb") as f:
+            f.write(struct.pack("<Q", len(blob)))
+            f.write(blob)
+            for _, a in items:
+                np.ascontiguousarray(a).tofile(f)
+            if token_table:
+                rows = 8192
+                for r0 in range(0, VOCAB, rows):
+                    synth_bf16((rows, DIM), self.seed, tok_name, first=r0 * DIM).tofile(f)
+        return path
+
 
 # --------------------------------------------------------------------------
 # thin object over the C ABI (one context per process, like the reference)
