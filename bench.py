@@ -91,26 +91,10 @@ def prompt_rows(pkg, model, seed):
 
 
 def noise_rows(seed, n):
-    """n x 36 normals from the reference's generator (xorshift64, shifts 13/7/17, Box-Muller
-    cosine branch; voxtral_tts_kernels.c:640-669), written out in numpy."""
-    mask = (1 << 64) - 1
-    s = seed if seed else 0x12345678ABCDEF01
-    out = np.empty(n * 36, dtype=np.float32)
-
-    def nxt():
-        nonlocal s
-        s ^= (s << 13) & mask
-        s ^= s >> 7
-        s ^= (s << 17) & mask
-        return np.float32(np.float32(s >> 11) * np.float32(1.0 / 9007199254740992.0))
-
-    for i in range(n * 36):
-        u1 = nxt()
-        while u1 < np.float32(1e-30):
-            u1 = nxt()
-        u2 = nxt()
-        out[i] = np.sqrt(np.float32(-2.0) * np.log(u1)) * np.cos(np.float32(6.2831853071795864) * u2)
-    return out.reshape(n, 36)
+    """n x 36 normals from the reference's generator (the library's bit-exact restatement of
+    tts_randn_fill, voxtral_tts_kernels.c:640-669), state = seed."""
+    vals, _ = load_package().randn(seed, n * 36)
+    return vals.reshape(n, 36)
 
 
 class ClockSampler:
@@ -198,65 +182,171 @@ def measured_hbm_peak():
 # ----------------------------------------------------------------------------------------------
 # reference CPU arm and cpu_baseline
 # ----------------------------------------------------------------------------------------------
-def cpu_reference(pkg, model, kv_prefix, first_embed, noise, n_frames, budget_s):
-    """Times frames on the host with the reference's own CPU code. Returns a dict."""
+def set_host_threads():
+    """All host cores for the CPU arm, whatever the launcher exported (torchrun sets
+    OMP_NUM_THREADS=1). Must run before the BLAS library is loaded."""
+    n = str(os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = n
+    os.environ["OPENBLAS_NUM_THREADS"] = n
+    return int(n)
+
+
+def cpu_reference(pkg, model, rows, first_embed, noise_seed, n_warm, n_frames, budget_s):
+    """Times the same workload on the host with the reference's own CPU code: the 256-row prompt
+    is prefilled by the reference (outside the timed frames; its time is the configuration-3
+    figure), then n_warm untimed and up to n_frames timed frames (decoder step, acoustic frame,
+    re-embedding). Also one decoder step at 64 cached positions and one acoustic frame
+    (configurations 1 and 2). Returns a dict."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
+    cores = set_host_threads()
     import oracle_bind
-    cores = os.cpu_count() or 1
     ref = oracle_bind.load_ref("blas")
     kind, what = "reference", "reference C sources, -DUSE_BLAS with scipy's OpenBLAS"
     if ref is None:
         ref = oracle_bind.load_ref("noblas")
         what = "reference C sources, portable build without BLAS"
-    kvk, kvv = kv_prefix
-    pos0 = kvk.shape[1]
+    pos0 = rows.shape[0]
+    per_config = {}
     t_frames, done = 0.0, 0
     if ref is not None:
-        ref.open(model, kv_max=pos0 + n_frames + 8)
-        k, v = ref.kv()
-        k[:, :pos0] = kvk
-        v[:, :pos0] = kvv
-        ref.set_kv_len(pos0)
-        ref.set_rng_state(1)
+        ref.open(model, kv_max=pos0 + n_warm + n_frames + 8)
+        ref.seed(noise_seed)
+        ref.set_kv_len(64)                       # 64 cached positions (their values do not change the work)
+        ref.llm_forward(first_embed)             # pages the decoder weights in
+        ref.set_kv_len(64)
+        t0 = time.perf_counter()
+        h = ref.llm_forward(first_embed)
+        per_config["decoder_step_ms_at_64_cached_positions"] = (time.perf_counter() - t0) * 1000.0
+        ref.acoustic_forward(h)
+        t0 = time.perf_counter()
+        ref.acoustic_forward(h)
+        per_config["acoustic_frame_ms"] = (time.perf_counter() - t0) * 1000.0
+        ref.set_kv_len(0)
+        t0 = time.perf_counter()
+        ref.llm_prefill(rows)
+        per_config["prefill_s_256_rows"] = time.perf_counter() - t0
+        ref.seed(noise_seed)
         e = first_embed
-        h = ref.llm_forward(e)                 # warm-up step (pages the weights in), then rewind
-        ref.set_kv_len(pos0)
         t_start = time.perf_counter()
-        while done < n_frames:
+        for f in range(n_warm + n_frames):
             t0 = time.perf_counter()
             h = ref.llm_forward(e)
             codes = ref.acoustic_forward(h)
             e = ref.audio_embed(codes)
-            t_frames += time.perf_counter() - t0
-            done += 1
-            if time.perf_counter() - t_start + t_frames / done > budget_s:
+            dt = time.perf_counter() - t0
+            if f >= n_warm:
+                t_frames += dt
+                done += 1
+            elif time.perf_counter() - t_start > 0.4 * budget_s:
+                n_warm = f + 1                   # the warm-up may not eat the budget
+            if done and time.perf_counter() - t_start + t_frames / done > budget_s:
                 break
         ref.close()
     else:
         kind, what = "port", "CPU restatement (oracle/vox_oracle.c, OpenMP over output rows)"
         orc = oracle_bind.Oracle()
         dec, ac = orc.decoder(model), orc.acoustic(model)
-        k = np.zeros((26, pos0 + n_frames + 8, 1024), dtype=np.float32)
+        k = np.zeros((26, pos0 + n_warm + n_frames + 8, 1024), dtype=np.float32)
         v = np.zeros_like(k)
-        k[:, :pos0] = kvk
-        v[:, :pos0] = kvv
-        st, e = 1, first_embed
+        t0 = time.perf_counter()
+        orc.llm_prefill(dec, k, v, 0, rows)
+        per_config["prefill_s_256_rows"] = time.perf_counter() - t0
+        st, e = orc.seed(noise_seed), first_embed
         t_start = time.perf_counter()
-        while done < n_frames:
+        for f in range(n_warm + n_frames):
             t0 = time.perf_counter()
-            h = orc.llm_forward(dec, k, v, pos0 + done, e)
+            h = orc.llm_forward(dec, k, v, pos0 + f, e)
             codes, _, _, st = orc.acoustic_forward(ac, st, h)
             e = orc.audio_embed(model.audio_table(), codes)
-            t_frames += time.perf_counter() - t0
-            done += 1
-            if time.perf_counter() - t_start + t_frames / done > budget_s:
+            dt = time.perf_counter() - t0
+            if f >= n_warm:
+                t_frames += dt
+                done += 1
+            if done and time.perf_counter() - t_start + t_frames / done > budget_s:
                 break
     fps = done / t_frames
-    return {"value": fps, "unit": "frames/s", "cores": cores, "kind": kind,
-            "sample": f"{done} frame(s) of the same workload (decoder step at {pos0}+ keys, acoustic frame, "
-                      f"re-embedding) after one warm-up decoder step; {what}; the M=1 decoder matvecs are "
-                      f"single-threaded by construction, the M=3 acoustic GEMMs use up to {cores} threads",
+    return {"value": fps, "unit": "frames/s", "cores": cores, "kind": kind, "per_config": per_config,
+            "sample": f"{done} timed frame(s) of the same workload (decoder step at {pos0}+ cached positions of the "
+                      f"prefilled prompt, acoustic frame, re-embedding) after {n_warm} warm-up frame(s); {what}; the "
+                      f"M=1 decoder matvecs are single-threaded by construction, the M=3 acoustic GEMMs and the "
+                      f"prefill use up to {cores} threads",
             "ms_per_frame": 1000.0 / fps}
+
+
+def gpu_reference_worker(n_frames):
+    """Runs in a process of its own (the reference's CUDA object exports the same symbol names as
+    this repository's library): the reference's own CUDA backend, built unchanged for sm_100 into
+    oracle/_ref/libvoxref_cuda.so, on the same synthetic weights: per frame tts_cuda_llm_forward
+    and the 14 tts_cuda_predict_velocity calls of the Euler loop (voxtral_tts_acoustic.c:336-355),
+    wall clock (every call ends with a blocking copy to the host). Prints one JSON line."""
+    pkg = load_package()
+    path = os.path.join(ROOT, "oracle", "_ref", "libvoxref_cuda.so")
+    if not os.path.exists(path):
+        print(json.dumps({"unavailable": "oracle/_ref/libvoxref_cuda.so not built (needs the reference checkout and cuBLAS at build time)"}))
+        return
+    try:
+        R = C.CDLL(path)
+    except OSError as e:
+        print(json.dumps({"unavailable": f"cannot load the reference CUDA object: {e}"}))
+        return
+    model = pkg.SynthModel(seed=1234)
+    tok = pkg.synth_bf16((pkg.VOCAB, pkg.DIM), 1234, "mm_audio_embeddings.tok_embeddings.weight")
+    dec, ac = model.decoder_struct(), model.acoustic_struct()
+    dec.tok_embeddings = tok.ctypes.data_as(pkg.u16p)
+    R.tts_cuda_init.restype = C.c_int
+    R.tts_cuda_upload_llm_weights.restype = C.c_int
+    R.tts_cuda_upload_acoustic_weights.restype = C.c_int
+    kv_max = PROMPT_ROWS + n_frames + 16
+    if R.tts_cuda_init(kv_max) != 0 or R.tts_cuda_upload_llm_weights(C.byref(dec)) != 0 or \
+            R.tts_cuda_upload_acoustic_weights(C.byref(ac)) != 0:
+        print(json.dumps({"unavailable": "the reference's tts_cuda_init / weight upload failed on this GPU"}))
+        return
+    vp = C.c_void_p
+    R.tts_cuda_llm_forward.argtypes = [vp, vp, C.c_int]
+    R.tts_cuda_predict_velocity.argtypes = [vp, vp, vp, C.c_float]
+    embed = (tok[24].astype(np.uint32) << 16).view(np.float32).copy()
+    hidden = np.zeros(pkg.DIM, dtype=np.float32)
+    zeros = np.zeros(pkg.DIM, dtype=np.float32)
+    vc, vu = np.zeros(36, dtype=np.float32), np.zeros(36, dtype=np.float32)
+    noise = noise_rows(5, n_frames + 1)
+    ms = []
+    for f in range(n_frames + 1):                # the first frame is the warm-up
+        t0 = time.perf_counter()
+        R.tts_cuda_llm_forward(hidden.ctypes.data, embed.ctypes.data, PROMPT_ROWS + f)
+        x = noise[f].copy()
+        for i in range(pkg.FLOW_STEPS - 1):
+            t = np.float32(i) / np.float32(pkg.FLOW_STEPS - 1)
+            R.tts_cuda_predict_velocity(vc.ctypes.data, x.ctypes.data, hidden.ctypes.data, C.c_float(float(t)))
+            R.tts_cuda_predict_velocity(vu.ctypes.data, x.ctypes.data, zeros.ctypes.data, C.c_float(float(t)))
+            x = x + (np.float32(1.2) * vc - np.float32(0.2) * vu) * np.float32(1.0 / (pkg.FLOW_STEPS - 1))
+        if f:
+            ms.append((time.perf_counter() - t0) * 1000.0)
+    ok = bool(np.isfinite(hidden).all() and np.isfinite(x).all())
+    R.tts_cuda_free()
+    print(json.dumps({"ms_per_frame": float(np.mean(ms)), "frames_per_s": 1000.0 / float(np.mean(ms)), "frames": len(ms),
+                      "finite_outputs": ok,
+                      "what": "the reference's own CUDA backend (voxtral_tts_cuda.cu, cuBLAS SGEMM after a BF16->fp32 "
+                              "expansion of every weight per call), built unchanged with -arch=sm_100: "
+                              "tts_cuda_llm_forward at cache rows 256.. + 14 x tts_cuda_predict_velocity per frame, "
+                              "wall clock; the semantic head, FSQ and re-embedding, which the reference leaves on the "
+                              "CPU, are not included; cache rows below 256 are zero"}))
+
+
+def gpu_reference(n_frames=4, timeout=600):
+    """The GPU reference arm, from a child process. Returns a dict (with `unavailable` and the reason
+    when it cannot run)."""
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "gpu_reference_worker", "--steps",
+                            str(n_frames)], capture_output=True, text=True, timeout=timeout,
+                           env={k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")})
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"the reference CUDA backend did not finish {n_frames} frames in {timeout} s"}
+    for line in reversed(r.stdout.strip().splitlines()):
+        try:
+            return json.loads(line)
+        except ValueError:
+            continue
+    return {"unavailable": f"the reference CUDA backend exited with {r.returncode}: {r.stderr.strip()[-300:]}"}
 
 
 def micro_gemm(args):
@@ -357,7 +447,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=212)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "gpu_reference_worker"])
+    ap.add_argument("--no-gpu-reference", action="store_true", help="skip the reference's own CUDA backend (child process)")
+    ap.add_argument("--no-tp-leg", action="store_true",
+                    help="with N > 1 ranks: skip the extra one-utterance tensor-parallel measurement")
     ap.add_argument("--e2e-steps", type=int, default=0, help="frames of the host-ABI measurement (default: min(steps, 64))")
     ap.add_argument("--cpu-budget", type=float, default=25.0, help="seconds of CPU-baseline frames")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -383,6 +476,8 @@ def main():
     args = ap.parse_args()
     if args.micro:
         return micro(args)
+    if args.impl == "gpu_reference_worker":
+        return gpu_reference_worker(max(args.steps, 1))
     quiet_stdout()
     K, W = max(args.steps, 1), max(args.warmup, 0)
 
@@ -401,17 +496,17 @@ def main():
         if rank != 0:
             return
         model = pkg.SynthModel(seed=1234)
-        kvk = pkg.synth_f32((26, PROMPT_ROWS, 1024), 7, "bench.ref.kv_k")
-        kvv = pkg.synth_f32((26, PROMPT_ROWS, 1024), 7, "bench.ref.kv_v")
+        seeds = utterance_seeds(0)
+        rows = prompt_rows(pkg, model, seeds["prompt"])
         first = model.token_rows([24])[0]
-        budget = min(150.0, max(20.0, 6.0 * (K + W)))
-        r = cpu_reference(pkg, model, (kvk, kvv), first, None, K, budget)
-        config["cache_prefix"] = "synthetic N(0,1) rows (no GPU prefill in this arm)"
+        budget = min(170.0, max(30.0, 6.0 * (K + W)))
+        r = cpu_reference(pkg, model, rows, first, seeds["noise"], W, K, budget)
+        cb = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "per_config")}
         line = {"impl": "reference", "metric": "frames_per_s", "value": r["value"], "unit": "frames/s",
                 "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": r["ms_per_frame"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": config,
-                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32 (BF16 weights, fp32 activations and accumulation)",
+                "data": "synthetic", "config": config, "cpu_baseline": cb,
                 "e2e": {"value": r["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         emit(line)
         return
@@ -636,6 +731,62 @@ def main():
         finally:
             Lb.vb200_set_option(b"decoder_kernel", 0)
 
+    # ---- N > 1: ONE utterance with the decoder tensor-parallel over the N GPUs (strong scaling) ----
+    tp_leg = None
+    if world > 1 and not tp and not args.no_tp_leg:
+        def all_ok(flag):
+            t = torch.tensor([1 if flag else 0], dtype=torch.int32, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            return bool(t.item())
+
+        Kt, Wt = min(K, 64), min(W, 5)
+        stage, ok = "arena", True
+        try:
+            handle = (C.c_ubyte * 64)()
+            ok = all_ok(Lb.vb200_tp_arena(rank, world, handle) == 0)
+            if ok:
+                stage = "connect"
+                handles = [None] * world
+                dist.all_gather_object(handles, bytes(handle))
+                ok = all_ok(Lb.vb200_tp_connect(b"".join(handles)) == 0)
+            tms, tcodes, run_ok = 0.0, None, False
+            if ok:
+                stage = "run"
+                try:
+                    s0 = utterance_seeds(0)                  # every rank decodes the same utterance
+                    rows0 = rows if rank == 0 else prompt_rows(pkg, model, s0["prompt"])
+                    noise0 = noise if rank == 0 else noise_rows(s0["noise"], W + K)
+                    eng.prefill(rows0, 0)
+                    run_ok = Lb.vb200_utterance_begin(first.ctypes.data, PROMPT_ROWS, noise0.ctypes.data, Wt + Kt) == 0
+                    run_ok = run_ok and Lb.vb200_utterance_run(Wt) == 0
+                except Exception:
+                    run_ok = False
+                ok = all_ok(run_ok)                          # also the barrier before the timed frames
+                if ok:
+                    torch.cuda.synchronize()
+                    run_ok = Lb.vb200_utterance_run(Kt) == 0
+                    tcodes = np.zeros((Wt + Kt, pkg.CODES), dtype=np.int32)
+                    tdone, tend, tm = C.c_int(0), C.c_int(0), C.c_float(0.0)
+                    run_ok = run_ok and Lb.vb200_utterance_end(tcodes.ctypes.data, C.byref(tdone), C.byref(tend),
+                                                               C.byref(tm)) == 0 and tdone.value == Wt + Kt
+                    tms = tm.value
+                    ok = all_ok(run_ok)
+            if ok:
+                tval, tmax = aggregate(tms, Kt, dist, shared=True)
+                tp_leg = {"parallelism": f"tp{world}", "ms_per_frame": tmax / Kt, "frames_per_s": tval, "steps": Kt,
+                          "codes_equal_to_single_gpu": bool(np.array_equal(tcodes, codes[:Wt + Kt])) if rank == 0 else None,
+                          "what": "one utterance, every decoder-layer GEMM sliced by output tiles over the ranks, "
+                                  "results exchanged by peer stores over NVLink inside the GEMM epilogue"}
+            else:
+                tp_leg = {"error": f"tensor-parallel leg failed at stage '{stage}' on at least one rank"}
+        except Exception as e:                              # never lose the main line to the extra leg
+            tp_leg = {"error": f"{type(e).__name__}: {e}"}
+        try:
+            dist.barrier()                                   # nobody unmaps an arena a peer may still write to
+            Lb.vb200_tp_close()
+        except Exception:
+            pass
+
     if tp:
         barrier()                                            # nobody unmaps an arena a peer may still write to
     if rank != 0:
@@ -646,11 +797,12 @@ def main():
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        kvk = np.stack([eng.kv_read(l, 0, PROMPT_ROWS)[0] for l in range(26)])
-        kvv = np.stack([eng.kv_read(l, 0, PROMPT_ROWS)[1] for l in range(26)])
-        r = cpu_reference(pkg, model, (kvk, kvv), first, None, 8, args.cpu_budget)
-        cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        r = cpu_reference(pkg, model, rows, first, seeds["noise"], 1, 6, args.cpu_budget)
+        cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "per_config")}
     eng.close()
+    gpu_ref = None
+    if world == 1 and not args.no_gpu_reference:
+        gpu_ref = gpu_reference()                   # after eng.close(): the child has the GPU to itself
 
     line = {"metric": "frames_per_s", "value": value, "unit": "frames/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak",
@@ -659,9 +811,10 @@ def main():
             "e2e": {"value": e2e_value, "unit": "frames/s", "steps": Ke,
                     "h2d_bytes_per_step": 16 + 3072 * 4 + 36 * 4, "d2h_bytes_per_step": 176 + 3072 * 4},
             "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu,
+            "gpu_reference": gpu_ref, "tp": tp_leg,
             "batched": batched, "streaming_decoder": streaming,
             "utterance": {"prefill_rows": PROMPT_ROWS, "prefill_ms": min(prefill_ms),
-                          "first_frame_after_ms": min(prefill_ms) + 1000.0 / e2e_value,
+                          "first_frame_after_ms": min(prefill_ms) + 1000.0 * (1 if tp else world) / e2e_value,
                           "frames": 212,
                           "total_ms_at_measured_rates": min(prefill_ms) + 212 * 1000.0 * (1 if tp else world) / e2e_value,
                           "note": "tts_cuda_llm_prefill with host rows (wall clock, synchronous), then "

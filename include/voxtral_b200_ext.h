@@ -162,6 +162,11 @@ void vb200_synth_bf16(uint16_t *dst, size_t n, uint64_t seed, uint64_t stream, u
 void vb200_synth_f32(float *dst, size_t n, uint64_t seed, uint64_t stream, uint64_t first,
                      float mean, float sigma);
 
+/* The reference's noise generator (tts_rng_seed / tts_randn_fill, voxtral_tts_kernels.c:640-669),
+ * bit for bit: n normals, *state advanced in place (a zero state is replaced by the reference's
+ * default seed). One frame that is not END consumes 36 of them (voxtral_tts_acoustic.c:329). */
+void vb200_randn_fill(uint64_t *state, float *out, size_t n);
+
 #ifdef __cplusplus
 }
 #endif

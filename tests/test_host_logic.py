@@ -101,3 +101,22 @@ def test_tensor_parallel_slices_tile_every_matrix(pkg):
     for world in (5, 7, 9, 0):
         assert L.vb200_tp_plan(0, world, 148, out) == -1
     assert L.vb200_tp_plan(2, 2, 148, out) == -1
+
+
+def test_bench_noise_generator_is_the_reference_rng(pkg, oracle):
+    """The benchmark draws its noise from the library's restatement of the reference generator
+    (vb200_randn_fill; voxtral_tts_kernels.c:640-669); it must give the oracle's (pinned) values and
+    state bit for bit."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for seed in (1000, 1007):
+        want, _ = oracle.randn(seed, 36 * 3)
+        got = bench.noise_rows(seed, 3).ravel()
+        assert np.array_equal(got, want), seed
+    vals, st = pkg.randn(0, 7)
+    want, wst = oracle.randn(oracle.seed(0), 7)
+    assert np.array_equal(vals, want) and st == wst

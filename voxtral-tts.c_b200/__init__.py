@@ -153,15 +153,46 @@ def stream_id(name):
     return zlib.crc32(name.encode())
 
 
+_synth = None
+
+
+def synth_lib():
+    """The synthetic-tensor generator alone (lib/libvb_synth.so, plain C++, no CUDA): what the
+    benchmark's CPU reference arm loads, so that it never maps the CUDA library."""
+    global _synth
+    if _synth is not None:
+        return _synth
+    path = os.path.join(HERE, "lib", "libvb_synth.so")
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: run `python voxtral-tts.c_b200/build.py`")
+    S = C.CDLL(path)
+    S.vb200_synth_bf16.restype = None
+    S.vb200_synth_bf16.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float]
+    S.vb200_synth_f32.restype = None
+    S.vb200_synth_f32.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_float]
+    S.vb200_randn_fill.restype = None
+    S.vb200_randn_fill.argtypes = [C.POINTER(C.c_uint64), C.c_void_p, C.c_size_t]
+    _synth = S
+    return S
+
+
+def randn(state, n):
+    """n normals of the reference's generator from `state`; returns (values, new state)."""
+    st = C.c_uint64(state)
+    out = np.empty(n, dtype=np.float32)
+    synth_lib().vb200_randn_fill(C.byref(st), _ptr(out), n)
+    return out, st.value
+
+
 def synth_bf16(shape, seed, name, sigma=0.02, first=0):
     out = np.empty(shape, dtype=np.uint16)
-    lib().vb200_synth_bf16(_ptr(out), out.size, seed, stream_id(name), first, sigma)
+    synth_lib().vb200_synth_bf16(_ptr(out), out.size, seed, stream_id(name), first, sigma)
     return out
 
 
 def synth_f32(shape, seed, name, mean=0.0, sigma=1.0, first=0):
     out = np.empty(shape, dtype=np.float32)
-    lib().vb200_synth_f32(_ptr(out), out.size, seed, stream_id(name), first, mean, sigma)
+    synth_lib().vb200_synth_f32(_ptr(out), out.size, seed, stream_id(name), first, mean, sigma)
     return out
 
 

@@ -61,6 +61,14 @@ def build(force=False, verbose_ptxas=False):
         if force or _stale(o, [s] + headers):
             _run(["g++", "-O3", "-std=c++17", "-fPIC", "-fopenmp", "-ffp-contract=off", "-Wall", "-c", s, "-o", o])
         objs.append(o)
+    # the synthetic-tensor generator also as a small library of its own: code that must not map
+    # the CUDA library (the CPU reference arm of the benchmark) loads only this one
+    synth_lib = os.path.join(LIBDIR, "libvb_synth.so")
+    synth_obj = os.path.join(OBJDIR, "vb_synth.cpp.o")
+    if force or _stale(synth_lib, [synth_obj]):
+        tmp = synth_lib + ".tmp"
+        _run(["g++", "-shared", "-o", tmp, synth_obj, "-fopenmp"])
+        os.replace(tmp, synth_lib)
     if force or _stale(LIB, objs):
         # link under a temporary name and rename: a reader never sees a half-written library
         tmp = LIB + ".tmp"

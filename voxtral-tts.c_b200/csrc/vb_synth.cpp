@@ -11,6 +11,7 @@
  * BF16 values are rounded to nearest even from fp32.
  */
 #include <stddef.h>
+#include <math.h>
 #include <stdint.h>
 #include <string.h>
 
@@ -58,4 +59,26 @@ extern "C" void vb200_synth_f32(float *dst, size_t n, uint64_t seed, uint64_t st
 #pragma omp parallel for schedule(static)
     for (long long i = 0; i < (long long)n; i++)
         dst[i] = mean + unit_normal_times(key, first + (uint64_t)i, scale);
+}
+
+/* The reference's noise generator (tts_rng_seed / tts_randn_fill, voxtral_tts_kernels.c:640-669):
+ * xorshift64 with shifts 13, 7, 17; uniform = (float)(x >> 11) * 2^-53; Box-Muller, cosine branch
+ * only, in single precision with the C library's logf / cosf / sqrtf. For callers of
+ * vb200_frame / vb200_utterance_* that do not link the reference's own RNG: they need the 36
+ * normals per frame that the reference would draw. state is advanced in place. */
+extern "C" void vb200_randn_fill(uint64_t *state, float *out, size_t n) {
+    uint64_t x = *state ? *state : 0x12345678ABCDEF01ULL;
+    auto uniform = [&x]() {
+        x ^= x << 13;
+        x ^= x >> 7;
+        x ^= x << 17;
+        return (float)(x >> 11) * (1.0f / 9007199254740992.0f);
+    };
+    for (size_t i = 0; i < n; i++) {
+        float u1;
+        do { u1 = uniform(); } while (u1 < 1e-30f);
+        const float u2 = uniform();
+        out[i] = sqrtf(-2.0f * logf(u1)) * cosf(6.2831853071795864f * u2);
+    }
+    *state = x;
 }
