@@ -41,6 +41,15 @@ int vb200_acoustic_frame(const float *llm_hidden, const float *noise36, int *cod
 int vb200_frame_chained(const float *noise36, int pos, float *hidden_out, int *codes37);
 int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows);
 
+/* The prompt of voxtral_tts.c:230-272 assembled on the device and prefilled:
+ *   [BOS=1] [BEGIN_AUDIO=25] voice rows [/INST=36] text tokens [INST=35] [BEGIN_AUDIO=25]
+ * Token rows come from the token table that tts_cuda_upload_llm_weights uploaded (the decoder
+ * struct's tok_embeddings must have been set), voice rows from `voice_bf16` ([n_voice, 3072] BF16 in
+ * host memory, the payload of a voice file; tts_voice_embed, voxtral_tts_voice.c:228-248). Only
+ * ids and BF16 rows cross to the device; nothing is expanded to fp32 on the host. The rows land in
+ * the cache from row start_pos. Returns the number of prompt rows (n_voice + n_text + 5) or -1. */
+int vb200_prefill_prompt(const int *text_ids, int n_text, const uint16_t *voice_bf16, int n_voice, int start_pos);
+
 /* The orchestrator's frame loop (voxtral_tts.c:301-321) kept on the device: no host
  * round trip per frame. begin: first decoder input, first cache row, and the noise
  * of all n_frames frames ([n_frames, 36]; the reference RNG draws 36 normals per

@@ -86,6 +86,7 @@ def lib():
         "vb200_frame_chained": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
         "vb200_acoustic_frame": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
         "vb200_upload_audio_embed": (C.c_int, [C.c_void_p, C.c_int]),
+        "vb200_prefill_prompt": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int]),
         "vb200_utterance_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
         "vb200_utterance_run": (C.c_int, [C.c_int]),
         "vb200_batch_open": (C.c_int, [C.c_int, C.c_int, C.c_int]),
@@ -276,11 +277,20 @@ class SynthModel:
         L.attention_norm = g[f"{name}.attention_norm.weight"].ctypes.data_as(f32p)
         L.ffn_norm = g[f"{name}.ffn_norm.weight"].ctypes.data_as(f32p)
 
-    def decoder_struct(self):
+    def token_table(self):
+        """The whole 131072-row token table (0.8 GB), generated once on first use."""
+        name = "mm_audio_embeddings.tok_embeddings.weight"
+        if getattr(self, "_tok", None) is None:
+            self._tok = synth_bf16((VOCAB, DIM), self.seed, name)
+        return self._tok
+
+    def decoder_struct(self, token_table=False):
         w = DecoderWeights()
         for i in range(DEC_LAYERS):
             self._fill_layer(w.layers[i], f"layers.{i}")
         w.norm = self.t["norm.weight"].ctypes.data_as(f32p)
+        if token_table:
+            w.tok_embeddings = self.token_table().ctypes.data_as(u16p)
         return w
 
     def acoustic_struct(self):
@@ -352,9 +362,9 @@ class Engine:
         self.kv_max = kv_cache_max
         self._keep = []
 
-    def upload(self, model, decoder=True, acoustic=True, audio_table=False):
+    def upload(self, model, decoder=True, acoustic=True, audio_table=False, token_table=False):
         if decoder:
-            w = model.decoder_struct()
+            w = model.decoder_struct(token_table=token_table)
             self._keep.append(w)
             if self.L.tts_cuda_upload_llm_weights(C.byref(w)) != 0:
                 raise RuntimeError("tts_cuda_upload_llm_weights failed")
@@ -383,6 +393,16 @@ class Engine:
         embeds = np.ascontiguousarray(embeds, dtype=np.float32)
         self.L.tts_cuda_llm_prefill(_ptr(embeds), embeds.shape[0], int(start_pos))
         self._ok("tts_cuda_llm_prefill")
+
+    def prefill_prompt(self, text_ids, voice_bf16, start_pos=0):
+        """vb200_prefill_prompt: returns the number of prompt rows."""
+        ids = np.ascontiguousarray(text_ids, dtype=np.int32)
+        voice = np.ascontiguousarray(voice_bf16, dtype=np.uint16).reshape(-1, DIM)
+        n = self.L.vb200_prefill_prompt(_ptr(ids) if ids.size else None, ids.size, _ptr(voice) if voice.size else None,
+                                        voice.shape[0], int(start_pos))
+        if n < 0:
+            raise RuntimeError(f"vb200_prefill_prompt failed (device status={self.L.vb200_last_status()})")
+        return n
 
     def predict_velocity(self, x_t, hidden, t):
         x_t = np.ascontiguousarray(x_t, dtype=np.float32)

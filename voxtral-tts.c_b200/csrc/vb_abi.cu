@@ -233,6 +233,10 @@ int vb200_utterance_end(int *codes_out, int *frames_done, int *hit_end, float *d
     return utterance_end(codes_out, frames_done, hit_end, device_ms);
 }
 
+int vb200_prefill_prompt(const int *text_ids, int n_text, const uint16_t *voice_bf16, int n_voice, int start_pos) {
+    return prefill_prompt(text_ids, n_text, voice_bf16, n_voice, start_pos);
+}
+
 int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows) {
     return model_upload_audio_embed(table_bf16, rows);
 }

@@ -119,6 +119,7 @@ int predict_velocity(float *out_v, const float *x_t, const float *hidden, float 
 int linear(float *y, const float *x, const uint16_t *W_host, int M, int K, int N, const void *W_gpu);
 int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int K, int N);
 int prefill(const float *embeds, int seq_len, int start_pos);
+int prefill_prompt(const int *text_ids, int n_text, const uint16_t *voice_bf16, int n_voice, int start_pos);
 int prefill_tc_setup();
 /* tensor-core acoustic path (vb_acoustic_tc.cu) */
 int acoustic_tc_setup();

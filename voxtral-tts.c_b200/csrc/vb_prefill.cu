@@ -3,10 +3,11 @@
  * (tts_llm_prefill, voxtral_tts_llm.c:277-373): all prompt rows go through the
  * 26 layers, K and V of every row land in the cache, hidden states are dropped.
  *
- * The linears run as batches of row blocks through the streaming engine (fp32
- * activations, exact BF16 weights, fp32 accumulation - the arithmetic of the
- * reference); RoPE, the cache write and the causal attention use the
- * stand-alone kernels.
+ * The linears run on the tensor-core GEMM (vb_tc.cu; fp32 rows as three BF16 terms) in
+ * blocks of up to 256 rows; RoPE, the cache write and the causal attention use the
+ * stand-alone kernels. When the tensor maps cannot be made the same layer loop runs
+ * on the streaming engine, eight rows at a time. Also here: the prompt assembled on
+ * the device from token ids and BF16 voice rows (voxtral_tts.c:230-272).
  */
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
@@ -15,6 +16,7 @@
 #include <math.h>
 #include <stdio.h>
 #include <string.h>
+#include <vector>
 
 namespace vb {
 
@@ -253,4 +255,67 @@ int prefill(const float *embeds, int seq_len, int start_pos) {
     return rc;
 }
 
+/* ---- the prompt, assembled on the device ---- */
+/* Row r of the prompt: a token-table row (ids[r] >= 0) or voice row -ids[r] - 1, BF16 -> fp32
+ * (tts_embed_token_bf16, voxtral_tts_kernels.c:55-59; tts_voice_embed, voxtral_tts_voice.c:228-248). */
+__global__ void prompt_rows_kernel(float *out, const uint16_t *table, const uint16_t *voice, const int *ids, int dim) {
+    const int id = ids[blockIdx.y];
+    const uint16_t *src = id >= 0 ? table + (size_t)id * dim : voice + (size_t)(-id - 1) * dim;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < dim) out[(size_t)blockIdx.y * dim + i] = __uint_as_float((uint32_t)src[i] << 16);
+}
+
+/* The prompt the orchestrator assembles on the host (voxtral_tts.c:230-272):
+ *   [BOS=1] [BEGIN_AUDIO=25] voice rows [/INST=36] text tokens [INST=35] [BEGIN_AUDIO=25]
+ * built on the device from the token table uploaded with the decoder weights and the BF16 voice
+ * rows (host memory, [n_voice, 3072]), then prefilled from cache row start_pos. Only the token ids
+ * and the BF16 voice rows cross PCIe (1.4 MB for 224 voice rows instead of 3 MB of fp32 rows, and
+ * no BF16 -> fp32 pass on the host). Returns the number of prompt rows, or -1. */
+int prefill_prompt(const int *text_ids, int n_text, const uint16_t *voice_bf16, int n_voice, int start_pos) {
+    Model &m = model();
+    if (!m.inited || !m.llm_ready || !m.tok_emb) {
+        fprintf(stderr, "voxtral_b200: the prompt needs the decoder weights with the token table uploaded\n");
+        return -1;
+    }
+    if (n_text < 0 || n_voice < 0 || (n_text > 0 && !text_ids) || (n_voice > 0 && !voice_bf16)) return -1;
+    const int n = n_voice + n_text + 5;
+    if (start_pos < 0 || start_pos + n > m.kv_max) {
+        fprintf(stderr, "voxtral_b200: a prompt of %d rows at %d exceeds the %d-row cache\n", n, start_pos, m.kv_max);
+        return -1;
+    }
+    std::vector<int> ids;
+    ids.reserve(n);
+    ids.push_back(1);
+    ids.push_back(25);
+    for (int i = 0; i < n_voice; i++) ids.push_back(-(i + 1));
+    ids.push_back(36);
+    for (int i = 0; i < n_text; i++) {
+        if (text_ids[i] < 0 || text_ids[i] >= VB200_VOCAB) return -1;
+        ids.push_back(text_ids[i]);
+    }
+    ids.push_back(35);
+    ids.push_back(25);
+    int *d_ids = nullptr;
+    uint16_t *d_voice = nullptr;
+    float *d_rows = nullptr;
+    int rc = -1;
+    do {
+        if (cudaMalloc(&d_ids, sizeof(int) * n) != cudaSuccess || cudaMalloc(&d_rows, sizeof(float) * (size_t)n * D) != cudaSuccess)
+            break;
+        if (n_voice > 0 && cudaMalloc(&d_voice, (size_t)n_voice * D * 2) != cudaSuccess) break;
+        if (cudaMemcpyAsync(d_ids, ids.data(), sizeof(int) * n, cudaMemcpyHostToDevice, m.st) != cudaSuccess) break;
+        if (n_voice > 0 &&
+            cudaMemcpyAsync(d_voice, voice_bf16, (size_t)n_voice * D * 2, cudaMemcpyHostToDevice, m.st) != cudaSuccess)
+            break;
+        prompt_rows_kernel<<<dim3((D + 255) / 256, n), 256, 0, m.st>>>(d_rows, m.tok_emb, d_voice, d_ids, D);
+        if (cudaGetLastError() != cudaSuccess) break;
+        rc = prefill(d_rows, n, start_pos) == 0 ? n : -1;    /* synchronises the stream */
+    } while (0);
+    cudaStreamSynchronize(m.st);
+    cudaFree(d_ids); cudaFree(d_voice); cudaFree(d_rows);
+    cudaGetLastError();
+    return rc;
+}
+
 } // namespace vb
+
