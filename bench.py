@@ -538,6 +538,11 @@ def main():
     kv_max = PROMPT_ROWS + W + K + 72
     eng = pkg.Engine(kv_cache_max=kv_max)
     eng.upload(model, decoder=True, acoustic=True, audio_table=True)
+    up_s, up_b = eng.upload_stats()
+    upload = {"seconds": up_s, "bytes": up_b, "gbs": up_b / up_s / 1e9 if up_s > 0 else None,
+              "what": "tts_cuda_upload_llm_weights + tts_cuda_upload_acoustic_weights + vb200_upload_audio_embed from "
+                      "pageable host memory: pinned staging ring filled by host threads, copies and repacking "
+                      "kernels on one stream, one wait per call"}
     eng.L.vb200_set_option(b"ignore_end", 1)
 
     tp = bool(args.tp and world > 1)
@@ -813,6 +818,7 @@ def main():
             "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu,
             "gpu_reference": gpu_ref, "tp": tp_leg,
             "batched": batched, "streaming_decoder": streaming,
+            "upload": upload,
             "utterance": {"prefill_rows": PROMPT_ROWS, "prefill_ms": min(prefill_ms),
                           "first_frame_after_ms": min(prefill_ms) + 1000.0 * (1 if tp else world) / e2e_value,
                           "frames": 212,

@@ -41,6 +41,13 @@ int vb200_acoustic_frame(const float *llm_hidden, const float *noise36, int *cod
 int vb200_frame_chained(const float *noise36, int pos, float *hidden_out, int *codes37);
 int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows);
 
+/* What the weight uploads since tts_cuda_init have cost: wall-clock seconds inside the upload
+ * calls (host -> device copies through a ring of pinned staging buffers filled by
+ * VB200_UPLOAD_THREADS host threads, repacking kernels behind them on the same stream, one
+ * wait at the end of each call) and the bytes copied. The reference's counterpart is one
+ * blocking cudaMemcpy per matrix (voxtral_tts_cuda.cu:223-310). Either pointer may be null. */
+void vb200_upload_stats(double *seconds, double *bytes);
+
 /* The prompt of voxtral_tts.c:230-272 assembled on the device and prefilled:
  *   [BOS=1] [BEGIN_AUDIO=25] voice rows [/INST=36] text tokens [INST=35] [BEGIN_AUDIO=25]
  * Token rows come from the token table that tts_cuda_upload_llm_weights uploaded (the decoder

@@ -87,6 +87,7 @@ def lib():
         "vb200_acoustic_frame": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
         "vb200_upload_audio_embed": (C.c_int, [C.c_void_p, C.c_int]),
         "vb200_prefill_prompt": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int]),
+        "vb200_upload_stats": (None, [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
         "vb200_utterance_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
         "vb200_utterance_run": (C.c_int, [C.c_int]),
         "vb200_batch_open": (C.c_int, [C.c_int, C.c_int, C.c_int]),
@@ -393,6 +394,12 @@ class Engine:
         embeds = np.ascontiguousarray(embeds, dtype=np.float32)
         self.L.tts_cuda_llm_prefill(_ptr(embeds), embeds.shape[0], int(start_pos))
         self._ok("tts_cuda_llm_prefill")
+
+    def upload_stats(self):
+        """(seconds spent inside the weight-upload calls, bytes copied host -> device) so far."""
+        s, b = C.c_double(0.0), C.c_double(0.0)
+        self.L.vb200_upload_stats(C.byref(s), C.byref(b))
+        return s.value, b.value
 
     def prefill_prompt(self, text_ids, voice_bf16, start_pos=0):
         """vb200_prefill_prompt: returns the number of prompt rows."""

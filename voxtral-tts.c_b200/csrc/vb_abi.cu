@@ -241,6 +241,11 @@ int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows) {
     return model_upload_audio_embed(table_bf16, rows);
 }
 
+void vb200_upload_stats(double *seconds, double *bytes) {
+    if (seconds) *seconds = model().upload_seconds;
+    if (bytes) *bytes = model().upload_bytes;
+}
+
 static int kv_rows(int layer, int pos0, int n, float *k_rows, float *v_rows, bool to_device) {
     Model &m = model();
     if (!m.inited || layer < 0 || layer >= VB200_DEC_LAYERS || pos0 < 0 || n < 0 || pos0 + n > m.kv_max) return -1;

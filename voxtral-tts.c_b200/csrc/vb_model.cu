@@ -15,6 +15,10 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <chrono>
+#include <thread>
+#include <vector>
+
 namespace vb {
 
 #define VB_CHECK(call)                                                                         \
@@ -184,24 +188,109 @@ static void drop(T **p) {
     if (*p) { dev_release(*p); *p = nullptr; }
 }
 
+/* Host -> device copies of the weights go through a small ring of pinned staging buffers:
+ * a few host threads fill buffer n + 1 from the caller's (pageable, usually memory-mapped:
+ * voxtral_tts_safetensors.c:400-405) memory while the copy engine drains buffer n, and the
+ * repacking kernels run behind the copies on the same stream. Nothing waits for the device
+ * except a buffer that is still being drained; the upload call synchronises once at its end.
+ * The reference copies every matrix with a blocking cudaMemcpy (voxtral_tts_cuda.cu:223-310). */
+struct Stager {
+    static const int kBufs = 3;
+    size_t cap = (size_t)64 << 20;
+    void *pin[kBufs] = {};
+    cudaEvent_t drained[kBufs] = {};
+    bool busy[kBufs] = {};
+    int next = 0, threads = 4;
+    bool ok = false;
+};
+static Stager g_stage;
+
+static void stage_open() {
+    Stager &s = g_stage;
+    if (s.ok) return;
+    const char *env = getenv("VB200_UPLOAD_THREADS");
+    unsigned hc = std::thread::hardware_concurrency();
+    s.threads = env ? atoi(env) : (hc >= 16 ? 8 : hc >= 4 ? 4 : 1);
+    if (s.threads < 1) s.threads = 1;
+    if (s.threads > 32) s.threads = 32;
+    for (int i = 0; i < Stager::kBufs; i++) {
+        if (cudaHostAlloc(&s.pin[i], s.cap, cudaHostAllocDefault) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.drained[i], cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            return;   /* no pinned memory: stage_copy() falls back to plain copies */
+        }
+        s.busy[i] = false;
+    }
+    s.ok = true;
+}
+
+static void stage_close() {
+    Stager &s = g_stage;
+    for (int i = 0; i < Stager::kBufs; i++) {
+        if (s.pin[i]) cudaFreeHost(s.pin[i]);
+        if (s.drained[i]) cudaEventDestroy(s.drained[i]);
+        s.pin[i] = nullptr; s.drained[i] = nullptr; s.busy[i] = false;
+    }
+    s.ok = false;
+}
+
+static void fill_parallel(char *dst, const char *src, size_t n, int threads) {
+    const size_t min_part = (size_t)4 << 20;
+    int parts = (int)((n + min_part - 1) / min_part);
+    if (parts > threads) parts = threads;
+    if (parts <= 1) { memcpy(dst, src, n); return; }
+    const size_t per = ((n / parts) + 4095) & ~(size_t)4095;
+    std::vector<std::thread> pool;
+    for (int i = 1; i < parts; i++) {
+        const size_t off = per * i;
+        if (off >= n) break;
+        const size_t len = off + per < n ? per : n - off;
+        pool.emplace_back([=] { memcpy(dst + off, src + off, len); });
+    }
+    memcpy(dst, src, per < n ? per : n);
+    for (auto &t : pool) t.join();
+}
+
+/* Asynchronous on m.st as far as the device goes; the source may be reused on return. */
+static int stage_copy(void *dst, const void *src, size_t bytes) {
+    Model &m = g_model;
+    Stager &s = g_stage;
+    m.upload_bytes += (double)bytes;
+    if (!s.ok) {
+        VB_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, m.st));
+        VB_CHECK(cudaStreamSynchronize(m.st));
+        return 0;
+    }
+    for (size_t off = 0; off < bytes; off += s.cap) {
+        const size_t n = bytes - off < s.cap ? bytes - off : s.cap;
+        const int b = s.next;
+        s.next = (s.next + 1) % Stager::kBufs;
+        if (s.busy[b]) VB_CHECK(cudaEventSynchronize(s.drained[b]));
+        fill_parallel((char *)s.pin[b], (const char *)src + off, n, s.threads);
+        VB_CHECK(cudaMemcpyAsync((char *)dst + off, s.pin[b], n, cudaMemcpyHostToDevice, m.st));
+        VB_CHECK(cudaEventRecord(s.drained[b], m.st));
+        s.busy[b] = true;
+    }
+    return 0;
+}
+
 static int upload_bf16(uint16_t **dst, const uint16_t *src, size_t n) {
     if (!src) return -1;
     drop(dst);
     if (dev_alloc(dst, n)) return -1;
-    VB_CHECK(cudaMemcpy(*dst, src, n * 2, cudaMemcpyHostToDevice));
-    return 0;
+    return stage_copy(*dst, src, n * 2);
 }
 
 static int upload_f32(float **dst, const float *src, size_t n) {
     if (!src) return -1;
     drop(dst);
     if (dev_alloc(dst, n)) return -1;
-    VB_CHECK(cudaMemcpy(*dst, src, n * 4, cudaMemcpyHostToDevice));
-    return 0;
+    return stage_copy(*dst, src, n * 4);
 }
 
 /* Column-split projections of one layer become single matrices: [wq; wk; wv] and
- * gate/up interleaved row by row. tmp_a / tmp_b hold the staged gate and up. */
+ * gate/up interleaved row by row. tmp_a / tmp_b hold the staged gate and up; everything is
+ * ordered by the stream, so they are reused from layer to layer without a host wait. */
 static int upload_layer(LayerDev &L, const vb200_layer_weights_t &w, uint16_t *tmp_a, uint16_t *tmp_b) {
     Model &m = g_model;
     if (!w.wq || !w.wk || !w.wv || !w.wo || !w.w1 || !w.w2 || !w.w3 || !w.attention_norm || !w.ffn_norm)
@@ -209,20 +298,32 @@ static int upload_layer(LayerDev &L, const vb200_layer_weights_t &w, uint16_t *t
     drop(&L.wqkv);
     drop(&L.w13);
     if (dev_alloc(&L.wqkv, (size_t)QKV * D)) return -1;
-    VB_CHECK(cudaMemcpy(L.wqkv, w.wq, (size_t)QD * D * 2, cudaMemcpyHostToDevice));
-    VB_CHECK(cudaMemcpy(L.wqkv + (size_t)QD * D, w.wk, (size_t)KVD * D * 2, cudaMemcpyHostToDevice));
-    VB_CHECK(cudaMemcpy(L.wqkv + (size_t)(QD + KVD) * D, w.wv, (size_t)KVD * D * 2, cudaMemcpyHostToDevice));
+    if (stage_copy(L.wqkv, w.wq, (size_t)QD * D * 2)) return -1;
+    if (stage_copy(L.wqkv + (size_t)QD * D, w.wk, (size_t)KVD * D * 2)) return -1;
+    if (stage_copy(L.wqkv + (size_t)(QD + KVD) * D, w.wv, (size_t)KVD * D * 2)) return -1;
     if (upload_bf16(&L.wo, w.wo, (size_t)D * QD)) return -1;
     if (upload_bf16(&L.w2, w.w2, (size_t)D * HID)) return -1;
     if (dev_alloc(&L.w13, (size_t)2 * HID * D)) return -1;
-    VB_CHECK(cudaMemcpy(tmp_a, w.w1, (size_t)HID * D * 2, cudaMemcpyHostToDevice));
-    VB_CHECK(cudaMemcpy(tmp_b, w.w3, (size_t)HID * D * 2, cudaMemcpyHostToDevice));
+    if (stage_copy(tmp_a, w.w1, (size_t)HID * D * 2)) return -1;
+    if (stage_copy(tmp_b, w.w3, (size_t)HID * D * 2)) return -1;
     interleave_rows(L.w13, tmp_a, tmp_b, HID, D, m.st);
-    VB_CHECK(cudaStreamSynchronize(m.st));
     if (upload_f32(&L.attn_norm, w.attention_norm, D)) return -1;
     if (upload_f32(&L.ffn_norm, w.ffn_norm, D)) return -1;
     return 0;
 }
+
+/* Brackets one upload call: opens the staging ring, and on the way out waits for the stream
+ * once, releases the ring and adds the call's wall-clock time to the model's upload record. */
+struct UploadScope {
+    std::chrono::steady_clock::time_point t0;
+    UploadScope() : t0(std::chrono::steady_clock::now()) { stage_open(); }
+    int finish(int rc) {
+        if (cudaStreamSynchronize(g_model.st) != cudaSuccess) rc = -1;
+        stage_close();
+        g_model.upload_seconds += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        return rc;
+    }
+};
 
 static void upload_failed() {
     g_model.llm_ready = g_model.ac_ready = false;
@@ -234,12 +335,14 @@ int model_upload_llm(const vb200_decoder_weights_t *w) {
     if (!m.inited || !w) return -1;
     uint16_t *ta = nullptr, *tb = nullptr;
     if (dev_alloc(&ta, (size_t)HID * D) || dev_alloc(&tb, (size_t)HID * D)) { upload_failed(); return -1; }
+    UploadScope scope;
     int rc = 0;
     for (int i = 0; i < VB200_DEC_LAYERS && !rc; i++) rc = upload_layer(m.dec[i], w->layers[i], ta, tb);
-    dev_release(ta);
-    dev_release(tb);
     if (!rc) rc = upload_f32(&m.dec_norm, w->norm, D);
     if (!rc && w->tok_embeddings) rc = upload_bf16(&m.tok_emb, w->tok_embeddings, (size_t)VB200_VOCAB * D);
+    rc = scope.finish(rc);
+    dev_release(ta);
+    dev_release(tb);
     if (rc) {
         fprintf(stderr, "voxtral_b200: decoder weight upload failed\n");
         upload_failed();
@@ -258,10 +361,9 @@ int model_upload_acoustic(const vb200_acoustic_weights_t *w) {
     if (!m.inited || !w) return -1;
     uint16_t *ta = nullptr, *tb = nullptr;
     if (dev_alloc(&ta, (size_t)HID * D) || dev_alloc(&tb, (size_t)HID * D)) { upload_failed(); return -1; }
+    UploadScope scope;
     int rc = 0;
     for (int i = 0; i < VB200_AC_LAYERS && !rc; i++) rc = upload_layer(m.ac[i], w->layers[i], ta, tb);
-    dev_release(ta);
-    dev_release(tb);
     if (!rc) rc = upload_bf16(&m.ac_input_proj, w->input_proj, (size_t)D * A);
     if (!rc) rc = upload_bf16(&m.ac_time_proj, w->time_proj, (size_t)D * D);
     if (!rc) rc = upload_bf16(&m.ac_llm_proj, w->llm_proj, (size_t)D * D);
@@ -271,6 +373,9 @@ int model_upload_acoustic(const vb200_acoustic_weights_t *w) {
     if (!w->semantic_out_bias) drop(&m.ac_sem_bias);
     if (!rc && w->semantic_out_bias) rc = upload_f32(&m.ac_sem_bias, w->semantic_out_bias, VB200_SEM_PADDED);
     if (!rc && !w->time_inv_freq) rc = -1;
+    rc = scope.finish(rc);
+    dev_release(ta);
+    dev_release(tb);
     if (rc) {
         fprintf(stderr, "voxtral_b200: acoustic weight upload failed\n");
         upload_failed();
@@ -316,7 +421,8 @@ int model_upload_audio_embed(const uint16_t *table, int rows) {
     Model &m = g_model;
     if (!m.inited || !table || rows < VB200_AUDIO_ROWS) return -1;
     if (m.audio_table) { dev_release(m.audio_table); m.audio_table = nullptr; }
-    if (upload_bf16(&m.audio_table, table, (size_t)rows * D)) return -1;
+    UploadScope scope;
+    if (scope.finish(upload_bf16(&m.audio_table, table, (size_t)rows * D))) return -1;
     m.embed_ready = true;
     return model_rebuild_programs();
 }

@@ -52,6 +52,7 @@ struct Model {
     int device = 0, n_cta = 0, sm_count = 0;
     cudaStream_t st = nullptr;
     std::vector<void *> allocs;
+    double upload_seconds = 0.0, upload_bytes = 0.0;   /* host -> device weight copies so far */
 
     LayerDev dec[VB200_DEC_LAYERS], ac[VB200_AC_LAYERS];
     uint16_t *tok_emb = nullptr;

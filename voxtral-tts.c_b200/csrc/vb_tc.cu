@@ -121,6 +121,8 @@ int tc_acts(TcActs *a, uint16_t *d_buf, int rows_pad, int K) {
     a->buf = d_buf; a->rows_pad = rows_pad; a->K = K;
     if ((rows_pad != 16 && rows_pad != 64 && rows_pad != 256) || (K % kTcBlockK) != 0) return -1;
     if (make_map(&a->map, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, (uint32_t)rows_pad)) return -1;
+    /* the row-block kernel fetches 128 rows of one term at a time */
+    if (rows_pad == 256 && make_map(&a->map_rows, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, 128u)) return -1;
     a->ok = true;
     return 0;
 }
@@ -443,6 +445,284 @@ static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka,
     return launch_tc_tp<NB, ST, false>(w, a, ka, tpa, st);
 }
 
+/* ---------------------------------------------------------------- row-block kernel */
+/* 65 .. 256 activation rows (the prompt prefill, tts_cuda_linear_bf16 on many rows). A CTA owns
+ * TWO 128-row weight tiles and ONE block of 128 activation rows: per 64-column k-block it
+ * fetches 2 x 16 KB of weights and the hi and lo BF16 terms of the activations (2 x 16 KB), and
+ * issues 2 tiles x 2 terms x 4 MMAs of 128 x 128 x 16 into two 128-column accumulators. Against
+ * one weight tile x 256 rows x 3 terms (16 KB + 96 KB per k-block for the same arithmetic per
+ * term) this moves 64 KB instead of 112 KB from L2 per k-block, fits three stages instead of
+ * two, and drops the third term: hi + lo carry 16 mantissa bits, a relative error of 4e-6 on the
+ * result, against the 2e-3 the path is allowed. The decode path (1 .. 64 rows) keeps all three
+ * terms. Grid: (tile pairs) x (row blocks) x (K splits), row blocks and splits adjacent so that
+ * the CTAs that share weight tiles run together and the second read hits L2. */
+constexpr int kRbRows = 128, kRbTiles = 2, kRbTerms = 2, kRbStages = 3;
+constexpr int kRbStageW = kTcTileN * kTcBlockK * 2, kRbStageX = kRbRows * kTcBlockK * 2;
+constexpr int kRbStage = kRbTiles * kRbStageW + kRbTerms * kRbStageX;
+constexpr int kRbTmemCols = kRbTiles * kRbRows;
+constexpr int kRbSmemBytes = kRbStages * kRbStage + 1024 + 256 + 4 * kRbRows;
+static_assert(kRbSmemBytes <= 232448, "over the 227 KB a CTA may use");
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+vb_tc_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                  const TcKernelArgs ka) {
+    const int N = ka.N, K = ka.K, M = ka.M, rows_pad = ka.rows_pad, ld_out = ka.ld_out, splits = ka.splits,
+              epi = ka.epi;
+    float *const out = ka.out;
+    int *const status = ka.status;
+    pdl_launch_dependents();
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char *base = (unsigned char *)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char *stages = base;
+    uint64_t *full = (uint64_t *)(base + kRbStages * kRbStage);
+    uint64_t *empty = full + kRbStages;
+    uint64_t *accum = empty + kRbStages;
+    uint32_t *tmem_slot = (uint32_t *)(accum + 1);
+    int *abort_flag = (int *)(tmem_slot + 1);
+    float *rscale = (float *)(abort_flag + 1);   /* [128] per-row scales of this row block */
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int issued = 0;
+    const int row_blocks = (M + kRbRows - 1) / kRbRows;
+    const int sp = blockIdx.x % splits, rb = (blockIdx.x / splits) % row_blocks;
+    const int pair = blockIdx.x / (splits * row_blocks);
+    const int tiles_total = (N + kTcTileN - 1) / kTcTileN;
+    const int t0 = pair * kRbTiles;
+    const int nt = tiles_total - t0 < kRbTiles ? tiles_total - t0 : kRbTiles;
+    const int kblocks = K / kTcBlockK;
+    const int kb0 = (int)((long long)kblocks * sp / splits), kb1 = (int)((long long)kblocks * (sp + 1) / splits);
+    const int n_it = kb1 - kb0;
+    const int m0 = rb * kRbRows;
+    const int Mb = M - m0 < kRbRows ? M - m0 : kRbRows;
+    const uint32_t stage_tx = (uint32_t)(nt * kRbStageW + kRbTerms * kRbStageX);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kRbStages; i++) { vb_mbar_init(&full[i], 1); vb_mbar_init(&empty[i], 1); }
+        vb_mbar_init(accum, 1);
+        *abort_flag = 0;
+        vb_mbar_init_fence();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(vb_smem_u32(tmem_slot)),
+                     "r"((uint32_t)kRbTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *(volatile uint32_t *)tmem_slot;
+
+    if (warp == 4 && lane == 0) {
+        /* ---- TMA producer: weights first (they depend on nothing), activation terms after the
+         * predecessor kernel has finished ---- */
+        auto load_w = [&](int it, int s) {
+            unsigned char *sa = stages + (size_t)s * kRbStage;
+            for (int t = 0; t < nt; t++) {
+                if (ka.a_tiled) tma_load_2d(sa + t * kRbStageW, &mapA, 0, ((t0 + t) * kblocks + kb0 + it) * kTcTileN, &full[s]);
+                else tma_load_2d(sa + t * kRbStageW, &mapA, (kb0 + it) * kTcBlockK, (t0 + t) * kTcTileN, &full[s]);
+            }
+        };
+        auto load_x = [&](int it, int s) {
+            unsigned char *sx = stages + (size_t)s * kRbStage + kRbTiles * kRbStageW;
+#pragma unroll
+            for (int j = 0; j < kRbTerms; j++)
+                tma_load_2d(sx + j * kRbStageX, &mapB, (kb0 + it) * kTcBlockK, j * rows_pad + m0, &full[s]);
+        };
+        const int first = n_it < kRbStages ? n_it : kRbStages;
+        for (int it = 0; it < first; it++) {
+            vb_mbar_arrive_expect_tx(&full[it], stage_tx);
+            load_w(it, it);
+        }
+        issued = first;
+        pdl_wait();
+        for (int it = 0; it < first; it++) load_x(it, it);
+        for (int it = first; it < n_it; it++) {
+            const int s = it % kRbStages, use = it / kRbStages;
+            if (!vb_mbar_wait(&empty[s], (use & 1u) ^ 1u, abort_flag)) {
+                atomicCAS(status, 0, 11);
+                *(volatile int *)abort_flag = 1;
+                break;
+            }
+            vb_mbar_arrive_expect_tx(&full[s], stage_tx);
+            load_w(it, s);
+            load_x(it, s);
+            issued = it + 1;
+        }
+    } else if (warp == 5 && lane == 0) {
+        /* ---- MMA issuer ---- */
+        const uint32_t idesc = umma_idesc_bf16(kRbRows);
+        for (int it = 0; it < n_it; it++) {
+            const int s = it % kRbStages, use = it / kRbStages;
+            if (!vb_mbar_wait(&full[s], use & 1u, abort_flag)) {
+                atomicCAS(status, 0, 12);
+                *(volatile int *)abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const unsigned char *sa = stages + (size_t)s * kRbStage;
+            for (int t = 0; t < nt; t++) {
+                const uint64_t adesc = umma_desc_k_sw128(sa + t * kRbStageW);
+#pragma unroll
+                for (int j = 0; j < kRbTerms; j++) {
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + kRbTiles * kRbStageW + j * kRbStageX);
+#pragma unroll
+                    for (int k = 0; k < kTcBlockK / 16; k++)
+                        umma_bf16(tmem + (uint32_t)(t * kRbRows), adesc + 2 * k, bdesc + 2 * k, idesc,
+                                  (it | j | k) != 0 ? 1u : 0u);
+                }
+            }
+            umma_commit(&empty[s]);
+        }
+        umma_commit(accum);
+    } else if (warp < 4) {
+        /* ---- epilogue: TMEM -> registers -> global ---- */
+        pdl_wait();
+        if (ka.ssq) {
+            for (int m = threadIdx.x; m < Mb; m += 128) {
+                float t = 0.0f;
+                for (int c = 0; c < ka.ssq_chunks; c++) t += __ldcg(ka.ssq + (m0 + m) * ka.ssq_chunks + c);
+                rscale[m] = 1.0f / sqrtf(t / (float)K + ka.eps);
+            }
+            vb_named_bar(1, 128);
+        }
+        bool ok = vb_mbar_wait(accum, 0u, abort_flag);
+        if (!ok) {
+            atomicCAS(status, 0, 13);
+            *(volatile int *)abort_flag = 1;
+        }
+        tc_fence_after();
+        if (ok && n_it > 0) {
+            /* The accumulators go through shared memory (the pipeline stages are free now: every
+             * MMA has completed, so every load has landed and been read) and leave as whole
+             * 512-byte row segments, 16 bytes per lane. Storing straight from the TMEM layout -
+             * lane = output column, one 4-byte store per activation row - took 23 us per CTA
+             * for 128 KB of results: five times the main loop's share. */
+            float *stg = (float *)stages;                       /* [tile][128 rows m][128 columns n] */
+            for (int t = 0; t < nt; t++) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < Mb; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(t * kRbRows + c0), r);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        float v = __uint_as_float(r[i]);
+                        if (ka.ssq && c0 + i < Mb) v *= rscale[c0 + i];
+                        stg[(t * kRbRows + c0 + i) * kTcTileN + warp * 32 + lane] = v;
+                    }
+                }
+            }
+            vb_named_bar(1, 128);
+            if (epi == TC_EPI_SWIGLU || epi == TC_EPI_SWIGLU_TERMS) {
+                /* a lane turns 8 staged values (4 (gate, up) pairs) into 4 results; the 32 lanes
+                 * cover the 128 results of the CTA's two tiles for one activation row */
+                const int tt = lane >> 4, n8 = (lane & 15) * 8;
+                const int col = (t0 + tt) * (kTcTileN / 2) + (lane & 15) * 4;       /* first result column */
+                const size_t ko = (size_t)(N >> 1);
+                if (tt < nt && 2 * col + 7 < N) {
+                    for (int mb = warp; mb < Mb; mb += 4) {
+                        const float4 a = *(const float4 *)(stg + (tt * kRbRows + mb) * kTcTileN + n8);
+                        const float4 b = *(const float4 *)(stg + (tt * kRbRows + mb) * kTcTileN + n8 + 4);
+                        float res[4];
+                        res[0] = (a.x / (1.0f + expf(-a.x))) * a.y;
+                        res[1] = (a.z / (1.0f + expf(-a.z))) * a.w;
+                        res[2] = (b.x / (1.0f + expf(-b.x))) * b.y;
+                        res[3] = (b.z / (1.0f + expf(-b.z))) * b.w;
+                        const int m = m0 + mb;
+                        if (epi == TC_EPI_SWIGLU) {
+                            *(float4 *)(out + (size_t)m * ld_out + col) = make_float4(res[0], res[1], res[2], res[3]);
+                        } else {
+                            uint16_t q[3][4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) vb_split3(res[i], q[0][i], q[1][i], q[2][i]);
+                            const size_t o = (size_t)m * ko + col;
+#pragma unroll
+                            for (int j = 0; j < 3; j++)
+                                *(uint2 *)(ka.out_terms + (size_t)j * ka.out_rows_pad * ko + o) =
+                                    make_uint2(q[j][0] | ((uint32_t)q[j][1] << 16), q[j][2] | ((uint32_t)q[j][3] << 16));
+                        }
+                    }
+                } else if (tt < nt) {
+                    /* ragged edge of the matrix: element by element */
+                    for (int mb = warp; mb < Mb; mb += 4) {
+                        for (int i = 0; i < 4; i++) {
+                            if (2 * (col + i) + 1 >= N) break;
+                            const float g = stg[(tt * kRbRows + mb) * kTcTileN + n8 + 2 * i];
+                            const float u = stg[(tt * kRbRows + mb) * kTcTileN + n8 + 2 * i + 1];
+                            const float res = (g / (1.0f + expf(-g))) * u;
+                            const int m = m0 + mb;
+                            if (epi == TC_EPI_SWIGLU) out[(size_t)m * ld_out + col + i] = res;
+                            else {
+                                uint16_t q0, q1, q2;
+                                vb_split3(res, q0, q1, q2);
+                                const size_t o = (size_t)m * ko + col + i;
+                                ka.out_terms[o] = q0;
+                                ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = q1;
+                                ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int t = 0; t < nt; t++) {
+                    const int n = (t0 + t) * kTcTileN + lane * 4;
+                    for (int mb = warp; mb < Mb; mb += 4) {
+                        float4 v = *(const float4 *)(stg + (t * kRbRows + mb) * kTcTileN + lane * 4);
+                        const size_t o = ((size_t)(epi == TC_EPI_STORE ? 0 : sp) * M + m0 + mb) * ld_out + n;
+                        if (n + 3 < N && (ld_out & 3) == 0) {
+                            if (epi == TC_EPI_STORE && ka.bias) {
+                                const float4 bb = __ldg((const float4 *)(ka.bias + n));
+                                v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+                            }
+                            *(float4 *)(out + o) = v;
+                        } else {
+                            const float e[4] = {v.x, v.y, v.z, v.w};
+                            for (int i = 0; i < 4 && n + i < N; i++)
+                                out[o + i] = e[i] + (epi == TC_EPI_STORE && ka.bias ? __ldg(ka.bias + n + i) : 0.0f);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4 && lane == 0 && *(volatile int *)abort_flag) {
+        /* abort path: let copies already in flight land before the shared memory goes away */
+        const int first_it = issued > kRbStages ? issued - kRbStages : 0;
+        for (int it = first_it; it < issued; it++) {
+            const long long t0c = clock64();
+            while (!vb_mbar_try_wait(&full[it % kRbStages], (uint32_t)(it / kRbStages) & 1u)) {
+                if (clock64() - t0c > VB_WAIT_CYCLES / 8) break;
+            }
+        }
+    }
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kRbTmemCols)
+                     : "memory");
+    }
+}
+
+static int launch_rows(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, cudaStream_t st) {
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(vb_tc_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRbSmemBytes) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return -1;
+        }
+        attr = true;
+    }
+    const int tiles = (ka.N + kTcTileN - 1) / kTcTileN, pairs = (tiles + kRbTiles - 1) / kRbTiles;
+    const int row_blocks = (ka.M + kRbRows - 1) / kRbRows;
+    return launch_pdl(vb_tc_rows_kernel, dim3(pairs * row_blocks * ka.splits), dim3(kTcThreads), (size_t)kRbSmemBytes, st,
+                      w.map, a.map_rows, ka) == cudaSuccess
+               ? 0
+               : -1;
+}
+
 int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st) {
     if (!w.ok || !a.ok || w.K != a.K || g.M < 1 || g.M > a.rows_pad) return -1;
     if (g.splits < 1 || g.splits > kTcMaxSplits || g.splits > w.K / kTcBlockK) return -1;
@@ -468,7 +748,12 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
     switch (a.rows_pad) {
     case 16: return launch_tc<16, 6>(w, a, ka, tpa, st);
     case 64: return launch_tc<64, 5>(w, a, ka, tpa, st);
-    case 256: return launch_tc<256, 2>(w, a, ka, tpa, st);
+    case 256:
+        /* whole-launch calls on one GPU take the row-block kernel; sliced or exchanged launches
+         * (tensor parallelism) do not occur at this size */
+        if (g.n_tiles == 0 && tpa.push.n_dst == 0 && tpa.wait.n == 0 && !getenv("VB200_TC_ROWS_OLD"))
+            return launch_rows(w, a, ka, st);
+        return launch_tc<256, 2>(w, a, ka, tpa, st);
     default: return -1;
     }
 }

@@ -45,6 +45,7 @@ struct TcWeight {
 /* Activation rows split into BF16 terms: [terms][rows_pad][K], rows_pad = 16, 64 or 256. */
 struct TcActs {
     CUtensorMap map;
+    CUtensorMap map_rows;   /* rows_pad == 256 only: box of 128 rows (row-block kernel) */
     uint16_t *buf;
     int rows_pad, K;
     bool ok;
