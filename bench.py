@@ -389,6 +389,25 @@ def micro_stream(args):
                       "peak_source": src}))
 
 
+def micro_prefill(args):
+    """tts_cuda_llm_prefill alone: `--m` prompt rows (host fp32 rows in, cache rows out), `--reps`
+    calls, wall clock per call (the call is synchronous). Uploads the decoder only. The launch
+    list of the prefill is taken from this command."""
+    pkg = load_package()
+    model = pkg.SynthModel(seed=1234)
+    eng = pkg.Engine(kv_cache_max=max(64, args.m + 8))
+    eng.upload(model, decoder=True, acoustic=False)
+    rows = prompt_rows(pkg, model, utterance_seeds(0)["prompt"])[:args.m]
+    eng.prefill(rows, 0)
+    t = []
+    for _ in range(args.reps):
+        t0 = time.perf_counter()
+        eng.prefill(rows, 0)
+        t.append((time.perf_counter() - t0) * 1e3)
+    print(json.dumps({"micro": "prefill", "rows": int(rows.shape[0]), "calls": args.reps, "ms_per_call_min": min(t),
+                      "ms_per_call_median": sorted(t)[len(t) // 2]}))
+
+
 def micro(args):
     """One GEMV op of the frame kernel through tts_cuda_linear_bf16 on device buffers:
     y[m,n] = x[m,k] . W[n,k]^T. Not the headline metric: a small, self-contained case for profiling."""
@@ -396,6 +415,8 @@ def micro(args):
         return micro_gemm(args)
     if args.micro == "stream":
         return micro_stream(args)
+    if args.micro == "prefill":
+        return micro_prefill(args)
     pkg = load_package()
     eng = pkg.Engine(kv_cache_max=64)
     L = eng.L
@@ -467,7 +488,7 @@ def main():
                     help="--micro gemm: one weight copy (stays in L2 when it fits) instead of rotating copies")
     ap.add_argument("--ops", type=int, default=16, help="--micro stream: GEMV ops per launch")
     ap.add_argument("--no-sync", action="store_true", help="--micro stream: no grid barrier between the ops")
-    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm", "stream"],
+    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm", "stream", "prefill"],
                     help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--k", type=int, default=3072)

@@ -596,7 +596,9 @@ static int bt_weights() {
             tiled(&w.w2[l], L.w2, D, HID))
             return -1;
     }
-    if (tiled(&w.wsem, m.ac_sem_out, NSEM, D) || tiled(&w.wllm, m.ac_llm_proj, D, D)) return -1;
+    /* the two heads belong to the acoustic upload; a decoder-only model (prefill) does without */
+    w.wsem.ok = w.wllm.ok = false;
+    if (m.ac_ready && (tiled(&w.wsem, m.ac_sem_out, NSEM, D) || tiled(&w.wllm, m.ac_llm_proj, D, D))) return -1;
     if (cudaStreamSynchronize(m.st) != cudaSuccess) return -1;
     w.s_qkv = tc_pick_splits(QKV, D, m.sm_count);
     w.s_wo = tc_pick_splits(D, QD, m.sm_count);
@@ -604,6 +606,13 @@ static int bt_weights() {
     w.s_sem = tc_pick_splits(NSEM, D, m.sm_count);
     w.s_llm = tc_pick_splits(D, D, m.sm_count);
     w.ready = true;
+    return 0;
+}
+
+/* The decoder's tile-contiguous matrices for the prefill: [26] each, in layer order. */
+int batch_tiled_decoder(const TcWeight **wqkv, const TcWeight **wo, const TcWeight **w13, const TcWeight **w2) {
+    if (!model().llm_ready || bt_weights()) return -1;
+    *wqkv = g_w.wqkv; *wo = g_w.wo; *w13 = g_w.w13; *w2 = g_w.w2;
     return 0;
 }
 

@@ -151,6 +151,8 @@ int tp_plan(int rank, int world, int n_sm, int *out);
 void tp_close();
 void batch_close();
 void batch_invalidate();
+struct TcWeight;
+int batch_tiled_decoder(const TcWeight **wqkv, const TcWeight **wo, const TcWeight **w13, const TcWeight **w2);
 void batch_options_changed();
 void single_path_changed();
 void batch_free_all();

@@ -46,10 +46,138 @@ static int run_row_blocks(VbOp proto, int M, int x_ld, int y_ld, bool res_is_y) 
     return 0;
 }
 
+/* ---- glue kernels of the tensor-core prefill ---- */
+
+/* QKV of a row block: sums the split-K partials in fixed order, rotates the q and k heads
+ * (interleaved pairs, voxtral_tts_kernels.c:616-634), leaves q in `qkv` for the attention
+ * and writes k and v straight into the cache rows (voxtral_tts_llm.c:318-330). One thread per
+ * pair of columns. */
+__global__ void pf_qkv_finish_kernel(float *qkv, const float *part, int n_part, size_t part_stride, const float *cs,
+                                     float *k_rows, float *v_rows, int rows) {
+    const int m = blockIdx.y;
+    const int col = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (col >= QKV || m >= rows) return;
+    float2 v = make_float2(0.0f, 0.0f);
+    for (int p = 0; p < n_part; p++) {
+        const float2 t = __ldcg(reinterpret_cast<const float2 *>(part + (size_t)p * part_stride + (size_t)m * QKV + col));
+        v.x += t.x; v.y += t.y;
+    }
+    if (col < QD + KVD) {
+        const int d = (col % VB200_HEAD_DIM) >> 1;
+        const float2 t = *reinterpret_cast<const float2 *>(cs + ((size_t)m * (VB200_HEAD_DIM / 2) + d) * 2);
+        const float a = v.x, b = v.y;
+        v.x = a * t.x - b * t.y;
+        v.y = a * t.y + b * t.x;
+    }
+    if (col < QD) *reinterpret_cast<float2 *>(qkv + (size_t)m * QKV + col) = v;
+    else if (col < QD + KVD) *reinterpret_cast<float2 *>(k_rows + (size_t)m * KVD + (col - QD)) = v;
+    else *reinterpret_cast<float2 *>(v_rows + (size_t)m * KVD + (col - QD - KVD)) = v;
+}
+
+/* Causal attention of a block of prompt rows over the cache prefix (tts_causal_attention,
+ * voxtral_tts_kernels.c:403-465), head_dim 128, four query heads per KV head. A CTA owns one KV
+ * head and 8 query rows: 8 rows x 4 heads = 32 queries, each spread over 4 threads that own
+ * every fourth 16-byte piece of the head dimension. K and V rows are staged in shared memory 32
+ * keys at a time, once per KV head, and every thread walks the staged keys in steps of eight:
+ * eight partial dot products, two shuffles each to join the four pieces, one running-maximum
+ * update per eight keys. Row blocks are issued heaviest (latest rows) first. */
+constexpr int kPaRows = 8, kPaKeys = 32, kPaThreads = kPaRows * 4 * 4;
+
+__global__ void __launch_bounds__(kPaThreads)
+pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc, int M, int start_pos, int ldq,
+                    int ldkv, int ldo, float scale) {
+    __shared__ float4 Ks[kPaKeys * 32];
+    __shared__ float4 Vs[kPaKeys * 32];
+    const int g = blockIdx.y, r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPaRows;
+    const int tid = threadIdx.x, sl = tid & 3, qi = tid >> 2;
+    const int hl = qi & 3, rl = qi >> 2;
+    const int row = r0 + rl, h = g * 4 + hl;
+    const bool valid = row < M;
+    const int limit = valid ? start_pos + row : 0;               /* last key this query sees */
+    const int rows_here = M - r0 < kPaRows ? M - r0 : kPaRows;
+    const int n_keys = start_pos + r0 + rows_here;               /* keys 0 .. n_keys-1 serve this block */
+    float qv[32], o[32];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid) t = *reinterpret_cast<const float4 *>(q + (size_t)row * ldq + h * VB200_HEAD_DIM + 4 * (sl + 4 * j));
+        qv[4 * j] = t.x * scale; qv[4 * j + 1] = t.y * scale; qv[4 * j + 2] = t.z * scale; qv[4 * j + 3] = t.w * scale;
+        o[4 * j] = o[4 * j + 1] = o[4 * j + 2] = o[4 * j + 3] = 0.0f;
+    }
+    float mx = -1e30f, den = 0.0f;
+    for (int k0 = 0; k0 < n_keys; k0 += kPaKeys) {
+        __syncthreads();
+        for (int i = tid; i < kPaKeys * 32; i += kPaThreads) {
+            const int kk = k0 + (i >> 5), f = i & 31;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+            if (kk < n_keys) {
+                a = __ldg(reinterpret_cast<const float4 *>(kc + (size_t)kk * ldkv + g * VB200_HEAD_DIM) + f);
+                b = __ldg(reinterpret_cast<const float4 *>(vc + (size_t)kk * ldkv + g * VB200_HEAD_DIM) + f);
+            }
+            Ks[i] = a;
+            Vs[i] = b;
+        }
+        __syncthreads();
+        const int kt = n_keys - k0 < kPaKeys ? n_keys - k0 : kPaKeys;
+        for (int c = 0; c < kt; c += 8) {
+            float sc[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                float d = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float4 kv = Ks[(c + u) * 32 + sl + 4 * j];
+                    d += qv[4 * j] * kv.x + qv[4 * j + 1] * kv.y + qv[4 * j + 2] * kv.z + qv[4 * j + 3] * kv.w;
+                }
+                sc[u] = d;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], 1);
+                sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], 2);
+            }
+            float cm = -1e30f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (k0 + c + u > limit) sc[u] = -1e30f;
+                cm = fmaxf(cm, sc[u]);
+            }
+            const float m_new = fmaxf(mx, cm);
+            const float corr = expf(mx - m_new);
+            float p[8], ps = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                p[u] = k0 + c + u > limit ? 0.0f : expf(sc[u] - m_new);
+                ps += p[u];
+            }
+            den = den * corr + ps;
+            mx = m_new;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float4 acc = make_float4(o[4 * j] * corr, o[4 * j + 1] * corr, o[4 * j + 2] * corr, o[4 * j + 3] * corr);
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const float4 vv = Vs[(c + u) * 32 + sl + 4 * j];
+                    acc.x += p[u] * vv.x; acc.y += p[u] * vv.y; acc.z += p[u] * vv.z; acc.w += p[u] * vv.w;
+                }
+                o[4 * j] = acc.x; o[4 * j + 1] = acc.y; o[4 * j + 2] = acc.z; o[4 * j + 3] = acc.w;
+            }
+        }
+    }
+    if (valid) {
+        const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            *reinterpret_cast<float4 *>(out + (size_t)row * ldo + h * VB200_HEAD_DIM + 4 * (sl + 4 * j)) =
+                make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+    }
+}
+
 /* ---- tensor-core prefill ---- */
 struct PrefillTc {
     bool ready = false;
-    TcWeight wqkv[VB200_DEC_LAYERS], wo[VB200_DEC_LAYERS], w13[VB200_DEC_LAYERS], w2[VB200_DEC_LAYERS];
+    /* the decoder's tile-contiguous matrices (shared with the frame graph), fetched per call */
+    const TcWeight *wqkv = nullptr, *wo = nullptr, *w13 = nullptr, *w2 = nullptr;
     uint16_t *bD = nullptr, *bQ = nullptr, *bH = nullptr;
     float *part = nullptr, *ssq = nullptr;
     TcActs aD[3], aQ[3], aH[3];   /* for 16, 64 and 256 padded rows, over the same buffers */
@@ -59,19 +187,12 @@ static const int kPfRows = 256;
 
 static int pf_slot(int rows_pad) { return rows_pad == 16 ? 0 : rows_pad == 64 ? 1 : 2; }
 
-/* Tensor maps of the decoder weights and the activation-term buffers; called after the
- * decoder upload. Failing here is not fatal: prefill() then uses the streaming kernel. */
+/* The activation-term buffers and their tensor maps; called after the decoder upload. Failing here is not fatal: prefill() then uses the streaming kernel. */
 int prefill_tc_setup() {
     Model &m = model();
     PrefillTc &t = g_pf;
     t.ready = false;
     if (getenv("VB200_NO_TC") || tc_init()) return 0;
-    for (int l = 0; l < VB200_DEC_LAYERS; l++) {
-        const LayerDev &L = m.dec[l];
-        if (tc_weight(&t.wqkv[l], L.wqkv, QKV, D) || tc_weight(&t.wo[l], L.wo, D, QD) ||
-            tc_weight(&t.w13[l], L.w13, 2 * HID, D) || tc_weight(&t.w2[l], L.w2, D, HID))
-            return 0;
-    }
     if (!t.bD) {
         void *p[5] = {};
         const size_t sz[5] = {tc_acts_bytes(kPfRows, D), tc_acts_bytes(kPfRows, QD), tc_acts_bytes(kPfRows, HID),
@@ -115,21 +236,14 @@ static int prefill_tc(float *x, float *qkv, float *attn, const float *cs, int M,
             g.M = rows; g.status = &m.d_out->status; g.epi = TC_EPI_PARTIAL; g.out = t.part; g.ld_out = QKV;
             g.splits = s_qkv; g.ssq = t.ssq; g.ssq_chunks = chunksD; g.eps = VB200_NORM_EPS;
             if (tc_gemm(t.wqkv[l], t.aD[slot], g, st)) return -1;
-            tc_reduce(qr, t.part, s_qkv, (size_t)rows * QKV, (size_t)rows * QKV, nullptr, QKV, st);
-            rope_apply(qr, cs + (size_t)r0 * VB200_HEAD_DIM, rows, VB200_HEADS, VB200_HEAD_DIM, QKV, st);
-            rope_apply(qr + QD, cs + (size_t)r0 * VB200_HEAD_DIM, rows, VB200_KV_HEADS, VB200_HEAD_DIM, QKV, st);
             float *ck = m.kv_k + ((size_t)l * m.kv_max + start_pos + r0) * KVD;
             float *cv = m.kv_v + ((size_t)l * m.kv_max + start_pos + r0) * KVD;
-            if (cudaMemcpy2DAsync(ck, (size_t)KVD * 4, qr + QD, (size_t)QKV * 4, (size_t)KVD * 4, rows,
-                                  cudaMemcpyDeviceToDevice, st) != cudaSuccess ||
-                cudaMemcpy2DAsync(cv, (size_t)KVD * 4, qr + QD + KVD, (size_t)QKV * 4, (size_t)KVD * 4, rows,
-                                  cudaMemcpyDeviceToDevice, st) != cudaSuccess)
-                return -1;
+            pf_qkv_finish_kernel<<<dim3(QKV / 2 / 256, rows), 256, 0, st>>>(qr, t.part, s_qkv, (size_t)rows * QKV,
+                                                                            cs + (size_t)r0 * VB200_HEAD_DIM, ck, cv, rows);
         }
         const float *k0 = m.kv_k + (size_t)l * m.kv_max * KVD, *v0 = m.kv_v + (size_t)l * m.kv_max * KVD;
-        if (attention_rows(attn, qkv, k0, v0, M, start_pos + M, VB200_HEADS, VB200_KV_HEADS, VB200_HEAD_DIM, scale,
-                           start_pos, 1, QKV, KVD, QD, st))
-            return -1;
+        pf_attention_kernel<<<dim3((M + kPaRows - 1) / kPaRows, VB200_KV_HEADS), kPaThreads, 0, st>>>(
+            attn, qkv, k0, v0, M, start_pos, QKV, KVD, QD, scale);
         if (l == VB200_DEC_LAYERS - 1) break;   /* only the cache is kept (voxtral_tts_llm.c:281) */
         for (int r0 = 0; r0 < M; r0 += kPfRows) {
             const int rows = M - r0 < kPfRows ? M - r0 : kPfRows;
@@ -176,7 +290,7 @@ int prefill(const float *embeds, int seq_len, int start_pos) {
     if (!rc && cudaMemcpyAsync(x, embeds, (size_t)M * D * 4, cudaMemcpyDefault, m.st) != cudaSuccess) rc = -1;
     if (!rc) rope_table(cs, start_pos, M, VB200_HEAD_DIM, VB200_ROPE_THETA, m.st);
 
-    if (!rc && g_pf.ready) {
+    if (!rc && g_pf.ready && batch_tiled_decoder(&g_pf.wqkv, &g_pf.wo, &g_pf.w13, &g_pf.w2) == 0) {
         rc = prefill_tc(x, qkv, attn, cs, M, start_pos);
         if (cudaStreamSynchronize(m.st) != cudaSuccess) rc = -1;
         cudaFree(x); cudaFree(qkv); cudaFree(attn); cudaFree(h); cudaFree(cs);
