@@ -184,7 +184,7 @@ struct TcNoTpArgs {};
 template <bool TP> struct TcTpSel { using type = TcNoTpArgs; };
 template <> struct TcTpSel<true> { using type = TcTpArgs; };
 
-template <int NB, int ST, bool TP>
+template <int NB, int ST, bool TP, bool STG>
 __global__ void __launch_bounds__(kTcThreads, 1)
 vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                   const TcKernelArgs ka, const typename TcTpSel<TP>::type tp) {
@@ -330,6 +330,11 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         }
         tc_fence_after();
         const int row = tile * kTcTileN + warp * 32 + lane;
+        /* From four activation rows on, the results leave through shared memory (the pipeline
+         * stages are free once every MMA has completed) as 16-byte stores along the output
+         * columns: one 4-byte store per row straight from the TMEM layout costs ~90 ns each. */
+        constexpr bool staged = STG;     /* a separate instantiation: the one-row launches of the frame keep their lean code */
+        float *stg = (float *)stages;                              /* [M][128 output columns] */
         if (ok && n_it > 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < NB && c0 < M; c0 += 16) {
@@ -349,6 +354,10 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                     const int m = c0 + i;
                     float v = __uint_as_float(r[i]);
                     if (ka.ssq && m < M) v *= rscale[m];
+                    if constexpr (staged) {
+                        if (m < M) stg[m * kTcTileN + warp * 32 + lane] = v;
+                        continue;
+                    }
                     if (epi == TC_EPI_SWIGLU || epi == TC_EPI_SWIGLU_TERMS) {
                         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
                         if (m < M && row < N && (lane & 1) == 0) {
@@ -380,6 +389,66 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                             if constexpr (TP) {
                                 for (int d = 1; d < tp.push.n_dst; d++)
                                     *(float *)((char *)(out + o) + tp.push.dst_off[d]) = v;
+                            }
+                        }
+                    }
+                }
+            }
+            if constexpr (staged) {
+                vb_named_bar(1, 128);
+                const int n = tile * kTcTileN + lane * 4;             /* this lane's four output columns */
+                for (int m = warp; m < M; m += 4) {
+                    const float4 v = *(const float4 *)(stg + m * kTcTileN + lane * 4);
+                    if (epi == TC_EPI_SWIGLU || epi == TC_EPI_SWIGLU_TERMS) {
+                        /* (gate, up, gate, up) -> two results */
+                        const float res[2] = {(v.x / (1.0f + expf(-v.x))) * v.y, (v.z / (1.0f + expf(-v.z))) * v.w};
+                        const int col = n >> 1;
+                        const size_t ko = (size_t)(N >> 1);
+                        for (int i = 0; i < 2; i++) {
+                            if (n + 2 * i + 1 >= N) break;
+                            if (epi == TC_EPI_SWIGLU) {
+                                out[(size_t)m * ld_out + col + i] = res[i];
+                            } else {
+                                uint16_t q0, q1, q2;
+                                vb_split3(res[i], q0, q1, q2);
+                                const size_t o = (size_t)m * ko + col + i;
+                                ka.out_terms[o] = q0;
+                                ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = q1;
+                                ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
+                                if constexpr (TP) {
+                                    for (int d = 1; d < tp.push.n_dst; d++) {
+                                        uint16_t *pt = (uint16_t *)((char *)ka.out_terms + tp.push.dst_off[d]);
+                                        pt[o] = q0;
+                                        pt[(size_t)ka.out_rows_pad * ko + o] = q1;
+                                        pt[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
+                                    }
+                                }
+                            }
+                        }
+                    } else {
+                        const size_t o = ((size_t)(epi == TC_EPI_STORE ? 0 : sp) * M + m) * ld_out + n;
+                        if (n + 3 < N && (ld_out & 3) == 0) {
+                            float4 w4 = v;
+                            if (epi == TC_EPI_STORE && bias) {
+                                w4.x += __ldg(bias + n); w4.y += __ldg(bias + n + 1);
+                                w4.z += __ldg(bias + n + 2); w4.w += __ldg(bias + n + 3);
+                            }
+                            *(float4 *)(out + o) = w4;
+                            if constexpr (TP) {
+                                if (epi != TC_EPI_STORE)
+                                    for (int d = 1; d < tp.push.n_dst; d++)
+                                        *(float4 *)((char *)(out + o) + tp.push.dst_off[d]) = w4;
+                            }
+                        } else {
+                            const float e[4] = {v.x, v.y, v.z, v.w};
+                            for (int i = 0; i < 4 && n + i < N; i++) {
+                                const float w1 = e[i] + (epi == TC_EPI_STORE && bias ? __ldg(bias + n + i) : 0.0f);
+                                out[o + i] = w1;
+                                if constexpr (TP) {
+                                    if (epi != TC_EPI_STORE)
+                                        for (int d = 1; d < tp.push.n_dst; d++)
+                                            *(float *)((char *)(out + o + i) + tp.push.dst_off[d]) = w1;
+                                }
                             }
                         }
                     }
@@ -417,13 +486,13 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     }
 }
 
-template <int NB, int ST, bool TP>
+template <int NB, int ST, bool TP, bool STG>
 static int launch_tc_tp(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, const TcTpArgs &tpa,
                         cudaStream_t st) {
     using Cfg = TcCfg<NB, ST>;
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST, TP, STG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemBytes) != cudaSuccess) {
             cudaGetLastError();
             return -1;
@@ -433,16 +502,20 @@ static int launch_tc_tp(const TcWeight &w, const TcActs &a, const TcKernelArgs &
     const int tiles = ka.n_tiles_launch;
     typename TcTpSel<TP>::type arg;
     if constexpr (TP) arg = tpa;
-    return launch_pdl(vb_tc_gemm_kernel<NB, ST, TP>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
-                      w.map, a.map, ka, arg) == cudaSuccess
+    return launch_pdl(vb_tc_gemm_kernel<NB, ST, TP, STG>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes,
+                      st, w.map, a.map, ka, arg) == cudaSuccess
                ? 0
                : -1;
 }
 
+/* Launches with four or more activation rows take the instantiation whose results leave
+ * through shared memory. */
 template <int NB, int ST>
 static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, const TcTpArgs &tpa, cudaStream_t st) {
-    if (tpa.push.n_dst > 0 || tpa.wait.n > 0) return launch_tc_tp<NB, ST, true>(w, a, ka, tpa, st);
-    return launch_tc_tp<NB, ST, false>(w, a, ka, tpa, st);
+    const bool tp = tpa.push.n_dst > 0 || tpa.wait.n > 0;
+    if (ka.M >= 4)
+        return tp ? launch_tc_tp<NB, ST, true, true>(w, a, ka, tpa, st) : launch_tc_tp<NB, ST, false, true>(w, a, ka, tpa, st);
+    return tp ? launch_tc_tp<NB, ST, true, false>(w, a, ka, tpa, st) : launch_tc_tp<NB, ST, false, false>(w, a, ka, tpa, st);
 }
 
 /* ---------------------------------------------------------------- row-block kernel */
