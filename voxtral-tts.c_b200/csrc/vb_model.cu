@@ -210,7 +210,7 @@ static void stage_open() {
     if (s.ok) return;
     const char *env = getenv("VB200_UPLOAD_THREADS");
     unsigned hc = std::thread::hardware_concurrency();
-    s.threads = env ? atoi(env) : (hc >= 16 ? 8 : hc >= 4 ? 4 : 1);
+    s.threads = env ? atoi(env) : (hc >= 4 ? 4 : 1);   /* four saturate the host's copy bandwidth where measured */
     if (s.threads < 1) s.threads = 1;
     if (s.threads > 32) s.threads = 32;
     for (int i = 0; i < Stager::kBufs; i++) {
