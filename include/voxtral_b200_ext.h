@@ -183,6 +183,51 @@ void vb200_synth_f32(float *dst, size_t n, uint64_t seed, uint64_t stream, uint6
  * default seed). One frame that is not END consumes 36 of them (voxtral_tts_acoustic.c:329). */
 void vb200_randn_fill(uint64_t *state, float *out, size_t n);
 
+/* ---- codec decoder on the GPU (tts_codec_decode, voxtral_tts_codec.c:389-510) ----
+ * 37 codes per frame -> 24 kHz waveform, 1920 samples per frame: code embedding, causal
+ * convolution 292 -> 1024, four stages of two transformer layers (ALiBi sliding-window
+ * attention, QK norm, layer scale; voxtral_tts_codec.c:306-383) with three stride-2 transposed
+ * convolutions between them, causal convolution 1024 -> 240. The three structs mirror tts_conv_t,
+ * tts_codec_layer_t and tts_codec_t (voxtral_tts.h:172-225) field by field, so a host that has run
+ * the reference's tts_codec_load passes &ctx->codec. All pointers are host fp32 arrays.
+ *
+ * The transformer matrices must be exactly representable in BF16 (they are when the checkpoint
+ * stores them as BF16, which safetensors_get_f32 merely widens): they are kept as BF16 on the
+ * device and multiplied on the tensor cores; vb200_codec_upload returns -1 and says so when a
+ * value would be rounded. The (weight-normed) convolution weights stay fp32. */
+typedef struct {
+    float *weight;              /* conv: [out_ch, in_ch, kernel]; transposed conv: [in_ch, out_ch, kernel] */
+    float *bias;                /* [out_ch] or NULL */
+    int in_ch, out_ch, kernel, stride, is_transpose;
+} vb200_conv_t;
+
+typedef struct {
+    float *wq, *wk, *wv, *wo;   /* [1024, 1024] */
+    float *q_norm, *k_norm;     /* [1024] or NULL */
+    float *attention_norm;      /* [1024] */
+    float *w1, *w2, *w3;        /* [4096, 1024], [1024, 4096], [4096, 1024] */
+    float *ffn_norm;            /* [1024] */
+    float *attn_scale, *ffn_scale; /* [1024] or NULL */
+    int window_size;
+} vb200_codec_layer_t;
+
+typedef struct {
+    float *semantic_embedding;  /* [8192, 256] */
+    vb200_conv_t input_conv;    /* 292 -> 1024, kernel 3 */
+    vb200_codec_layer_t transformers[8];
+    vb200_conv_t stage_convs[4];/* [0..2]: transposed, 1024 -> 1024, kernel 4, stride 2; [3] unused */
+    vb200_conv_t output_proj;   /* 1024 -> 240, kernel 7 */
+    float alibi_slopes[8];
+} vb200_codec_weights_t;
+
+/* Needs tts_cuda_init. 0 on success. */
+int vb200_codec_upload(const vb200_codec_weights_t *w);
+/* codes: [n_frames, 37] host ints. Writes n_frames * 1920 samples to samples_out (host) when
+ * max_samples allows, stores the count in *n_samples; -1 on any failure (nothing is written). */
+int vb200_codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples);
+/* Device time of the last vb200_codec_decode in milliseconds (CUDA events around its kernels). */
+float vb200_codec_last_ms(void);
+
 #ifdef __cplusplus
 }
 #endif

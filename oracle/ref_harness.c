@@ -69,6 +69,7 @@ void refh_destroy(void *p) {
 size_t refh_sizeof_ctx(void) { return sizeof(tts_ctx_t); }
 size_t refh_sizeof_decoder(void) { return sizeof(tts_decoder_t); }
 size_t refh_sizeof_acoustic(void) { return sizeof(tts_acoustic_t); }
+size_t refh_sizeof_codec(void) { return sizeof(tts_codec_t); }
 void *refh_decoder_ptr(void *p) { return &((tts_ctx_t *)p)->decoder; }
 void *refh_acoustic_ptr(void *p) { return &((tts_ctx_t *)p)->acoustic; }
 
@@ -165,4 +166,22 @@ void refh_constants(int *out) {
     out[7] = TTS_ACOUSTIC_DIM; out[8] = TTS_SEMANTIC_CB_PADDED; out[9] = TTS_FLOW_STEPS;
     out[10] = TTS_FSQ_LEVELS; out[11] = TTS_CODES_PER_FRAME; out[12] = TTS_SEMANTIC_CB_SIZE;
     out[13] = TTS_VOCAB_SIZE;
+}
+
+/* ---- codec decoder (voxtral_tts_codec.c, compiled unchanged beside this file) ----
+ * `weights` is a tts_codec_t filled by the caller (pointers into the caller's arrays). Runs
+ * tts_codec_decode (voxtral_tts_codec.c:389-510) and copies the waveform out. Returns the number
+ * of samples, or -1. */
+int refh_codec_decode(void *p, const void *weights, const int *codes, int n_frames, float *out, int max_samples) {
+    tts_ctx_t *c = (tts_ctx_t *)p;
+    if (!c || !weights) return -1;
+    memcpy(&c->codec, weights, sizeof(tts_codec_t));
+    float *samples = NULL;
+    int n = 0;
+    tts_codec_decode(c, codes, n_frames, &samples, &n);
+    memset(&c->codec, 0, sizeof(tts_codec_t));       /* the arrays are the caller's */
+    if (!samples || n <= 0 || n > max_samples) { free(samples); return -1; }
+    memcpy(out, samples, sizeof(float) * (size_t)n);
+    free(samples);
+    return n;
 }

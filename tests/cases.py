@@ -60,3 +60,25 @@ def config3_prompt(pkg, model):
 
 def config4_first_embed(model):
     return model.token_rows([24])[0]          # embed(AUDIO), voxtral_tts.c:295
+
+
+# ---- codec decoder (voxtral_tts_codec.c:389-510) ----
+CODEC_SEED = 77
+CODEC_GOLDEN_FRAMES = 5
+
+
+def codec_codes(n_frames, seed=5):
+    """[n_frames, 37] codes as the acoustic stage emits them: semantic 2 .. 8193, acoustic
+    2 .. 22 (FSQ level + 2). Frame 0 also carries values below the special-token offset and
+    above the code books (the decoder clamps them, voxtral_tts_codec.c:283-296) when there is
+    more than one frame."""
+    import numpy as np
+    rng = np.random.default_rng(seed + 1000 * n_frames)
+    codes = np.concatenate([rng.integers(2, 8194, size=(n_frames, 1)), rng.integers(2, 23, size=(n_frames, 36))],
+                           axis=1).astype(np.int32)
+    if n_frames > 1:
+        codes[0, 0] = 0
+        codes[0, 1] = 1
+        codes[0, 2] = 30
+        codes[1, 0] = 9000
+    return codes

@@ -15,6 +15,8 @@ With --full (minutes of CPU; uses the OpenBLAS build, as the reference's `make b
   config3_prefill.npz  cache rows after a 256-row prompt: three rows of three layers in full,
                        and the norm of every row of those layers
   config4_slice.npz    that prompt followed by 16 generated frames: codes, hidden rows, RNG state
+With --codec (seconds):
+  codec_frames.npz     the codec decoder's waveform for a few frames of seeded codes (SynthCodec)
 """
 import os
 import sys
@@ -60,8 +62,22 @@ def full_size(pkg, model):
     print("full-size fixtures written to", HERE)
 
 
+def codec(pkg):
+    """The reference's tts_codec_decode on the seeded synthetic codec weights."""
+    from cases import CODEC_GOLDEN_FRAMES, CODEC_SEED, codec_codes
+    ref = ob.load_ref("noblas")
+    if ref is None or not hasattr(ref.L, "refh_codec_decode"):
+        raise SystemExit("oracle/_ref/libvoxref_noblas.so (with the codec) missing: run oracle/build_oracle.py")
+    w = pkg.SynthCodec(seed=CODEC_SEED)
+    pcm = ref.codec_decode(w.struct(), codec_codes(CODEC_GOLDEN_FRAMES))
+    np.savez_compressed(os.path.join(HERE, "codec_frames.npz"), pcm=pcm)
+    print("codec fixture written:", pcm.shape)
+
+
 def main():
     pkg = load_package()
+    if "--codec" in sys.argv:
+        return codec(pkg)
     if "--full" in sys.argv:
         return full_size(pkg, pkg.SynthModel(seed=MODEL_SEED))
     ref = ob.load_ref("noblas")

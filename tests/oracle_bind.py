@@ -258,6 +258,9 @@ class Ref:
         L.refh_sizeof_ctx.restype = C.c_size_t
         L.refh_sizeof_decoder.restype = C.c_size_t
         L.refh_sizeof_acoustic.restype = C.c_size_t
+        if hasattr(L, "refh_codec_decode"):
+            L.refh_sizeof_codec.restype = C.c_size_t
+            L.refh_codec_decode.argtypes = [vp, vp, vp, C.c_int, vp, C.c_int]
         L.refh_decoder_ptr.argtypes = [vp]
         L.refh_decoder_ptr.restype = vp
         L.refh_acoustic_ptr.argtypes = [vp]
@@ -318,6 +321,17 @@ class Ref:
         if self.ctx:
             self.L.refh_destroy(self.ctx)
             self.ctx = None
+
+    def codec_decode(self, codec_struct, codes):
+        """tts_codec_decode (voxtral_tts_codec.c:389-510) on a caller-filled tts_codec_t."""
+        codes = np.ascontiguousarray(codes, dtype=np.int32).reshape(-1, 37)
+        ctx = self.L.refh_create()
+        out = np.empty(codes.shape[0] * 1920, dtype=np.float32)
+        n = self.L.refh_codec_decode(ctx, C.byref(codec_struct), _p(codes), codes.shape[0], _p(out), out.size)
+        self.L.refh_destroy(ctx)
+        if n < 0:
+            raise RuntimeError("reference tts_codec_decode failed")
+        return out[:n]
 
     def kv(self):
         n = DEC_LAYERS * self.kv_max * KV_DIM

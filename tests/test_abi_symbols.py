@@ -37,6 +37,8 @@ def test_g_cuda_layout_matches_reference(pkg, ref_noblas):
     """Struct sizes of the weight tables the upload calls receive match the reference's."""
     assert ref_noblas.L.refh_sizeof_decoder() == C.sizeof(pkg.DecoderWeights)
     assert ref_noblas.L.refh_sizeof_acoustic() == C.sizeof(pkg.AcousticWeights)
+    ref_noblas.L.refh_sizeof_codec.restype = C.c_size_t
+    assert ref_noblas.L.refh_sizeof_codec() == C.sizeof(pkg.CodecWeights)
     c = ref_noblas.constants()
     assert list(c[:14]) == [pkg.DIM, pkg.DEC_LAYERS, pkg.HEADS, pkg.KV_HEADS, pkg.HEAD_DIM, pkg.HIDDEN,
                             pkg.AC_LAYERS, pkg.ACOUSTIC_DIM, pkg.SEM_PADDED, pkg.FLOW_STEPS, pkg.FSQ_LEVELS,

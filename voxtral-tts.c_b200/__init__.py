@@ -88,6 +88,9 @@ def lib():
         "vb200_upload_audio_embed": (C.c_int, [C.c_void_p, C.c_int]),
         "vb200_prefill_prompt": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int]),
         "vb200_upload_stats": (None, [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+        "vb200_codec_upload": (C.c_int, [C.c_void_p]),
+        "vb200_codec_decode": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_int)]),
+        "vb200_codec_last_ms": (C.c_float, []),
         "vb200_utterance_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
         "vb200_utterance_run": (C.c_int, [C.c_int]),
         "vb200_batch_open": (C.c_int, [C.c_int, C.c_int, C.c_int]),
@@ -142,6 +145,26 @@ EXPORTED_SYMBOLS_REFERENCE = [
     "tts_cuda_predict_velocity", "tts_cuda_to_device", "tts_cuda_to_host", "tts_cuda_memset", "tts_cuda_alloc",
     "tts_cuda_free_ptr", "tts_cuda_sync",
 ]
+
+
+class ConvWeights(C.Structure):
+    """tts_conv_t (voxtral_tts.h:172-181)."""
+    _fields_ = [("weight", C.c_void_p), ("bias", C.c_void_p), ("in_ch", C.c_int), ("out_ch", C.c_int),
+                ("kernel", C.c_int), ("stride", C.c_int), ("is_transpose", C.c_int)]
+
+
+class CodecLayerWeights(C.Structure):
+    """tts_codec_layer_t (voxtral_tts.h:184-205)."""
+    _fields_ = [(n, C.c_void_p) for n in ("wq", "wk", "wv", "wo", "q_norm", "k_norm", "attention_norm",
+                                          "w1", "w2", "w3", "ffn_norm", "attn_scale", "ffn_scale")] + \
+               [("window_size", C.c_int)]
+
+
+class CodecWeights(C.Structure):
+    """tts_codec_t (voxtral_tts.h:207-225)."""
+    _fields_ = [("semantic_embedding", C.c_void_p), ("input_conv", ConvWeights),
+                ("transformers", CodecLayerWeights * 8), ("stage_convs", ConvWeights * 4),
+                ("output_proj", ConvWeights), ("alibi_slopes", C.c_float * 8)]
 
 
 def _ptr(a):
@@ -354,6 +377,75 @@ class SynthModel:
 # --------------------------------------------------------------------------
 # thin object over the C ABI (one context per process, like the reference)
 # --------------------------------------------------------------------------
+class SynthCodec:
+    """Seeded random-init codec-decoder weights in the form tts_codec_load leaves them
+    (voxtral_tts_codec.c:177-262): transformer matrices BF16-representable fp32 (the checkpoint
+    stores BF16, the loader widens), effective (weight-normed) convolution weights plain fp32,
+    semantic embedding ~N(0, 1), layer scales 0.5 + N(0, 0.1)."""
+
+    CODEC_DIM, CODEC_HIDDEN, EMBED, PATCH = 1024, 4096, 292, 240
+
+    def __init__(self, seed=77, qk_norm=True, layer_scale=True, conv_bias=True):
+        D, Hd = self.CODEC_DIM, self.CODEC_HIDDEN
+        self.seed = seed
+        t = self.t = {}
+
+        def mat(name, shape):
+            # BF16 values widened to fp32: exactly what safetensors_get_f32 returns for a BF16 tensor
+            b = synth_bf16(shape, seed, name, 0.02)
+            return (b.astype(np.uint32) << 16).view(np.float32)
+
+        t["semantic_embedding"] = synth_f32((8192, 256), seed, "codec.semantic_embedding", 0.0, 1.0)
+
+        def conv(name, shape, fan_in, n_bias):
+            t[f"{name}.weight"] = synth_f32(shape, seed, f"{name}.weight", 0.0, 1.0 / np.sqrt(fan_in))
+            t[f"{name}.bias"] = synth_f32(n_bias, seed, f"{name}.bias", 0.0, 0.05) if conv_bias else None
+
+        conv("input_conv", (D, self.EMBED, 3), self.EMBED * 3, D)
+        for s_ in range(3):
+            conv(f"up{s_}", (D, D, 4), D * 2, D)                 # [in_ch, out_ch, kernel]
+        conv("output_proj", (self.PATCH, D, 7), D * 7, self.PATCH)
+        for l in range(8):
+            n = f"codec.layers.{l}"
+            for k, shape in (("wq", (D, D)), ("wk", (D, D)), ("wv", (D, D)), ("wo", (D, D)),
+                             ("w1", (Hd, D)), ("w2", (D, Hd)), ("w3", (Hd, D))):
+                t[f"{n}.{k}"] = mat(f"{n}.{k}", shape)
+            t[f"{n}.attention_norm"] = synth_f32(D, seed, f"{n}.attention_norm", 1.0, 0.02)
+            t[f"{n}.ffn_norm"] = synth_f32(D, seed, f"{n}.ffn_norm", 1.0, 0.02)
+            t[f"{n}.q_norm"] = synth_f32(D, seed, f"{n}.q_norm", 1.0, 0.05) if qk_norm else None
+            t[f"{n}.k_norm"] = synth_f32(D, seed, f"{n}.k_norm", 1.0, 0.05) if qk_norm else None
+            t[f"{n}.attn_scale"] = synth_f32(D, seed, f"{n}.attn_scale", 0.5, 0.1) if layer_scale else None
+            t[f"{n}.ffn_scale"] = synth_f32(D, seed, f"{n}.ffn_scale", 0.5, 0.1) if layer_scale else None
+
+    def struct(self):
+        """A CodecWeights (== tts_codec_t) whose pointers reference this object's arrays."""
+        t, w = self.t, CodecWeights()
+        D = self.CODEC_DIM
+
+        def p(a):
+            return None if a is None else _ptr(a)
+
+        def conv(dst, name, in_ch, out_ch, kernel, stride, transpose):
+            dst.weight, dst.bias = p(t[f"{name}.weight"]), p(t[f"{name}.bias"])
+            dst.in_ch, dst.out_ch, dst.kernel, dst.stride, dst.is_transpose = in_ch, out_ch, kernel, stride, transpose
+
+        w.semantic_embedding = p(t["semantic_embedding"])
+        conv(w.input_conv, "input_conv", self.EMBED, D, 3, 1, 0)
+        for s_ in range(3):
+            conv(w.stage_convs[s_], f"up{s_}", D, D, 4, 2, 1)
+        conv(w.output_proj, "output_proj", D, self.PATCH, 7, 1, 0)
+        windows = (2, 4, 8, 16)                                   # voxtral_tts_codec.c:223
+        for l in range(8):
+            n, L = f"codec.layers.{l}", w.transformers[l]
+            for k in ("wq", "wk", "wv", "wo", "q_norm", "k_norm", "attention_norm", "w1", "w2", "w3", "ffn_norm",
+                      "attn_scale", "ffn_scale"):
+                setattr(L, k, p(t[f"{n}.{k}"]))
+            L.window_size = windows[l // 2]
+        for h in range(8):
+            w.alibi_slopes[h] = float(np.float32(2.0) ** np.float32(-8.0 / 8.0 * (h + 1)))   # voxtral_tts_codec.c:204-205
+        return w
+
+
 class Engine:
     def __init__(self, kv_cache_max=512):
         L = lib()
@@ -394,6 +486,22 @@ class Engine:
         embeds = np.ascontiguousarray(embeds, dtype=np.float32)
         self.L.tts_cuda_llm_prefill(_ptr(embeds), embeds.shape[0], int(start_pos))
         self._ok("tts_cuda_llm_prefill")
+
+    def codec_upload(self, codec):
+        """vb200_codec_upload of a SynthCodec (or anything with .struct())."""
+        w = codec.struct()
+        self._keep.append((codec, w))
+        if self.L.vb200_codec_upload(C.byref(w)) != 0:
+            raise RuntimeError("vb200_codec_upload failed")
+
+    def codec_decode(self, codes):
+        """codes [n_frames, 37] -> (waveform float32 [n_frames * 1920], device ms)."""
+        codes = np.ascontiguousarray(codes, dtype=np.int32).reshape(-1, CODES)
+        out = np.empty(codes.shape[0] * 1920, dtype=np.float32)
+        n = C.c_int(0)
+        if self.L.vb200_codec_decode(_ptr(codes), codes.shape[0], _ptr(out), out.size, C.byref(n)) != 0:
+            raise RuntimeError(f"vb200_codec_decode failed (device status={self.L.vb200_last_status()})")
+        return out[:n.value], self.L.vb200_codec_last_ms()
 
     def upload_stats(self):
         """(seconds spent inside the weight-upload calls, bytes copied host -> device) so far."""

@@ -18,7 +18,7 @@ LIB = os.path.join(LIBDIR, "libvoxtral_b200.so")
 OBJDIR = os.path.join(LIBDIR, "obj")
 
 CU_SOURCES = ["vb_engine.cu", "vb_simple.cu", "vb_model.cu", "vb_prefill.cu", "vb_abi.cu", "vb_noalloc.cu",
-              "vb_tc.cu", "vb_acoustic_tc.cu", "vb_batch.cu", "vb_stream.cu"]
+              "vb_tc.cu", "vb_acoustic_tc.cu", "vb_batch.cu", "vb_stream.cu", "vb_codec.cu"]
 CPP_SOURCES = ["vb_synth.cpp"]
 NVCC = os.environ.get("NVCC", "nvcc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -241,6 +241,12 @@ int vb200_upload_audio_embed(const uint16_t *table_bf16, int rows) {
     return model_upload_audio_embed(table_bf16, rows);
 }
 
+int vb200_codec_upload(const vb200_codec_weights_t *w) { return codec_upload(w); }
+int vb200_codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples) {
+    return codec_decode(codes, n_frames, samples_out, max_samples, n_samples);
+}
+float vb200_codec_last_ms(void) { return codec_last_ms(); }
+
 void vb200_upload_stats(double *seconds, double *bytes) {
     if (seconds) *seconds = model().upload_seconds;
     if (bytes) *bytes = model().upload_bytes;

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "../../include/voxtral_b200.h"
+#include "../../include/voxtral_b200_ext.h"
 #include "vb_engine.cuh"
 
 namespace vb {
@@ -156,6 +157,11 @@ int batch_tiled_decoder(const TcWeight **wqkv, const TcWeight **wo, const TcWeig
 void batch_options_changed();
 void single_path_changed();
 void batch_free_all();
+/* vb_codec.cu */
+void codec_free_all();
+int codec_upload(const vb200_codec_weights_t *w);
+int codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples);
+float codec_last_ms();
 
 int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);
 int utterance_run(int n);

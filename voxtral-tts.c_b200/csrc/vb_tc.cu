@@ -114,15 +114,23 @@ int tc_weight_tiled(TcWeight *w, const uint16_t *d_W, int N, int K, uint16_t *d_
 
 int tc_rows_pad(int M) { return M <= 16 ? 16 : M <= 64 ? 64 : M <= 256 ? 256 : 0; }
 
+/* Any number of rows: beyond 256 the buffer is padded to whole 128-row blocks (row-block kernel). */
+int tc_rows_pad_any(int M) {
+    if (M <= 256) return tc_rows_pad(M);
+    return M <= kTcMaxRows ? (M + 127) / 128 * 128 : 0;
+}
+
 size_t tc_acts_bytes(int rows_pad, int K) { return (size_t)kTcTerms * rows_pad * K * 2; }
 
 int tc_acts(TcActs *a, uint16_t *d_buf, int rows_pad, int K) {
     a->ok = false;
     a->buf = d_buf; a->rows_pad = rows_pad; a->K = K;
-    if ((rows_pad != 16 && rows_pad != 64 && rows_pad != 256) || (K % kTcBlockK) != 0) return -1;
-    if (make_map(&a->map, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, (uint32_t)rows_pad)) return -1;
+    const bool big = rows_pad > 256 && rows_pad <= kTcMaxRows && rows_pad % 128 == 0;
+    if ((rows_pad != 16 && rows_pad != 64 && rows_pad != 256 && !big) || (K % kTcBlockK) != 0) return -1;
+    /* (a TMA box holds at most 256 rows: larger buffers only get the row-block kernel's map) */
+    if (!big && make_map(&a->map, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, (uint32_t)rows_pad)) return -1;
     /* the row-block kernel fetches 128 rows of one term at a time */
-    if (rows_pad == 256 && make_map(&a->map_rows, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, 128u)) return -1;
+    if (rows_pad >= 256 && make_map(&a->map_rows, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, 128u)) return -1;
     a->ok = true;
     return 0;
 }
@@ -827,7 +835,10 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
         if (g.n_tiles == 0 && tpa.push.n_dst == 0 && tpa.wait.n == 0 && !getenv("VB200_TC_ROWS_OLD"))
             return launch_rows(w, a, ka, st);
         return launch_tc<256, 2>(w, a, ka, tpa, st);
-    default: return -1;
+    default:
+        if (a.rows_pad > 256 && a.rows_pad % 128 == 0 && g.n_tiles == 0 && tpa.push.n_dst == 0 && tpa.wait.n == 0)
+            return launch_rows(w, a, ka, st);
+        return -1;
     }
 }
 

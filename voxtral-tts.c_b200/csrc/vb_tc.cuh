@@ -24,6 +24,7 @@ namespace vb {
 constexpr int kTcTileN = 128;     /* weight rows per CTA tile = UMMA M */
 constexpr int kTcBlockK = 64;     /* K elements per pipeline stage: one 128-byte swizzle row */
 constexpr int kTcTerms = 3;       /* BF16 terms per fp32 activation */
+constexpr int kTcMaxRows = 8192;  /* activation rows per launch (row-block kernel) */
 constexpr int kTcMaxSplits = 8;   /* split-K factor limit (partials are summed in fixed order) */
 
 enum TcEpilogue {
@@ -109,6 +110,7 @@ size_t tc_tiled_bytes(int N, int K);
 int tc_acts(TcActs *a, uint16_t *d_buf, int rows_pad, int K);
 size_t tc_acts_bytes(int rows_pad, int K);
 int tc_rows_pad(int M);                            /* 16, 64, 256; 0 when M is too large */
+int tc_rows_pad_any(int M);                        /* same, and whole 128-row blocks beyond 256 rows */
 int tc_pick_splits(int N, int K, int n_sm);
 int tc_prepare_chunks(int K);                      /* column chunks (and ssq entries) per row */
 
