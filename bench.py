@@ -389,6 +389,46 @@ def micro_stream(args):
                       "peak_source": src}))
 
 
+def codec_leg(pkg, eng, codes, cpu_frames):
+    """The codec decoder (vb200_codec_decode) on the utterance's codes: device time, wall time from
+    host codes to host waveform, and the reference's own tts_codec_decode on the host cores on the
+    first `cpu_frames` frames of the same codes (a bounded sample: its cost grows linearly with the
+    frame count)."""
+    codec = pkg.SynthCodec(seed=77)
+    t0 = time.perf_counter()
+    eng.codec_upload(codec)
+    up_s = time.perf_counter() - t0
+    eng.codec_decode(codes)
+    wall, dev = [], []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        pcm, ms = eng.codec_decode(codes)
+        wall.append((time.perf_counter() - t0) * 1e3)
+        dev.append(ms)
+    n = int(codes.shape[0])
+    out = {"frames": n, "audio_s": n / 12.5, "samples": int(pcm.size), "device_ms": min(dev), "wall_ms": min(wall),
+           "upload_s": up_s, "h2d_bytes": int(codes.nbytes), "d2h_bytes": int(pcm.nbytes),
+           "weights": "seeded random-init codec decoder of the real shapes (8 transformer layers of width 1024, "
+                      "4 convolutions)"}
+    if cpu_frames > 0:
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import oracle_bind
+            ref = oracle_bind.load_ref("blas") or oracle_bind.load_ref("noblas")
+            if ref is not None and hasattr(ref.L, "refh_codec_decode"):
+                k = min(cpu_frames, n)
+                t0 = time.perf_counter()
+                want = ref.codec_decode(codec.struct(), codes[:k])
+                cpu_ms = (time.perf_counter() - t0) * 1e3
+                got = pcm[:k * 1920].astype(np.float64)
+                err = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+                out["cpu_reference"] = {"frames": k, "ms": cpu_ms, "ms_per_frame": cpu_ms / k, "kind": ref.kind,
+                                        "rel_l2_gpu_vs_reference": err}
+        except Exception as e:                               # the extra leg never costs the main line
+            out["cpu_reference"] = {"error": f"{type(e).__name__}: {e}"}
+    return out
+
+
 def micro_prefill(args):
     """tts_cuda_llm_prefill alone: `--m` prompt rows (host fp32 rows in, cache rows out), `--reps`
     calls, wall clock per call (the call is synchronous). Uploads the decoder only. The launch
@@ -478,6 +518,7 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="with N > 1 ranks: ONE utterance, the decoder tensor-parallel over the N GPUs (strong scaling) "
                          "instead of one utterance per GPU")
+    ap.add_argument("--no-codec-leg", action="store_true", help="skip the codec-decoder leg")
     ap.add_argument("--no-streaming-leg", action="store_true",
                     help="skip the extra measurement with the decoder step on the persistent streaming kernel")
     ap.add_argument("--utterances", type=int, default=8,
@@ -821,6 +862,13 @@ def main():
             dist.destroy_process_group()
         return
 
+    codec = None
+    if not args.no_codec_leg:
+        try:
+            codec = codec_leg(pkg, eng, np.ascontiguousarray(codes[W:W + K]) if K <= 1024 else codes[W:W + 1024],
+                              24 if world == 1 and not args.no_cpu_baseline else 0)
+        except Exception as e:
+            codec = {"error": f"{type(e).__name__}: {e}"}
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         r = cpu_reference(pkg, model, rows, first, seeds["noise"], 1, 6, args.cpu_budget)
@@ -839,7 +887,7 @@ def main():
             "gpu_launches": K * launches_per_frame, "roofline": roofline, "cpu_baseline": cpu,
             "gpu_reference": gpu_ref, "tp": tp_leg,
             "batched": batched, "streaming_decoder": streaming,
-            "upload": upload,
+            "upload": upload, "codec": codec,
             "utterance": {"prefill_rows": PROMPT_ROWS, "prefill_ms": min(prefill_ms),
                           "first_frame_after_ms": min(prefill_ms) + 1000.0 * (1 if tp else world) / e2e_value,
                           "frames": 212,

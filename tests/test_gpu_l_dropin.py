@@ -69,3 +69,34 @@ def test_stage_entry_points_match_the_reference_stages(pkg, synth_model, oracle,
         for p in (ckpt, prompt_file):
             if os.path.exists(p):
                 os.remove(p)
+
+
+def test_codec_stage_matches_the_reference_codec(pkg, tmp_path_factory):
+    """tts_codec_load + tts_codec_decode of dropin/voxtral_tts_codec_b200.c against the reference's own
+    voxtral_tts_codec.c, both run by oracle/codec_harness.c on the same synthetic safetensors file
+    (weight-normed and plain convolutions, the cluster-usage clamp, BF16 matrices)."""
+    from cases import CODEC_SEED, codec_codes
+    cand, chk = os.path.join(REF_DIR, "codec_run_b200"), os.path.join(REF_DIR, "codec_run_ref")
+    if not (os.path.exists(cand) and os.path.exists(chk)):
+        pytest.skip("oracle/_ref/codec_run_* not built (needs the reference checkout at build time)")
+    d = tmp_path_factory.mktemp("codec")
+    ckpt, codes_file = str(d / "codec.safetensors"), str(d / "codes.i32")
+    outs = [str(d / "ref.f32"), str(d / "b200.f32")]
+    env = dict(os.environ)
+    env["LD_LIBRARY_PATH"] = os.path.join(ROOT, "voxtral-tts.c_b200", "lib") + os.pathsep + env.get("LD_LIBRARY_PATH", "")
+    try:
+        pkg.SynthCodec(seed=CODEC_SEED + 2).write_safetensors(ckpt)
+        n_frames = 12
+        codec_codes(n_frames).tofile(codes_file)
+        for exe, out in ((chk, outs[0]), (cand, outs[1])):
+            r = subprocess.run([exe, ckpt, codes_file, str(n_frames), out], capture_output=True, text=True, timeout=900,
+                               env=env)
+            assert r.returncode == 0 and f"samples {n_frames * 1920}" in r.stdout, (exe, r.stdout[-1000:], r.stderr[-1000:])
+        want, got = np.fromfile(outs[0], dtype=np.float32), np.fromfile(outs[1], dtype=np.float32)
+        assert want.shape == got.shape == (n_frames * 1920,)
+        err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64))
+        assert err < 1e-3, err
+    finally:
+        for p in [ckpt, codes_file] + outs:
+            if os.path.exists(p):
+                os.remove(p)

@@ -417,6 +417,66 @@ class SynthCodec:
             t[f"{n}.attn_scale"] = synth_f32(D, seed, f"{n}.attn_scale", 0.5, 0.1) if layer_scale else None
             t[f"{n}.ffn_scale"] = synth_f32(D, seed, f"{n}.ffn_scale", 0.5, 0.1) if layer_scale else None
 
+    def write_safetensors(self, path):
+        """The codec tensors in checkpoint form, under the names tts_codec_load reads
+        (voxtral_tts_codec.c:177-262): embedding_sum / cluster_usage, the input and the three
+        upsampling convolutions weight-normed (original0 = g, original1 = v), the output
+        convolution plain, transformer matrices BF16, vectors F32. The effective weights a loader
+        derives from this file are NOT the arrays of this object (g and v are fresh draws)."""
+        import json
+        import struct
+        t, seed, D = self.t, self.seed, self.CODEC_DIM
+        out = {}
+        usage = np.abs(synth_f32(8192, seed, "codec.cluster_usage", 1.0, 0.5)).astype(np.float32)
+        usage[:3] = (0.0, 1e-7, 2.0)                                   # the clamp at 1e-5
+        out["audio_tokenizer.quantizer.semantic_codebook.cluster_usage"] = usage
+        # sums chosen so that sum / max(usage, 1e-5) is again ~N(0, 1)
+        out["audio_tokenizer.quantizer.semantic_codebook.embedding_sum"] = (
+            t["semantic_embedding"] * np.maximum(usage, np.float32(1e-5))[:, None]).astype(np.float32)
+
+        def wn(prefix, name, lead):
+            v = t[f"{name}.weight"]
+            out[f"{prefix}.conv.parametrizations.weight.original1"] = v
+            out[f"{prefix}.conv.parametrizations.weight.original0"] = np.abs(
+                synth_f32((lead, 1, 1), seed, f"{prefix}.g", 1.0, 0.2)).astype(np.float32)
+            if t[f"{name}.bias"] is not None:
+                out[f"{prefix}.conv.bias"] = t[f"{name}.bias"]
+
+        B = "audio_tokenizer.decoder_blocks"
+        wn(f"{B}.0", "input_conv", D)
+        for s_ in range(3):
+            wn(f"{B}.{2 + 2 * s_}", f"up{s_}", D)
+        out["audio_tokenizer.output_proj.conv.weight"] = t["output_proj.weight"]
+        if t["output_proj.bias"] is not None:
+            out["audio_tokenizer.output_proj.conv.bias"] = t["output_proj.bias"]
+        names = {"wq": "attention.wq.weight", "wk": "attention.wk.weight", "wv": "attention.wv.weight",
+                 "wo": "attention.wo.weight", "w1": "feed_forward.w1.weight", "w2": "feed_forward.w2.weight",
+                 "w3": "feed_forward.w3.weight", "q_norm": "attention.q_norm.weight", "k_norm": "attention.k_norm.weight",
+                 "attention_norm": "attention_norm.weight", "ffn_norm": "ffn_norm.weight",
+                 "attn_scale": "attention_scale", "ffn_scale": "ffn_scale"}
+        for l in range(8):
+            for k, full in names.items():
+                a = t[f"codec.layers.{l}.{k}"]
+                if a is None:
+                    continue
+                if a.ndim == 2:                                        # back to the BF16 the values came from
+                    a = (a.view(np.uint32) >> 16).astype(np.uint16)
+                out[f"{B}.{1 + 2 * (l // 2)}.layers.{l % 2}.{full}"] = a
+        header, off = {}, 0
+        for name, a in out.items():
+            n = a.size * a.dtype.itemsize
+            header[name] = {"dtype": "BF16" if a.dtype == np.uint16 else "F32", "shape": list(a.shape),
+                            "data_offsets": [off, off + n]}
+            off += n
+        blob = json.dumps(header, separators=(",", ":")).encode()
+        blob += b" " * ((8 - len(blob) % 8) % 8)
+        with open(path, "wb") as f:
+            f.write(struct.pack("<Q", len(blob)))
+            f.write(blob)
+            for a in out.values():
+                np.ascontiguousarray(a).tofile(f)
+        return path
+
     def struct(self):
         """A CodecWeights (== tts_codec_t) whose pointers reference this object's arrays."""
         t, w = self.t, CodecWeights()
