@@ -13,10 +13,14 @@
  * Rows stay row-major [time, channel] throughout (the reference transposes to channel-first
  * around every convolution). The transformer linears run on the tensor-core row-block GEMM
  * (vb_tc.cu) with BF16 weights - exact, because the checkpoint's BF16 values were only widened to
- * fp32 by the loader - and the activations as hi + lo BF16 terms. The convolutions keep their
- * fp32 (weight-normed) weights and run as implicit GEMMs on the fp32 pipes: a convolution is
- * C[t][oc] = bias[oc] + sum over taps and input channels of X[src(t, tap)][ic] * W[oc][tap][ic],
- * and a stride-2 transposed convolution is two such products, one per output parity.
+ * fp32 by the loader - and the activations as hi + lo BF16 terms. A convolution is a GEMM too,
+ *   C[t][oc] = bias[oc] + sum over taps and input channels of X[src(t, tap)][ic] * W[oc][tap][ic],
+ * and a stride-2 transposed convolution is one with both output parities as columns,
+ *   C[m][parity * 1024 + oc] = sum over 2 taps of X[m - tap][ic] * W[ic][oc][parity + 2 tap],
+ * whose row-major result [T][2048] IS the upsampled sequence [2T][1024]. Their (weight-normed)
+ * weights are genuine fp32: they are split into W = hi + lo BF16 matrices (16 mantissa bits,
+ * relative error 4e-6) and the row-block GEMM runs once on each, on the gathered activation
+ * terms, into split-K partial buffers that one reduction sums together with the bias.
  */
 #include "vb_common.cuh"
 #include "vb_model.cuh"
@@ -35,6 +39,7 @@ constexpr int CD = 1024, CH = 4096, CQKV = 3 * CD, CHEADS = 8, CHD = 128;
 constexpr int CEMB = 292, CSEM = 256, CSEM_ROWS = 8192, CPATCH = 240, CLAYERS = 8, CSTAGES = 4;
 constexpr float CEPS = 1e-2f, CQK_EPS = 1e-6f;
 constexpr int CFSQ = 21, CSPECIAL = 2, CCODES = 37;
+constexpr int kConvSplits = 4;      /* K splits per half (hi / lo) of a convolution GEMM */
 
 struct CodecLayer {
     TcWeight wqkv, wo, w13, w2;
@@ -47,9 +52,12 @@ struct Codec {
     bool ready = false;
     std::vector<void *> allocs;          /* weights */
     float *sem = nullptr;
-    float *in_w = nullptr, *in_b = nullptr;          /* [1024][3][292] */
-    float *up_w[3] = {}, *up_b[3] = {};              /* [2 parities][1024][2 taps][1024] */
-    float *out_w = nullptr, *out_b = nullptr;        /* [240][7][1024] */
+    /* convolutions as GEMMs: hi / lo BF16 halves of W[N][Kpad], bias[N] */
+    struct Conv {
+        TcWeight hi, lo;
+        float *bias = nullptr;
+        int N = 0, K = 0, Kpad = 0, Cin = 0, taps = 0, mode = 0, left_pad = 0;
+    } in_conv, up_conv[3], out_conv;
     CodecLayer L[CLAYERS];
     float *d_slopes = nullptr;
     /* activations, sized for cap_rows = 8 * frames */
@@ -58,8 +66,9 @@ struct Codec {
     int *codes = nullptr;
     float *emb = nullptr, *x = nullptr, *x2 = nullptr, *y = nullptr, *qkv = nullptr, *attn = nullptr, *ssq = nullptr;
     float *pcm = nullptr;
-    uint16_t *tD = nullptr, *tH = nullptr;
-    TcActs aD, aH;
+    uint16_t *tD = nullptr, *tH = nullptr, *tC = nullptr;
+    float *part = nullptr;
+    TcActs aD, aH, aIn, aUp, aOut;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     float last_ms = 0.0f;
 };
@@ -135,82 +144,66 @@ __global__ void codec_embed_kernel(float *emb, const int *codes, const float *se
     }
 }
 
-/* Implicit GEMM on the fp32 pipes:
- *   C[out_row(m)][n] = bias[n] + sum_tap sum_ic X[src(m, tap)][ic] * W[n][tap * Cin + ic]
+/* The A operand of a convolution GEMM: terms[m][tap * Cin + ic] = hi / lo BF16 of X[src(m, tap)][ic]
+ * (columns from taps * Cin up to Kpad are zero).
  * MODE 0, causal convolution with the reference's reflect rule (voxtral_tts_kernels.c:246-262):
- *   src = m + tap - left_pad; src < 0 -> -src; src >= T -> 2T - 2 - src; outside [0, T) -> 0;
- *   out_row = m.
- * MODE 1, one output parity (blockIdx.z) of a stride-2 transposed convolution
- *   (voxtral_tts_kernels.c:272-327; kernel 4: no left trim, the last two raw outputs dropped):
- *   src = m - tap (>= 0), out_row = 2 m + parity, W advanced by parity * N * taps * Cin.
- * 64 x 64 output tile per CTA, 16-wide k steps, 256 threads x (4 x 4) outputs. */
-template <int MODE>
-__global__ void __launch_bounds__(256)
-codec_conv_kernel(float *C, int ldc, const float *X, int ldx, const float *W, const float *bias, int T, int N, int Cin,
-                  int taps, int left_pad) {
-    __shared__ float As[16][64 + 4];
-    __shared__ float Bs[16][64 + 4];
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    const int K = taps * Cin;
-    const float *Wp = W + (MODE == 1 ? (size_t)blockIdx.z * N * K : 0);
-    float acc[4][4] = {};
-    for (int k0 = 0; k0 < K; k0 += 16) {
-        /* 64 x 16 elements of each operand, 4 per thread: thread -> (row = tid / 4 .. , 4 k's) */
-        {
-            const int r = tid >> 2, kq = (tid & 3) * 4;
-            const int m = m0 + r;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int kk = k0 + kq + i;
-                float a = 0.0f, b = 0.0f;
-                if (kk < K) {
-                    const int tap = kk / Cin, ic = kk - tap * Cin;
-                    if (m < T) {
-                        int src;
-                        bool ok;
-                        if (MODE == 0) {
-                            src = m + tap - left_pad;
-                            if (src < 0) src = -src;
-                            else if (src >= T) src = 2 * T - 2 - src;
-                            ok = src >= 0 && src < T;
-                        } else {
-                            src = m - tap;
-                            ok = src >= 0;
-                        }
-                        if (ok) a = X[(size_t)src * ldx + ic];
-                    }
-                    const int n = n0 + r;
-                    if (n < N) b = __ldg(Wp + (size_t)n * K + kk);
-                }
-                As[kq + i][r] = a;
-                Bs[kq + i][r] = b;
-            }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int kk = 0; kk < 16; kk++) {
-            const float4 a4 = *reinterpret_cast<const float4 *>(&As[kk][ty * 4]);
-            const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4]);
-            const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] += a[i] * b[j];
-        }
-        __syncthreads();
-    }
+ *   src = m + tap - left_pad; src < 0 -> -src; src >= T -> 2T - 2 - src; outside [0, T) -> 0.
+ * MODE 1, stride-2 transposed convolution, kernel 4 (voxtral_tts_kernels.c:272-327: no left
+ *   trim, the last two raw outputs dropped): src = m - tap, zero when negative.
+ * grid = (Kpad / 1024 rounded up, T), 256 threads x 4 columns. */
+__global__ void codec_gather_kernel(uint16_t *buf, int rows_pad, int Kpad, const float *X, int ldx, int T, int Cin,
+                                    int taps, int mode, int left_pad) {
+    const int m = blockIdx.y, k = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (k >= Kpad) return;
+    float e[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const int m = m0 + ty * 4 + i;
-        if (m >= T) continue;
-        const size_t row = MODE == 1 ? (size_t)(2 * m + blockIdx.z) : (size_t)m;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int n = n0 + tx * 4 + j;
-            if (n < N) C[row * ldc + n] = acc[i][j] + (bias ? __ldg(bias + n) : 0.0f);
+        const int kk = k + i;
+        float v = 0.0f;
+        if (kk < taps * Cin) {
+            const int tap = kk / Cin, ic = kk - tap * Cin;
+            int src;
+            bool ok;
+            if (mode == 0) {
+                src = m + tap - left_pad;
+                if (src < 0) src = -src;
+                else if (src >= T) src = 2 * T - 2 - src;
+                ok = src >= 0 && src < T;
+            } else {
+                src = m - tap;
+                ok = src >= 0;
+            }
+            if (ok) v = X[(size_t)src * ldx + ic];
         }
+        e[i] = v;
     }
+    uint16_t t0[4], t1[4], t2[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) vb_split3(e[i], t0[i], t1[i], t2[i]);
+    const size_t o = (size_t)m * Kpad + k, term = (size_t)rows_pad * Kpad;
+    *reinterpret_cast<uint2 *>(buf + o) = make_uint2(t0[0] | ((uint32_t)t0[1] << 16), t0[2] | ((uint32_t)t0[3] << 16));
+    *reinterpret_cast<uint2 *>(buf + term + o) = make_uint2(t1[0] | ((uint32_t)t1[1] << 16), t1[2] | ((uint32_t)t1[3] << 16));
+    *reinterpret_cast<uint2 *>(buf + 2 * term + o) = make_uint2(t2[0] | ((uint32_t)t2[1] << 16), t2[2] | ((uint32_t)t2[3] << 16));
+}
+
+/* W[N][K] fp32 -> hi[N][Kpad], lo[N][Kpad] BF16 with W = hi + lo up to 2^-17 (hi truncated, lo the
+ * rounded remainder), zero beyond K. */
+__global__ void split_w_kernel(uint16_t *hi, uint16_t *lo, const float *W, int N, int K, int Kpad) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)N * Kpad) return;
+    const int n = (int)(i / Kpad), k = (int)(i % Kpad);
+    uint16_t h = 0, l = 0;
+    if (k < K) {
+        const float w = W[(size_t)n * K + k];
+        const uint32_t u = __float_as_uint(w) & 0xffff0000u;
+        h = (uint16_t)(u >> 16);
+        const float r = w - __uint_as_float(u);
+        uint32_t ru = __float_as_uint(r);
+        ru += 0x7fffu + ((ru >> 16) & 1u);                     /* round to nearest even */
+        l = (uint16_t)(ru >> 16);
+    }
+    hi[i] = h;
+    lo[i] = l;
 }
 
 /* Rows -> BF16 terms for the next GEMM, with the residual update folded in:
@@ -377,7 +370,21 @@ int ensure_buffers(int frames) {
     rc |= c_alloc((void **)&c.pcm, sizeof(float) * (size_t)rows * CPATCH, &c.act_allocs);
     rc |= c_alloc((void **)&c.tD, tc_acts_bytes(rp, CD), &c.act_allocs);
     rc |= c_alloc((void **)&c.tH, tc_acts_bytes(rp, CH), &c.act_allocs);
+    /* convolution operands: one buffer, laid out per convolution (every term is rewritten by the
+     * gather before each use); split-K partials of the largest convolution GEMM */
+    const int rp_in = tc_rows_pad_any(frames), rp_up = tc_rows_pad_any(4 * frames);
+    size_t conv_bytes = tc_acts_bytes(rp, c.out_conv.Kpad);
+    if (tc_acts_bytes(rp_up, c.up_conv[0].Kpad) > conv_bytes) conv_bytes = tc_acts_bytes(rp_up, c.up_conv[0].Kpad);
+    if (tc_acts_bytes(rp_in, c.in_conv.Kpad) > conv_bytes) conv_bytes = tc_acts_bytes(rp_in, c.in_conv.Kpad);
+    rc |= c_alloc((void **)&c.tC, conv_bytes, &c.act_allocs);
+    rc |= c_alloc((void **)&c.part, sizeof(float) * (size_t)2 * kConvSplits * 4 * frames * 2 * CD, &c.act_allocs);
     if (rc) { c_free(&c.act_allocs); return -1; }
+    cudaMemset(c.tC, 0, conv_bytes);
+    if (tc_acts(&c.aIn, c.tC, rp_in, c.in_conv.Kpad) || tc_acts(&c.aUp, c.tC, rp_up, c.up_conv[0].Kpad) ||
+        tc_acts(&c.aOut, c.tC, rp, c.out_conv.Kpad)) {
+        c_free(&c.act_allocs);
+        return -1;
+    }
     /* rows of the padding are multiplied like any other (their results are never stored):
      * keep them finite */
     cudaMemset(c.tD, 0, tc_acts_bytes(rp, CD));
@@ -421,14 +428,64 @@ int layer_forward(const CodecLayer &L, int rows, const float *y_prev, const floa
     return 0;   /* the caller folds x += y * ffn_scale into the next step */
 }
 
-int conv_reorder(float **dst, const vb200_conv_t &cv, bool transposed, float *stage, std::vector<void *> *owner,
-                 cudaStream_t st) {
-    const size_t n = (size_t)cv.in_ch * cv.out_ch * cv.kernel;
-    if (!cv.weight || c_alloc((void **)dst, n * 4, owner)) return -1;
-    if (cudaMemcpyAsync(stage, cv.weight, n * 4, cudaMemcpyHostToDevice, st) != cudaSuccess) return -1;
-    if (transposed) convt_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(*dst, stage, cv.in_ch, cv.out_ch, cv.kernel);
-    else conv_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(*dst, stage, cv.out_ch, cv.in_ch, cv.kernel);
-    return cudaStreamSynchronize(st) == cudaSuccess ? 0 : -1;
+/* One convolution made ready as a GEMM: weights reordered to [N][taps * Cin] (a transposed
+ * convolution: both parities stacked, N = 2 * out_ch, 2 taps each), split into hi / lo BF16
+ * matrices and tiled; bias (repeated per parity). */
+int conv_setup(Codec::Conv *cv, const vb200_conv_t &w, float *stage, std::vector<void *> *owner, cudaStream_t st) {
+    const bool tr = w.is_transpose != 0;
+    const size_t n = (size_t)w.in_ch * w.out_ch * w.kernel;
+    cv->Cin = w.in_ch;
+    cv->taps = tr ? w.kernel / 2 : w.kernel;
+    cv->N = tr ? 2 * w.out_ch : w.out_ch;
+    cv->K = cv->taps * w.in_ch;
+    cv->Kpad = (cv->K + 63) / 64 * 64;
+    cv->mode = tr ? 1 : 0;
+    cv->left_pad = tr ? 0 : w.kernel - w.stride;
+    float *ordered = stage + n;                                  /* second half of the staging buffer */
+    uint16_t *hi = nullptr, *lo = nullptr, *thi = nullptr, *tlo = nullptr;
+    const size_t nk = (size_t)cv->N * cv->Kpad;
+    int rc = 0;
+    if (!w.weight || cudaMemcpyAsync(stage, w.weight, n * 4, cudaMemcpyHostToDevice, st) != cudaSuccess) return -1;
+    if (tr) convt_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ordered, stage, w.in_ch, w.out_ch, w.kernel);
+    else conv_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ordered, stage, w.out_ch, w.in_ch, w.kernel);
+    if (cudaMalloc((void **)&hi, nk * 2) != cudaSuccess || cudaMalloc((void **)&lo, nk * 2) != cudaSuccess) rc = -1;
+    if (!rc) split_w_kernel<<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(hi, lo, ordered, cv->N, cv->K, cv->Kpad);
+    if (!rc && (c_alloc((void **)&thi, tc_tiled_bytes(cv->N, cv->Kpad), owner) ||
+                c_alloc((void **)&tlo, tc_tiled_bytes(cv->N, cv->Kpad), owner)))
+        rc = -1;
+    if (!rc && (tc_weight_tiled(&cv->hi, hi, cv->N, cv->Kpad, thi, st) || tc_weight_tiled(&cv->lo, lo, cv->N, cv->Kpad, tlo, st)))
+        rc = -1;
+    if (cudaStreamSynchronize(st) != cudaSuccess) rc = -1;
+    cudaFree(hi);
+    cudaFree(lo);
+    if (!rc && w.bias) {
+        if (c_alloc((void **)&cv->bias, sizeof(float) * cv->N, owner)) return -1;
+        for (int p = 0; p < (tr ? 2 : 1) && !rc; p++)
+            if (cudaMemcpy(cv->bias + (size_t)p * w.out_ch, w.bias, sizeof(float) * w.out_ch, cudaMemcpyHostToDevice) != cudaSuccess)
+                rc = -1;
+    }
+    return rc;
+}
+
+/* Runs one convolution: gather -> GEMM on the hi and on the lo matrix (split-K partials) -> sum +
+ * bias into out [T][N]. */
+int conv_run(const Codec::Conv &cv, const TcActs &acts, const float *X, int ldx, int T, float *out, cudaStream_t st) {
+    Codec &c = g_codec;
+    codec_gather_kernel<<<dim3((cv.Kpad + 1023) / 1024, T), 256, 0, st>>>(acts.buf, acts.rows_pad, cv.Kpad, X, ldx, T, cv.Cin,
+                                                                          cv.taps, cv.mode, cv.left_pad);
+    const int pairs = ((cv.N + kTcTileN - 1) / kTcTileN + 1) / 2, blocks = (T + 127) / 128;
+    int splits = model().sm_count / (pairs * blocks);
+    if (splits > kConvSplits) splits = kConvSplits;
+    if (splits > cv.Kpad / kTcBlockK) splits = cv.Kpad / kTcBlockK;
+    if (splits < 1) splits = 1;
+    TcGemm g;
+    g.M = T; g.splits = splits; g.epi = TC_EPI_PARTIAL; g.ld_out = cv.N; g.status = &model().d_out->status;
+    g.out = c.part;
+    if (tc_gemm(cv.hi, acts, g, st)) return -1;
+    g.out = c.part + (size_t)splits * T * cv.N;
+    if (tc_gemm(cv.lo, acts, g, st)) return -1;
+    tc_reduce(out, c.part, 2 * splits, (size_t)T * cv.N, (size_t)T * cv.N, cv.bias, cv.N, st);
+    return 0;
 }
 
 } // namespace
@@ -476,14 +533,9 @@ int codec_upload(const vb200_codec_weights_t *w) {
     cudaMemset(inexact, 0, sizeof(unsigned));
     int rc = 0;
     rc |= up_f32(&c.sem, w->semantic_embedding, (size_t)CSEM_ROWS * CSEM, &c.allocs);
-    rc |= conv_reorder(&c.in_w, ic, false, stage, &c.allocs, st);
-    rc |= up_f32(&c.in_b, ic.bias, CD, &c.allocs);
-    rc |= conv_reorder(&c.out_w, oc, false, stage, &c.allocs, st);
-    rc |= up_f32(&c.out_b, oc.bias, CPATCH, &c.allocs);
-    for (int s = 0; s < CSTAGES - 1 && !rc; s++) {
-        rc |= conv_reorder(&c.up_w[s], w->stage_convs[s], true, stage, &c.allocs, st);
-        rc |= up_f32(&c.up_b[s], w->stage_convs[s].bias, CD, &c.allocs);
-    }
+    rc |= conv_setup(&c.in_conv, ic, stage, &c.allocs, st);
+    rc |= conv_setup(&c.out_conv, oc, stage, &c.allocs, st);
+    for (int s = 0; s < CSTAGES - 1 && !rc; s++) rc |= conv_setup(&c.up_conv[s], w->stage_convs[s], stage, &c.allocs, st);
     for (int l = 0; l < CLAYERS && !rc; l++) {
         const vb200_codec_layer_t &L = w->transformers[l];
         CodecLayer &d = c.L[l];
@@ -542,8 +594,7 @@ int codec_decode(const int *codes, int n_frames, float *samples_out, int max_sam
     cudaEventRecord(c.e0, st);
     codec_embed_kernel<<<n_frames, 320, 0, st>>>(c.emb, c.codes, c.sem);
     int rows = n_frames;
-    codec_conv_kernel<0><<<dim3(CD / 64, (rows + 63) / 64, 1), 256, 0, st>>>(c.x, CD, c.emb, CEMB, c.in_w, c.in_b, rows, CD,
-                                                                         CEMB, 3, 2);
+    if (conv_run(c.in_conv, c.aIn, c.emb, CEMB, rows, c.x, st)) return -1;
     int l = 0;
     for (int stage = 0; stage < CSTAGES; stage++) {
         const float *y_prev = nullptr, *sc_prev = nullptr;
@@ -556,14 +607,13 @@ int codec_decode(const int *codes, int n_frames, float *samples_out, int max_sam
         codec_prepare_kernel<<<dim3(1, rows), 256, 0, st>>>(nullptr, c.rows_pad, CD, c.x, y_prev, sc_prev, c.x, nullptr,
                                                             nullptr);
         if (stage < CSTAGES - 1) {
-            codec_conv_kernel<1><<<dim3(CD / 64, (rows + 63) / 64, 2), 256, 0, st>>>(c.x2, CD, c.x, CD, c.up_w[stage],
-                                                                                 c.up_b[stage], rows, CD, CD, 2, 0);
+            /* [rows][2 x 1024] row-major = [2 rows][1024] */
+            if (conv_run(c.up_conv[stage], c.aUp, c.x, CD, rows, c.x2, st)) return -1;
             float *t = c.x; c.x = c.x2; c.x2 = t;
             rows *= 2;
         }
     }
-    codec_conv_kernel<0><<<dim3((CPATCH + 63) / 64, (rows + 63) / 64, 1), 256, 0, st>>>(c.pcm, CPATCH, c.x, CD, c.out_w, c.out_b,
-                                                                                    rows, CPATCH, CD, 7, 6);
+    if (conv_run(c.out_conv, c.aOut, c.x, CD, rows, c.pcm, st)) return -1;
     cudaEventRecord(c.e1, st);
     int status = 0;
     if (cudaMemcpyAsync(samples_out, c.pcm, sizeof(float) * (size_t)total, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
