@@ -58,7 +58,7 @@ LINEAR_SHAPES = [
     # the row counts of the other tensor-core tiles: 48 (eight utterances' acoustic rows, 64-row
     # tile), 100 and 256 (prefill, 256-row tile), and 257+ (two row blocks)
     (48, 3072, 6144), (48, 9216, 3072), (100, 3072, 1024), (256, 3072, 6144), (256, 4096, 3072),
-    (256, 9216, 3072), (300, 3072, 256),
+    (256, 9216, 3072), (300, 3072, 256), (700, 1024, 3072), (1000, 3072, 500),
     # K > 4096 with many rows per CTA on the streaming engine (cross-pass accumulators)
     (8, 9224, 4000),
 ]

@@ -193,3 +193,19 @@ def test_reference_test_kernels_shapes(pkg, oracle, ref_noblas):
         o_ref = np.zeros(4096, dtype=np.float32)
         ref_noblas.L.tts_causal_attention(_p(o_ref), _p(q), _p(k), _p(v), 1, sk, 32, 8, 128, scale, 0, sk - 1)
         assert np.array_equal(oracle.attention_causal(q, k, v, 32, 8, 128, scale, sk - 1)[0], o_ref), sk
+
+
+def test_codec_fixture_is_the_reference_decoder_output(ref_noblas):
+    """tests/golden/codec_frames.npz (what the GPU codec tests compare with when oracle/_ref is absent)
+    is reproduced by the reference's tts_codec_decode (voxtral_tts_codec.c:389-510) on the seeded
+    synthetic codec weights."""
+    import os
+    from cases import CODEC_GOLDEN_FRAMES, CODEC_SEED, codec_codes
+    from conftest import load_package
+    if not hasattr(ref_noblas.L, "refh_codec_decode"):
+        pytest.skip("oracle/_ref was built without the codec")
+    pkg = load_package()
+    want = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "codec_frames.npz"))["pcm"]
+    got = ref_noblas.codec_decode(pkg.SynthCodec(seed=CODEC_SEED).struct(), codec_codes(CODEC_GOLDEN_FRAMES))
+    assert got.shape == want.shape
+    assert np.array_equal(got, want)

@@ -480,6 +480,7 @@ class SynthCodec:
     def struct(self):
         """A CodecWeights (== tts_codec_t) whose pointers reference this object's arrays."""
         t, w = self.t, CodecWeights()
+        w._owner = self                                           # the arrays live as long as the struct
         D = self.CODEC_DIM
 
         def p(a):

@@ -925,20 +925,37 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
         linear_generic(d_y, d_x, d_W, nullptr, M, K, N, m.st);
         return 0;
     }
-    /* Two or more rows: the tensor-core GEMM (fp32 rows as three BF16 terms, vb_tc.cu). */
+    /* Two or more rows: the tensor-core GEMMs (fp32 rows as BF16 terms, vb_tc.cu), all rows of a
+     * block of up to kTcMaxRows in one launch. The term and split-K buffers are kept between
+     * calls and only ever grow; everything is ordered by the stream. */
     if (tc_rows && tc_init() == 0) {
         TcWeight w;
         if (tc_weight(&w, d_W, N, K) == 0) {
             int rc = 0;
-            for (int r = 0; r < M && !rc; r += 256) {
-                const int rows = (M - r < 256) ? M - r : 256;
-                const int rp = tc_rows_pad(rows);
-                const int splits = tc_pick_splits(N, K, m.sm_count);
-                void *buf = nullptr, *part = nullptr;
+            for (int r = 0; r < M && !rc; r += kTcMaxRows) {
+                const int rows = (M - r < kTcMaxRows) ? M - r : kTcMaxRows;
+                const int rp = tc_rows_pad_any(rows);
+                int splits = tc_pick_splits(N, K, m.sm_count);
+                if (rows > 256) {   /* many row blocks fill the GPU by themselves */
+                    const int ctas = ((N + 255) / 256) * ((rows + 127) / 128);
+                    splits = m.sm_count / ctas < 1 ? 1 : (m.sm_count / ctas < splits ? m.sm_count / ctas : splits);
+                }
+                const size_t need_t = tc_acts_bytes(rp, K), need_p = splits > 1 ? sizeof(float) * (size_t)splits * rows * N : 0;
+                if (need_t > m.lin_terms_cap) {
+                    if (m.lin_terms) dev_release(m.lin_terms);
+                    m.lin_terms = nullptr; m.lin_terms_cap = 0;
+                    if (dev_alloc((unsigned char **)&m.lin_terms, need_t)) return -1;
+                    m.lin_terms_cap = need_t;
+                }
+                if (need_p > m.lin_part_cap) {
+                    if (m.lin_part) dev_release(m.lin_part);
+                    m.lin_part = nullptr; m.lin_part_cap = 0;
+                    if (dev_alloc((unsigned char **)&m.lin_part, need_p)) return -1;
+                    m.lin_part_cap = need_p;
+                }
                 TcActs a;
-                if (cudaMalloc(&buf, tc_acts_bytes(rp, K)) != cudaSuccess) return -1;
-                cudaMemsetAsync(buf, 0, tc_acts_bytes(rp, K), m.st);
-                if (tc_acts(&a, (uint16_t *)buf, rp, K)) rc = -1;
+                cudaMemsetAsync(m.lin_terms, 0, need_t, m.st);       /* padding rows stay finite */
+                if (tc_acts(&a, (uint16_t *)m.lin_terms, rp, K)) rc = -1;
                 if (!rc) tc_prepare(a, d_x + (size_t)r * K, K, rows, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, m.st);
                 TcGemm g;
                 g.M = rows; g.status = &m.d_out->status; g.ld_out = N; g.splits = splits;
@@ -946,16 +963,13 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
                     g.epi = TC_EPI_STORE; g.out = d_y + (size_t)r * N;
                     rc = tc_gemm(w, a, g, m.st);
                 } else if (!rc) {
-                    if (cudaMalloc(&part, sizeof(float) * (size_t)splits * rows * N) != cudaSuccess) rc = -1;
-                    g.epi = TC_EPI_PARTIAL; g.out = (float *)part;
-                    if (!rc) rc = tc_gemm(w, a, g, m.st);
-                    if (!rc) tc_reduce(d_y + (size_t)r * N, (const float *)part, splits, (size_t)rows * N,
+                    g.epi = TC_EPI_PARTIAL; g.out = (float *)m.lin_part;
+                    rc = tc_gemm(w, a, g, m.st);
+                    if (!rc) tc_reduce(d_y + (size_t)r * N, (const float *)m.lin_part, splits, (size_t)rows * N,
                                        (size_t)rows * N, nullptr, N, m.st);
                 }
-                cudaStreamSynchronize(m.st);
-                cudaFree(buf);
-                cudaFree(part);
             }
+            if (cudaStreamSynchronize(m.st) != cudaSuccess) rc = -1;
             return rc;
         }
     }

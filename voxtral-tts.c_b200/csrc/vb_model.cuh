@@ -53,6 +53,8 @@ struct Model {
     int device = 0, n_cta = 0, sm_count = 0;
     cudaStream_t st = nullptr;
     std::vector<void *> allocs;
+    unsigned char *lin_terms = nullptr, *lin_part = nullptr;   /* scratch of tts_cuda_linear_bf16 on many rows (grow-only) */
+    size_t lin_terms_cap = 0, lin_part_cap = 0;
     double upload_seconds = 0.0, upload_bytes = 0.0;   /* host -> device weight copies so far */
 
     LayerDev dec[VB200_DEC_LAYERS], ac[VB200_AC_LAYERS];
