@@ -9,6 +9,7 @@
  * on the streaming engine, eight rows at a time. Also here: the prompt assembled on
  * the device from token ids and BF16 voice rows (voxtral_tts.c:230-272).
  */
+#include "vb_common.cuh"
 #include "vb_model.cuh"
 #include "vb_simple.cuh"
 #include "vb_tc.cuh"
@@ -75,101 +76,202 @@ __global__ void pf_qkv_finish_kernel(float *qkv, const float *part, int n_part, 
 }
 
 /* Causal attention of a block of prompt rows over the cache prefix (tts_causal_attention,
- * voxtral_tts_kernels.c:403-465), head_dim 128, four query heads per KV head. A CTA owns one KV
- * head and 8 query rows: 8 rows x 4 heads = 32 queries, each spread over 4 threads that own
- * every fourth 16-byte piece of the head dimension. K and V rows are staged in shared memory 32
- * keys at a time, once per KV head, and every thread walks the staged keys in steps of eight:
- * eight partial dot products, two shuffles each to join the four pieces, one running-maximum
- * update per eight keys. Row blocks are issued heaviest (latest rows) first. */
-constexpr int kPaRows = 8, kPaKeys = 32, kPaThreads = kPaRows * 4 * 4;
+ * voxtral_tts_kernels.c:403-465) on the warp-level tensor cores; head_dim 128, four query heads
+ * per KV head. A CTA owns one KV head and 16 query rows; warp w serves query head 4 g + w, so the
+ * K and V rows are staged in shared memory once per KV head, 32 keys at a time.
+ *
+ * fp32 accuracy from BF16 MMAs: every fp32 operand is split into hi + lo BF16 halves and a
+ * product a.b is taken as a_hi.b_hi + a_hi.b_lo + a_lo.b_hi (the dropped lo.lo term is 2^-16 of
+ * the product). Per 32-key tile a warp issues, with mma.sync.m16n8k16:
+ *   S[16 x 32]  = Q[16 x 128] . K^T     4 key tiles x 8 k-steps x 3 products
+ *   O[16 x 128] += P[16 x 32] . V      16 dim tiles x 2 k-steps x 3 products
+ * Q lives in registers as A fragments (scaled by 1/sqrt(128) before the split); K rows [key][dim]
+ * are the "column-major" B operand of Q.K^T (ldmatrix), V rows [key][dim] the row-major B operand
+ * of P.V (ldmatrix.trans); both sit in shared memory as BF16 with the 16-byte chunks of a row
+ * XOR-swizzled by the key index. The running maximum / sum update is the usual one per tile;
+ * S's accumulator fragments become P's A fragments without leaving registers. Row blocks are
+ * issued heaviest (latest rows) first. */
+constexpr int kFaRows = 16, kFaKeys = 32, kFaThreads = 128;
 
-__global__ void __launch_bounds__(kPaThreads)
+VB_DEVINL void fa_split(float v, uint32_t &hi, uint32_t &lo) {
+    uint16_t a, b, c;
+    vb_split3(v, a, b, c);
+    hi = a;
+    lo = b;
+}
+VB_DEVINL void fa_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+VB_DEVINL void fa_ldsm(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+VB_DEVINL void fa_ldsm_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+/* byte offset of 16-byte chunk `chunk` (0..15) of key row `key` in a [32][128] BF16 tile */
+VB_DEVINL uint32_t fa_off(int key, int chunk) { return (uint32_t)(key * 256 + (((chunk & 8) | ((chunk ^ key) & 7)) << 4)); }
+
+__global__ void __launch_bounds__(kFaThreads)
 pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc, int M, int start_pos, int ldq,
                     int ldkv, int ldo, float scale) {
-    __shared__ float4 Ks[kPaKeys * 32];
-    __shared__ float4 Vs[kPaKeys * 32];
-    const int g = blockIdx.y, r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kPaRows;
-    const int tid = threadIdx.x, sl = tid & 3, qi = tid >> 2;
-    const int hl = qi & 3, rl = qi >> 2;
-    const int row = r0 + rl, h = g * 4 + hl;
-    const bool valid = row < M;
-    const int limit = valid ? start_pos + row : 0;               /* last key this query sees */
-    const int rows_here = M - r0 < kPaRows ? M - r0 : kPaRows;
-    const int n_keys = start_pos + r0 + rows_here;               /* keys 0 .. n_keys-1 serve this block */
-    float qv[32], o[32];
+    __shared__ __align__(128) unsigned char Kh[kFaKeys * 256], Kl[kFaKeys * 256], Vh[kFaKeys * 256], Vl[kFaKeys * 256];
+    const int g = blockIdx.y, r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kFaRows;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+    const int h = g * 4 + warp;
+    const int rowA = r0 + gq, rowB = rowA + 8;
+    const bool validA = rowA < M, validB = rowB < M;
+    const int limA = validA ? start_pos + rowA : 0, limB = validB ? start_pos + rowB : 0;   /* last key a row sees */
+    const int rows_here = M - r0 < kFaRows ? M - r0 : kFaRows;
+    const int n_keys = start_pos + r0 + rows_here;
+
+    /* Q as A fragments: a0 (row A, k 2t..), a1 (row B, k 2t..), a2 (row A, k 8+2t..), a3 (row B, k 8+2t..) */
+    uint32_t qh[8][4], ql[8][4];
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid) t = *reinterpret_cast<const float4 *>(q + (size_t)row * ldq + h * VB200_HEAD_DIM + 4 * (sl + 4 * j));
-        qv[4 * j] = t.x * scale; qv[4 * j + 1] = t.y * scale; qv[4 * j + 2] = t.z * scale; qv[4 * j + 3] = t.w * scale;
-        o[4 * j] = o[4 * j + 1] = o[4 * j + 2] = o[4 * j + 3] = 0.0f;
+    for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                const int row = rr ? rowB : rowA;
+                float2 v = make_float2(0.f, 0.f);
+                if (rr ? validB : validA)
+                    v = *reinterpret_cast<const float2 *>(q + (size_t)row * ldq + h * VB200_HEAD_DIM + ks * 16 + half * 8 + 2 * tq);
+                uint32_t h0, l0, h1, l1;
+                fa_split(v.x * scale, h0, l0);
+                fa_split(v.y * scale, h1, l1);
+                qh[ks][half * 2 + rr] = h0 | (h1 << 16);
+                ql[ks][half * 2 + rr] = l0 | (l1 << 16);
+            }
+        }
     }
-    float mx = -1e30f, den = 0.0f;
-    for (int k0 = 0; k0 < n_keys; k0 += kPaKeys) {
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float mA = -1e30f, mB = -1e30f, lA = 0.0f, lB = 0.0f;
+    const uint32_t sKh = vb_smem_u32(Kh), sKl = vb_smem_u32(Kl), sVh = vb_smem_u32(Vh), sVl = vb_smem_u32(Vl);
+    const int mat = lane >> 3, mr = lane & 7;
+
+    for (int k0 = 0; k0 < n_keys; k0 += kFaKeys) {
         __syncthreads();
-        for (int i = tid; i < kPaKeys * 32; i += kPaThreads) {
-            const int kk = k0 + (i >> 5), f = i & 31;
+        /* stage 32 keys of K and V: fp32 -> hi / lo BF16, 4 values (8 bytes) per piece */
+        for (int i = tid; i < kFaKeys * 32; i += kFaThreads) {
+            const int key = i >> 5, f = i & 31, kk = k0 + key;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
             if (kk < n_keys) {
                 a = __ldg(reinterpret_cast<const float4 *>(kc + (size_t)kk * ldkv + g * VB200_HEAD_DIM) + f);
                 b = __ldg(reinterpret_cast<const float4 *>(vc + (size_t)kk * ldkv + g * VB200_HEAD_DIM) + f);
             }
-            Ks[i] = a;
-            Vs[i] = b;
+            const float ea[4] = {a.x, a.y, a.z, a.w}, eb[4] = {b.x, b.y, b.z, b.w};
+            uint32_t ah[4], al[4], bh[4], bl[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) { fa_split(ea[j], ah[j], al[j]); fa_split(eb[j], bh[j], bl[j]); }
+            const uint32_t off = fa_off(key, f >> 1) + (uint32_t)(f & 1) * 8u;
+            *reinterpret_cast<uint2 *>(Kh + off) = make_uint2(ah[0] | (ah[1] << 16), ah[2] | (ah[3] << 16));
+            *reinterpret_cast<uint2 *>(Kl + off) = make_uint2(al[0] | (al[1] << 16), al[2] | (al[3] << 16));
+            *reinterpret_cast<uint2 *>(Vh + off) = make_uint2(bh[0] | (bh[1] << 16), bh[2] | (bh[3] << 16));
+            *reinterpret_cast<uint2 *>(Vl + off) = make_uint2(bl[0] | (bl[1] << 16), bl[2] | (bl[3] << 16));
         }
         __syncthreads();
-        const int kt = n_keys - k0 < kPaKeys ? n_keys - k0 : kPaKeys;
-        for (int c = 0; c < kt; c += 8) {
-            float sc[8];
+
+        /* S = Q . K^T for 4 tiles of 8 keys */
+        float s[4][4];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                float d = 0.0f;
+        for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float4 kv = Ks[(c + u) * 32 + sl + 4 * j];
-                    d += qv[4 * j] * kv.x + qv[4 * j + 1] * kv.y + qv[4 * j + 2] * kv.z + qv[4 * j + 3] * kv.w;
-                }
-                sc[u] = d;
+        for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+            for (int np = 0; np < 2; np++) {
+                /* matrices: (keys np*16.., dims ks*16..), (same keys, dims +8), (keys +8, dims), (keys +8, dims +8) */
+                const uint32_t off = fa_off(np * 16 + (mat >> 1) * 8 + mr, ks * 2 + (mat & 1));
+                uint32_t bh[4], bl[4];
+                fa_ldsm(bh, sKh + off);
+                fa_ldsm(bl, sKl + off);
+                fa_mma(s[2 * np], qh[ks], bh[0], bh[1]);
+                fa_mma(s[2 * np], qh[ks], bl[0], bl[1]);
+                fa_mma(s[2 * np], ql[ks], bh[0], bh[1]);
+                fa_mma(s[2 * np + 1], qh[ks], bh[2], bh[3]);
+                fa_mma(s[2 * np + 1], qh[ks], bl[2], bl[3]);
+                fa_mma(s[2 * np + 1], ql[ks], bh[2], bh[3]);
             }
+        }
+        /* causal mask, running maximum and sum (rows A and B of this thread's quad) */
+        float tmA = -1e30f, tmB = -1e30f;
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], 1);
-                sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], 2);
+        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int key = k0 + nt * 8 + 2 * tq + (c & 1);
+                if (key > (c < 2 ? limA : limB)) s[nt][c] = -1e30f;
             }
-            float cm = -1e30f;
+            tmA = fmaxf(tmA, fmaxf(s[nt][0], s[nt][1]));
+            tmB = fmaxf(tmB, fmaxf(s[nt][2], s[nt][3]));
+        }
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+        const float nA = fmaxf(mA, tmA), nB = fmaxf(mB, tmB);
+        const float cA = expf(mA - nA), cB = expf(mB - nB);
+        mA = nA; mB = nB;
+        float sumA = 0.0f, sumB = 0.0f;
+        uint32_t ph[2][4], pl[2][4];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                if (k0 + c + u > limit) sc[u] = -1e30f;
-                cm = fmaxf(cm, sc[u]);
+        for (int nt = 0; nt < 4; nt++) {
+            float p[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int key = k0 + nt * 8 + 2 * tq + (c & 1);
+                p[c] = key > (c < 2 ? limA : limB) ? 0.0f : expf(s[nt][c] - (c < 2 ? nA : nB));
             }
-            const float m_new = fmaxf(mx, cm);
-            const float corr = expf(mx - m_new);
-            float p[8], ps = 0.0f;
+            sumA += p[0] + p[1];
+            sumB += p[2] + p[3];
+            /* accumulator layout of key tile nt -> A fragment of the k-step nt / 2:
+             * even tile: a0 (row A), a1 (row B); odd tile: a2 (row A), a3 (row B) */
+            uint32_t h0, l0, h1, l1;
+            fa_split(p[0], h0, l0); fa_split(p[1], h1, l1);
+            ph[nt >> 1][(nt & 1) * 2] = h0 | (h1 << 16);
+            pl[nt >> 1][(nt & 1) * 2] = l0 | (l1 << 16);
+            fa_split(p[2], h0, l0); fa_split(p[3], h1, l1);
+            ph[nt >> 1][(nt & 1) * 2 + 1] = h0 | (h1 << 16);
+            pl[nt >> 1][(nt & 1) * 2 + 1] = l0 | (l1 << 16);
+        }
+        lA = lA * cA + sumA;
+        lB = lB * cB + sumB;
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                p[u] = k0 + c + u > limit ? 0.0f : expf(sc[u] - m_new);
-                ps += p[u];
-            }
-            den = den * corr + ps;
-            mx = m_new;
+        for (int i = 0; i < 16; i++) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
+        /* O += P . V */
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                float4 acc = make_float4(o[4 * j] * corr, o[4 * j + 1] * corr, o[4 * j + 2] * corr, o[4 * j + 3] * corr);
+        for (int j = 0; j < 2; j++) {
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const float4 vv = Vs[(c + u) * 32 + sl + 4 * j];
-                    acc.x += p[u] * vv.x; acc.y += p[u] * vv.y; acc.z += p[u] * vv.z; acc.w += p[u] * vv.w;
-                }
-                o[4 * j] = acc.x; o[4 * j + 1] = acc.y; o[4 * j + 2] = acc.z; o[4 * j + 3] = acc.w;
+            for (int dp = 0; dp < 8; dp++) {
+                /* matrices: (keys j*16.., dims dp*16..), (keys +8, dims), (keys, dims +8), (keys +8, dims +8) */
+                const uint32_t off = fa_off(j * 16 + (mat & 1) * 8 + mr, dp * 2 + (mat >> 1));
+                uint32_t vh[4], vl[4];
+                fa_ldsm_t(vh, sVh + off);
+                fa_ldsm_t(vl, sVl + off);
+                fa_mma(o[2 * dp], ph[j], vh[0], vh[1]);
+                fa_mma(o[2 * dp], ph[j], vl[0], vl[1]);
+                fa_mma(o[2 * dp], pl[j], vh[0], vh[1]);
+                fa_mma(o[2 * dp + 1], ph[j], vh[2], vh[3]);
+                fa_mma(o[2 * dp + 1], ph[j], vl[2], vl[3]);
+                fa_mma(o[2 * dp + 1], pl[j], vh[2], vh[3]);
             }
         }
     }
-    if (valid) {
-        const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    const float iA = lA > 0.0f ? 1.0f / lA : 0.0f, iB = lB > 0.0f ? 1.0f / lB : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-            *reinterpret_cast<float4 *>(out + (size_t)row * ldo + h * VB200_HEAD_DIM + 4 * (sl + 4 * j)) =
-                make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+    for (int nt = 0; nt < 16; nt++) {
+        const int d = nt * 8 + 2 * tq;
+        if (validA) *reinterpret_cast<float2 *>(out + (size_t)rowA * ldo + h * VB200_HEAD_DIM + d) = make_float2(o[nt][0] * iA, o[nt][1] * iA);
+        if (validB) *reinterpret_cast<float2 *>(out + (size_t)rowB * ldo + h * VB200_HEAD_DIM + d) = make_float2(o[nt][2] * iB, o[nt][3] * iB);
     }
 }
 
@@ -242,7 +344,7 @@ static int prefill_tc(float *x, float *qkv, float *attn, const float *cs, int M,
                                                                             cs + (size_t)r0 * VB200_HEAD_DIM, ck, cv, rows);
         }
         const float *k0 = m.kv_k + (size_t)l * m.kv_max * KVD, *v0 = m.kv_v + (size_t)l * m.kv_max * KVD;
-        pf_attention_kernel<<<dim3((M + kPaRows - 1) / kPaRows, VB200_KV_HEADS), kPaThreads, 0, st>>>(
+        pf_attention_kernel<<<dim3((M + kFaRows - 1) / kFaRows, VB200_KV_HEADS), kFaThreads, 0, st>>>(
             attn, qkv, k0, v0, M, start_pos, QKV, KVD, QD, scale);
         if (l == VB200_DEC_LAYERS - 1) break;   /* only the cache is kept (voxtral_tts_llm.c:281) */
         for (int r0 = 0; r0 < M; r0 += kPfRows) {
