@@ -214,7 +214,7 @@ __global__ void ac_velocity_kernel(float *vel, const float *X6, const float *par
     /* 4 outputs per CTA, 4 warps per output, then a fixed-order sum of the 4 warp partials */
     __shared__ float wsum[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 4 + (warp >> 2), q = warp & 3;
+    const int q = warp & 3;   /* quarter of the row this warp sums; output blockIdx.x * 4 + (warp >> 2) */
     float acc = 0.0f;
 #pragma unroll
     for (int i = 0; i < kWPerLane; i++)
