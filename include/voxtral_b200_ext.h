@@ -124,8 +124,9 @@ int vb200_frame_on_stream_kernel(void);
  * (0, default) or as one launch of the persistent streaming kernel (1; one GPU only). Both give
  * the same results within the summation-order tolerance. "wait_limit_us": the limit of
  * every wait inside the streaming decoder kernel (default about one second); when a wait runs
- * out the call returns -1 and vb200_last_status() names the wait. Returns -1 for an unknown
- * name or value. */
+ * out the call returns -1 and vb200_last_status() names the wait. "codec_block_frames" (64 ..
+ * 2048, default 2048): vb200_codec_decode takes longer utterances block by block (see there).
+ * Returns -1 for an unknown name or value. */
 int vb200_set_option(const char *name, int value);
 
 /* Copy rows [pos0, pos0+n) of one layer's K and V cache to / from the host
@@ -223,7 +224,10 @@ typedef struct {
 /* Needs tts_cuda_init. 0 on success. */
 int vb200_codec_upload(const vb200_codec_weights_t *w);
 /* codes: [n_frames, 37] host ints. Writes n_frames * 1920 samples to samples_out (host) when
- * max_samples allows, stores the count in *n_samples; -1 on any failure (nothing is written). */
+ * max_samples allows, stores the count in *n_samples; -1 on any failure. Any number of frames:
+ * up to 2048 frames (164 s of audio; the reference's generation limit is 2000) go through in one
+ * piece, longer inputs block by block with 32 frames of left context that is decoded again and
+ * dropped - the decoder looks back less than 17 frames, so the result is that of one piece. */
 int vb200_codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples);
 /* Device time of the last vb200_codec_decode in milliseconds (CUDA events around its kernels). */
 float vb200_codec_last_ms(void);

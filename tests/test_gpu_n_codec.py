@@ -115,3 +115,20 @@ def test_frames_decode_independently_of_the_batch_they_come_in(codec_engine):
     short, _ = codec_engine.codec_decode(codes[:9])
     # the output convolution (kernel 7, reflect padding only on the left) never reads ahead
     assert rel_l2(long[:9 * 1920], short) < 1e-5
+
+
+def test_long_utterances_go_block_by_block(codec_engine):
+    """Blocks of 64 frames with 32 frames of re-decoded left context reproduce the one-piece decode
+    (the decoder's look-back is under 17 frames)."""
+    codes = codec_codes(200)
+    whole, _ = codec_engine.codec_decode(codes)
+    try:
+        assert codec_engine.L.vb200_set_option(b"codec_block_frames", 64) == 0
+        parts, _ = codec_engine.codec_decode(codes)
+    finally:
+        assert codec_engine.L.vb200_set_option(b"codec_block_frames", 2048) == 0
+    assert parts.shape == whole.shape
+    # not bit-identical: the split-K counts of the convolution GEMMs follow the row count
+    # (measured 3e-6, the level of the hi + lo operand split)
+    assert rel_l2(parts, whole) < 2e-5
+    assert codec_engine.L.vb200_set_option(b"codec_block_frames", 10) == -1

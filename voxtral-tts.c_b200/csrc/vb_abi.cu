@@ -221,6 +221,7 @@ int vb200_set_option(const char *name, int value) {
         }
         return 0;
     }
+    if (!strcmp(name, "codec_block_frames")) return codec_set_block_frames(value);
     if (!strcmp(name, "wait_limit_us")) {
         if (value < 1) return -1;
         model().wait_cycles = (long long)value * 2000;   /* SM clock, about 2 GHz */

@@ -73,6 +73,7 @@ struct Codec {
     float last_ms = 0.0f;
 };
 Codec g_codec;
+int g_block_frames = 0;   /* frames per decode block; 0: the largest the GEMM takes (an option, survives uploads) */
 
 int c_alloc(void **p, size_t bytes, std::vector<void *> *owner) {
     if (cudaMalloc(p, bytes) != cudaSuccess) {
@@ -580,13 +581,13 @@ int codec_upload(const vb200_codec_weights_t *w) {
     return 0;
 }
 
-int codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples) {
+/* One block of at most kTcMaxRows / 8 frames: the samples of frames [skip, n_frames) go to
+ * samples_out. */
+static int decode_block(const int *codes, int n_frames, int skip, float *samples_out, float *ms) {
     Model &m = model();
     Codec &c = g_codec;
-    if (n_samples) *n_samples = 0;
-    if (!m.inited || !c.ready || !codes || n_frames < 1 || !samples_out) return -1;
-    const long long total = (long long)n_frames * 8 * CPATCH;
-    if (total > max_samples || 8 * n_frames > kTcMaxRows) return -1;
+    if (8 * n_frames > kTcMaxRows || skip < 0 || skip >= n_frames) return -1;
+    const size_t total = (size_t)(n_frames - skip) * 8 * CPATCH;
     if (ensure_buffers(n_frames)) return -1;
     cudaStream_t st = m.st;
     if (cudaMemcpyAsync(c.codes, codes, sizeof(int) * (size_t)n_frames * CCODES, cudaMemcpyHostToDevice, st) != cudaSuccess)
@@ -616,18 +617,55 @@ int codec_decode(const int *codes, int n_frames, float *samples_out, int max_sam
     if (conv_run(c.out_conv, c.aOut, c.x, CD, rows, c.pcm, st)) return -1;
     cudaEventRecord(c.e1, st);
     int status = 0;
-    if (cudaMemcpyAsync(samples_out, c.pcm, sizeof(float) * (size_t)total, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+    if (cudaMemcpyAsync(samples_out, c.pcm + (size_t)skip * 8 * CPATCH, sizeof(float) * total, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
         cudaMemcpyAsync(&status, &m.d_out->status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
         cudaStreamSynchronize(st) != cudaSuccess) {
         cudaGetLastError();
         return -1;
     }
-    cudaEventElapsedTime(&c.last_ms, c.e0, c.e1);
+    float t = 0.0f;
+    cudaEventElapsedTime(&t, c.e0, c.e1);
+    *ms += t;
     m.last_status = status;
     if (status) {
         cudaMemset(&m.d_out->status, 0, sizeof(int));
         return -1;
     }
+    return 0;
+}
+
+
+/* The decoder only looks back: 2 frames in the input convolution, (window - 1) positions per
+ * transformer layer at its stage's rate (2 + 3 + 3.5 + 3.75 frames), one position per transposed
+ * convolution, 6/8 of a frame in the output convolution - under 17 frames in all. An utterance
+ * longer than one block is therefore decoded block by block with 32 frames of left context whose
+ * samples are dropped; what is kept equals the one-piece decode. */
+constexpr int kCodecContext = 32;
+
+int codec_set_block_frames(int frames) {
+    if (frames < 2 * kCodecContext || frames > kTcMaxRows / 8) return -1;
+    g_block_frames = frames;
+    return 0;
+}
+
+int codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples) {
+    Model &m = model();
+    Codec &c = g_codec;
+    if (n_samples) *n_samples = 0;
+    if (!m.inited || !c.ready || !codes || n_frames < 1 || !samples_out) return -1;
+    const long long total = (long long)n_frames * 8 * CPATCH;
+    if (total > max_samples) return -1;
+    const int block = g_block_frames > 0 ? g_block_frames : kTcMaxRows / 8;
+    float ms = 0.0f;
+    int pos = n_frames < block ? n_frames : block;
+    if (decode_block(codes, pos, 0, samples_out, &ms)) return -1;
+    while (pos < n_frames) {
+        const int start = pos - kCodecContext;
+        const int len = n_frames - start < block ? n_frames - start : block;
+        if (decode_block(codes + (size_t)start * CCODES, len, kCodecContext, samples_out + (size_t)pos * 8 * CPATCH, &ms)) return -1;
+        pos = start + len;
+    }
+    c.last_ms = ms;
     if (n_samples) *n_samples = (int)total;
     return 0;
 }

@@ -164,6 +164,7 @@ void codec_free_all();
 int codec_upload(const vb200_codec_weights_t *w);
 int codec_decode(const int *codes, int n_frames, float *samples_out, int max_samples, int *n_samples);
 float codec_last_ms();
+int codec_set_block_frames(int frames);
 
 int utterance_begin(const float *first_embed, int start_pos, const float *noise_all, int n_frames);
 int utterance_run(int n);

@@ -24,7 +24,7 @@ namespace vb {
 constexpr int kTcTileN = 128;     /* weight rows per CTA tile = UMMA M */
 constexpr int kTcBlockK = 64;     /* K elements per pipeline stage: one 128-byte swizzle row */
 constexpr int kTcTerms = 3;       /* BF16 terms per fp32 activation */
-constexpr int kTcMaxRows = 8192;  /* activation rows per launch (row-block kernel) */
+constexpr int kTcMaxRows = 16384;  /* activation rows per launch (row-block kernel) */
 constexpr int kTcMaxSplits = 8;   /* split-K factor limit (partials are summed in fixed order) */
 
 enum TcEpilogue {
