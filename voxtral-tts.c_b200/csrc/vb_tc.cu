@@ -222,11 +222,25 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     const int kb0 = (int)((long long)kblocks * sp / splits), kb1 = (int)((long long)kblocks * (sp + 1) / splits);
     const int n_it = kb1 - kb0;
 
-    if (threadIdx.x == 0) {
+    int first = 0;   /* producer thread only: stages of the first ring-full */
+    if (warp == 4 && lane == 0) {
+        /* The TMA producer sets the barriers up itself and requests the first ring-full of weight
+         * tiles at once - they depend on nothing, neither on the predecessor kernel nor on the
+         * TMEM allocation and the CTA-wide barrier below. */
         for (int i = 0; i < Cfg::kStages; i++) { vb_mbar_init(&full[i], 1); vb_mbar_init(&empty[i], 1); }
         vb_mbar_init(accum, 1);
         *abort_flag = 0;
         vb_mbar_init_fence();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapB) : "memory");
+        first = n_it < Cfg::kStages ? n_it : Cfg::kStages;
+        for (int it = 0; it < first; it++) {
+            unsigned char *sa = stages + (size_t)it * Cfg::kStage;
+            vb_mbar_arrive_expect_tx(&full[it], (uint32_t)Cfg::kStage);
+            if (ka.a_tiled) tma_load_2d(sa, &mapA, 0, (tile * kblocks + kb0 + it) * kTcTileN, &full[it]);
+            else tma_load_2d(sa, &mapA, (kb0 + it) * kTcBlockK, tile * kTcTileN, &full[it]);
+        }
+        issued = first;
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(vb_smem_u32(tmem_slot)),
@@ -241,17 +255,9 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 
     if (warp == 4 && lane == 0) {
         /* ---- TMA producer ----
-         * Weights do not depend on the previous kernel: the first ring-full of weight
-         * tiles is requested at once, then the kernel waits for its predecessor
-         * (griddepcontrol.wait) and only then fetches the activation terms. */
-        const int first = n_it < Cfg::kStages ? n_it : Cfg::kStages;
-        for (int it = 0; it < first; it++) {
-            unsigned char *sa = stages + (size_t)it * Cfg::kStage;
-            vb_mbar_arrive_expect_tx(&full[it], (uint32_t)Cfg::kStage);
-            if (ka.a_tiled) tma_load_2d(sa, &mapA, 0, (tile * kblocks + kb0 + it) * kTcTileN, &full[it]);
-            else tma_load_2d(sa, &mapA, (kb0 + it) * kTcBlockK, tile * kTcTileN, &full[it]);
-        }
-        issued = first;
+         * The weights of the first ring-full are already on their way (above). Now the kernel
+         * waits for its predecessor (griddepcontrol.wait) and only then fetches the activation
+         * terms. */
         pdl_wait();
         if constexpr (TP) {
             if (tp.wait.n > 0) {
