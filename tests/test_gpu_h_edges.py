@@ -2,11 +2,14 @@
 device-resident run, refused positions and sizes, and that a refused call leaves the library
 usable."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
 
 from gpu_common import rel_l2
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 pytestmark = pytest.mark.gpu
 
@@ -104,3 +107,33 @@ def test_long_device_loop_equals_frame_by_frame(pkg, engine, oracle, synth_model
             e = oracle.audio_embed(table, c)
     finally:
         engine.L.vb200_set_option(b"ignore_end", 0)
+
+
+def test_context_can_be_torn_down_and_brought_up_again():
+    """tts_cuda_free followed by tts_cuda_init in one process (a host that reloads its model): every
+    cached copy and buffer of the first context is forgotten, and the second context decodes the same
+    frame. Runs in a child process so that the suite's own context is not disturbed."""
+    import subprocess
+    import sys
+    code = r"""
+import os, sys
+import numpy as np
+sys.path.insert(0, os.path.join(%r, "tests"))
+from conftest import load_package
+pkg = load_package()
+model = pkg.SynthModel(seed=77, dec_layers=2)
+out = []
+for round_ in range(2):
+    eng = pkg.Engine(kv_cache_max=128)
+    eng.upload(model, decoder=True, acoustic=True, audio_table=True)
+    rows = pkg.synth_f32((70, 3072), 9, "reinit.rows", 0.0, 0.5)
+    eng.prefill(rows, 0)
+    noise = pkg.randn(123, 36)[0]
+    codes, hidden = eng.frame(model.token_rows([24])[0], noise, rows.shape[0])
+    out.append((codes.copy(), hidden.copy()))
+    eng.close()
+assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
+print("reinit ok")
+""" % ROOT
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "reinit ok" in r.stdout, (r.stdout[-1500:], r.stderr[-1500:])

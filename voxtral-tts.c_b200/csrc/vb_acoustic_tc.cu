@@ -413,6 +413,12 @@ void acoustic_tc_drop_graphs() {
     }
 }
 
+/* Called when the device context goes away: the tiled copies and buffers were the context's. */
+void acoustic_tc_free_all() {
+    acoustic_tc_drop_graphs();
+    g_ac = AcTc();
+}
+
 int acoustic_tc_enqueue(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end) {
     Model &m = model();
     if (getenv("VB200_NO_GRAPH")) return enqueue_direct(noise_all, codes_all, frame_cap, advance, ignore_end);

@@ -166,7 +166,9 @@ void model_free() {
     if (!m.inited) return;
     cudaDeviceSynchronize();
     batch_free_all();
+    acoustic_tc_free_all();
     codec_free_all();
+    prefill_free_all();
     for (void *p : m.allocs) cudaFree(p);
     m.allocs.clear();
     if (m.h_in) cudaFreeHost(m.h_in);

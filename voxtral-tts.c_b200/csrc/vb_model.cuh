@@ -125,9 +125,11 @@ int linear_device(float *d_y, const float *d_x, const uint16_t *d_W, int M, int 
 int prefill(const float *embeds, int seq_len, int start_pos);
 int prefill_prompt(const int *text_ids, int n_text, const uint16_t *voice_bf16, int n_voice, int start_pos);
 int prefill_tc_setup();
+void prefill_free_all();
 /* tensor-core acoustic path (vb_acoustic_tc.cu) */
 int acoustic_tc_setup();
 bool acoustic_tc_ready();
+void acoustic_tc_free_all();
 int acoustic_tc_enqueue(const float *noise_all, int *codes_all, int frame_cap, bool advance, bool ignore_end);
 
 /* several utterances in lock step (vb_batch.cu) */

@@ -192,7 +192,7 @@ struct TcNoTpArgs {};
 template <bool TP> struct TcTpSel { using type = TcNoTpArgs; };
 template <> struct TcTpSel<true> { using type = TcTpArgs; };
 
-template <int NB, int ST, bool TP, bool STG>
+template <int NB, int ST, bool TP>
 __global__ void __launch_bounds__(kTcThreads, 1)
 vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                   const TcKernelArgs ka, const typename TcTpSel<TP>::type tp) {
@@ -343,11 +343,10 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             *(volatile int *)abort_flag = 1;
         }
         tc_fence_after();
-        const int row = tile * kTcTileN + warp * 32 + lane;
-        /* From four activation rows on, the results leave through shared memory (the pipeline
-         * stages are free once every MMA has completed) as 16-byte stores along the output
-         * columns: one 4-byte store per row straight from the TMEM layout costs ~90 ns each. */
-        constexpr bool staged = STG;     /* a separate instantiation: the one-row launches of the frame keep their lean code */
+        /* The results leave through shared memory (the pipeline stages are free once every MMA has
+         * completed) as 16-byte stores along the output columns. Storing straight from the TMEM
+         * layout - a lane owns one output column, one 4-byte store per activation row - was
+         * measured at ~90 ns per store and 1.5 us per launch even with a single row. */
         float *stg = (float *)stages;                              /* [M][128 output columns] */
         if (ok && n_it > 0) {
 #pragma unroll 1
@@ -368,73 +367,56 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                     const int m = c0 + i;
                     float v = __uint_as_float(r[i]);
                     if (ka.ssq && m < M) v *= rscale[m];
-                    if constexpr (staged) {
-                        if (m < M) stg[m * kTcTileN + warp * 32 + lane] = v;
-                        continue;
-                    }
-                    if (epi == TC_EPI_SWIGLU || epi == TC_EPI_SWIGLU_TERMS) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-                        if (m < M && row < N && (lane & 1) == 0) {
-                            const float res = (v / (1.0f + expf(-v))) * other;
-                            if (epi == TC_EPI_SWIGLU) {
-                                out[(size_t)m * ld_out + (row >> 1)] = res;
-                            } else {
-                                uint16_t t0, t1, t2;
-                                vb_split3(res, t0, t1, t2);
-                                const size_t ko = (size_t)(N >> 1), o = (size_t)m * ko + (row >> 1);
-                                ka.out_terms[o] = t0;
-                                ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = t1;
-                                ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
-                                if constexpr (TP) {
-                                    for (int d = 1; d < tp.push.n_dst; d++) {
-                                        uint16_t *pt = (uint16_t *)((char *)ka.out_terms + tp.push.dst_off[d]);
-                                        pt[o] = t0;
-                                        pt[(size_t)ka.out_rows_pad * ko + o] = t1;
-                                        pt[(size_t)2 * ka.out_rows_pad * ko + o] = t2;
-                                    }
-                                }
-                            }
-                        }
-                    } else if (m < M && row < N) {
-                        if (epi == TC_EPI_STORE) out[(size_t)m * ld_out + row] = v + (bias ? __ldg(bias + row) : 0.0f);
-                        else {
-                            const size_t o = ((size_t)sp * M + m) * ld_out + row;
-                            out[o] = v;
-                            if constexpr (TP) {
-                                for (int d = 1; d < tp.push.n_dst; d++)
-                                    *(float *)((char *)(out + o) + tp.push.dst_off[d]) = v;
-                            }
-                        }
-                    }
+                    if (m < M) stg[m * kTcTileN + warp * 32 + lane] = v;
                 }
             }
-            if constexpr (staged) {
+            {
                 vb_named_bar(1, 128);
                 const int n = tile * kTcTileN + lane * 4;             /* this lane's four output columns */
                 for (int m = warp; m < M; m += 4) {
                     const float4 v = *(const float4 *)(stg + m * kTcTileN + lane * 4);
                     if (epi == TC_EPI_SWIGLU || epi == TC_EPI_SWIGLU_TERMS) {
-                        /* (gate, up, gate, up) -> two results */
+                        /* (gate, up, gate, up) -> two results at columns n / 2 and n / 2 + 1 */
                         const float res[2] = {(v.x / (1.0f + expf(-v.x))) * v.y, (v.z / (1.0f + expf(-v.z))) * v.w};
                         const int col = n >> 1;
                         const size_t ko = (size_t)(N >> 1);
-                        for (int i = 0; i < 2; i++) {
-                            if (n + 2 * i + 1 >= N) break;
+                        if (n + 3 < N && ((ko | (size_t)ld_out) & 1) == 0) {
                             if (epi == TC_EPI_SWIGLU) {
-                                out[(size_t)m * ld_out + col + i] = res[i];
+                                *(float2 *)(out + (size_t)m * ld_out + col) = make_float2(res[0], res[1]);
                             } else {
-                                uint16_t q0, q1, q2;
-                                vb_split3(res[i], q0, q1, q2);
-                                const size_t o = (size_t)m * ko + col + i;
-                                ka.out_terms[o] = q0;
-                                ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = q1;
-                                ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
-                                if constexpr (TP) {
-                                    for (int d = 1; d < tp.push.n_dst; d++) {
-                                        uint16_t *pt = (uint16_t *)((char *)ka.out_terms + tp.push.dst_off[d]);
-                                        pt[o] = q0;
-                                        pt[(size_t)ka.out_rows_pad * ko + o] = q1;
-                                        pt[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
+                                uint16_t q[3][2];
+                                vb_split3(res[0], q[0][0], q[1][0], q[2][0]);
+                                vb_split3(res[1], q[0][1], q[1][1], q[2][1]);
+                                const size_t o = (size_t)m * ko + col;
+#pragma unroll
+                                for (int j = 0; j < 3; j++) {
+                                    const uint32_t pk = q[j][0] | ((uint32_t)q[j][1] << 16);
+                                    *(uint32_t *)(ka.out_terms + (size_t)j * ka.out_rows_pad * ko + o) = pk;
+                                    if constexpr (TP) {
+                                        for (int d = 1; d < tp.push.n_dst; d++)
+                                            *(uint32_t *)((char *)(ka.out_terms + (size_t)j * ka.out_rows_pad * ko + o) + tp.push.dst_off[d]) = pk;
+                                    }
+                                }
+                            }
+                        } else {
+                            for (int i = 0; i < 2; i++) {
+                                if (n + 2 * i + 1 >= N) break;
+                                if (epi == TC_EPI_SWIGLU) {
+                                    out[(size_t)m * ld_out + col + i] = res[i];
+                                } else {
+                                    uint16_t q0, q1, q2;
+                                    vb_split3(res[i], q0, q1, q2);
+                                    const size_t o = (size_t)m * ko + col + i;
+                                    ka.out_terms[o] = q0;
+                                    ka.out_terms[(size_t)ka.out_rows_pad * ko + o] = q1;
+                                    ka.out_terms[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
+                                    if constexpr (TP) {
+                                        for (int d = 1; d < tp.push.n_dst; d++) {
+                                            uint16_t *pt = (uint16_t *)((char *)ka.out_terms + tp.push.dst_off[d]);
+                                            pt[o] = q0;
+                                            pt[(size_t)ka.out_rows_pad * ko + o] = q1;
+                                            pt[(size_t)2 * ka.out_rows_pad * ko + o] = q2;
+                                        }
                                     }
                                 }
                             }
@@ -500,13 +482,13 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     }
 }
 
-template <int NB, int ST, bool TP, bool STG>
+template <int NB, int ST, bool TP>
 static int launch_tc_tp(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, const TcTpArgs &tpa,
                         cudaStream_t st) {
     using Cfg = TcCfg<NB, ST>;
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST, TP, STG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(vb_tc_gemm_kernel<NB, ST, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemBytes) != cudaSuccess) {
             cudaGetLastError();
             return -1;
@@ -516,20 +498,16 @@ static int launch_tc_tp(const TcWeight &w, const TcActs &a, const TcKernelArgs &
     const int tiles = ka.n_tiles_launch;
     typename TcTpSel<TP>::type arg;
     if constexpr (TP) arg = tpa;
-    return launch_pdl(vb_tc_gemm_kernel<NB, ST, TP, STG>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes,
-                      st, w.map, a.map, ka, arg) == cudaSuccess
+    return launch_pdl(vb_tc_gemm_kernel<NB, ST, TP>, dim3(tiles * ka.splits), dim3(kTcThreads), (size_t)Cfg::kSmemBytes, st,
+                      w.map, a.map, ka, arg) == cudaSuccess
                ? 0
                : -1;
 }
 
-/* Launches with four or more activation rows take the instantiation whose results leave
- * through shared memory. */
 template <int NB, int ST>
 static int launch_tc(const TcWeight &w, const TcActs &a, const TcKernelArgs &ka, const TcTpArgs &tpa, cudaStream_t st) {
-    const bool tp = tpa.push.n_dst > 0 || tpa.wait.n > 0;
-    if (ka.M >= 4)
-        return tp ? launch_tc_tp<NB, ST, true, true>(w, a, ka, tpa, st) : launch_tc_tp<NB, ST, false, true>(w, a, ka, tpa, st);
-    return tp ? launch_tc_tp<NB, ST, true, false>(w, a, ka, tpa, st) : launch_tc_tp<NB, ST, false, false>(w, a, ka, tpa, st);
+    if (tpa.push.n_dst > 0 || tpa.wait.n > 0) return launch_tc_tp<NB, ST, true>(w, a, ka, tpa, st);
+    return launch_tc_tp<NB, ST, false>(w, a, ka, tpa, st);
 }
 
 /* ---------------------------------------------------------------- row-block kernel */
