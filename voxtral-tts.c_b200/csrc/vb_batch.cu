@@ -306,17 +306,18 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
             pk[p] = (on && kv) ? __ldcg(row + p * part_stride + QD + g * kHD + tid) : 0.0f;
             pv[p] = (on && kv) ? __ldcg(row + p * part_stride + QD + KVD + g * kHD + tid) : 0.0f;
         }
+        /* the rotation table is worked out while those loads are in flight */
+        if (tid < kHD / 2) {
+            const float freq = 1.0f / powf(theta, (float)(2 * tid) / (float)kHD);
+            const float ang = (float)pos * freq;
+            cs[2 * tid] = cosf(ang);
+            cs[2 * tid + 1] = sinf(ang);
+        }
         float v = 0.0f, kk = 0.0f, vv = 0.0f;
 #pragma unroll
         for (int p = 0; p < kTcMaxSplits; p++) { v += pq[p]; kk += pk[p]; vv += pv[p]; }
         qraw[tid] = v;
         if (kv) { kraw[tid] = kk; vraw[tid] = vv; }
-    }
-    if (tid < kHD / 2) {
-        const float freq = 1.0f / powf(theta, (float)(2 * tid) / (float)kHD);
-        const float ang = (float)pos * freq;
-        cs[2 * tid] = cosf(ang);
-        cs[2 * tid + 1] = sinf(ang);
     }
     __syncthreads();
     const int half = kHD / 2;
