@@ -197,6 +197,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                   const TcKernelArgs ka, const typename TcTpSel<TP>::type tp) {
     using Cfg = TcCfg<NB, ST>;
+    /* the tensor maps are fetched while the first reads of the parameter block are on their way */
+    if (threadIdx.x == 128) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapB) : "memory");
+    }
     const int N = ka.N, K = ka.K, M = ka.M, rows_pad = ka.rows_pad, ld_out = ka.ld_out, splits = ka.splits,
               epi = ka.epi;
     float *const out = ka.out;
@@ -231,8 +236,6 @@ vb_tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         vb_mbar_init(accum, 1);
         *abort_flag = 0;
         vb_mbar_init_fence();
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapA) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapB) : "memory");
         first = n_it < Cfg::kStages ? n_it : Cfg::kStages;
         for (int it = 0; it < first; it++) {
             unsigned char *sa = stages + (size_t)it * Cfg::kStage;
