@@ -819,7 +819,7 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
     case 256:
         /* whole-launch calls on one GPU take the row-block kernel; sliced or exchanged launches
          * (tensor parallelism) do not occur at this size */
-        if (g.n_tiles == 0 && tpa.push.n_dst == 0 && tpa.wait.n == 0 && !getenv("VB200_TC_ROWS_OLD"))
+        if (g.n_tiles == 0 && tpa.push.n_dst == 0 && tpa.wait.n == 0)
             return launch_rows(w, a, ka, st);
         return launch_tc<256, 2>(w, a, ka, tpa, st);
     default:
