@@ -15,7 +15,16 @@ value : frames/s with the whole loop resident on the device (inputs in HBM, no h
 e2e   : the same metric through the host-facing C-ABI call (vb200_frame: host embedding and
         noise in, host hidden state and codes out, every frame) with the re-embedding on the
         host, as the reference's frame loop does (voxtral_tts.c:301-318).
-N > 1 : independent utterances, one per GPU (weak scaling, no data-path collective).
+N > 1 : independent utterances, one per GPU (weak scaling, no data-path collective); the line also
+        carries `tp`, the same utterance decoded by all N GPUs together (tensor-parallel decoder).
+
+Further keys of the line: roofline (the GEMM kernel timed live, and the whole frame), cpu_baseline
+(the reference's CPU code on a bounded sample, with per-configuration timings), gpu_reference (the
+reference's own CUDA backend on the same GPU, in a child process), batched (8 utterances per GPU in
+lock step), streaming_decoder (the decoder step on the persistent streaming kernel), upload (weight
+upload seconds and bytes), codec (the codec decoder on the utterance's codes), utterance (prefill
+and first-frame latency), clocks. `--micro gemv|gemm|stream|prefill` runs one kernel or stage on
+its own (small cases for profiling).
 
 --impl reference times the reference's own CPU code for the same frames (oracle/_ref, the
 unmodified reference sources built with OpenBLAS; or the CPU restatement if that library is
