@@ -23,7 +23,7 @@ Further keys of the line: roofline (the GEMM kernel timed live, and the whole fr
 reference's own CUDA backend on the same GPU, in a child process), batched (8 utterances per GPU in
 lock step), streaming_decoder (the decoder step on the persistent streaming kernel), upload (weight
 upload seconds and bytes), codec (the codec decoder on the utterance's codes), utterance (prefill
-and first-frame latency), clocks. `--micro gemv|gemm|stream|prefill` runs one kernel or stage on
+and first-frame latency), clocks. `--micro gemv|gemm|stream|prefill|codec` runs one kernel or stage on
 its own (small cases for profiling).
 
 --impl reference times the reference's own CPU code for the same frames (oracle/_ref, the
@@ -457,6 +457,26 @@ def micro_prefill(args):
                       "ms_per_call_median": sorted(t)[len(t) // 2]}))
 
 
+def micro_codec(args):
+    """vb200_codec_decode alone on `--m` frames of seeded codes (no decoder upload): `--reps` calls,
+    device and wall time per call. The launch list of the codec decoder is taken from this command."""
+    pkg = load_package()
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from cases import codec_codes
+    eng = pkg.Engine(kv_cache_max=64)
+    eng.codec_upload(pkg.SynthCodec(seed=77))
+    codes = codec_codes(args.m)
+    eng.codec_decode(codes)
+    wall, dev = [], []
+    for _ in range(args.reps):
+        t0 = time.perf_counter()
+        _, ms = eng.codec_decode(codes)
+        wall.append((time.perf_counter() - t0) * 1e3)
+        dev.append(ms)
+    print(json.dumps({"micro": "codec", "frames": args.m, "calls": args.reps, "device_ms_min": min(dev),
+                      "wall_ms_min": min(wall), "audio_s": args.m / 12.5}))
+
+
 def micro(args):
     """One GEMV op of the frame kernel through tts_cuda_linear_bf16 on device buffers:
     y[m,n] = x[m,k] . W[n,k]^T. Not the headline metric: a small, self-contained case for profiling."""
@@ -466,6 +486,8 @@ def micro(args):
         return micro_stream(args)
     if args.micro == "prefill":
         return micro_prefill(args)
+    if args.micro == "codec":
+        return micro_codec(args)
     pkg = load_package()
     eng = pkg.Engine(kv_cache_max=64)
     L = eng.L
@@ -538,7 +560,7 @@ def main():
                     help="--micro gemm: one weight copy (stays in L2 when it fits) instead of rotating copies")
     ap.add_argument("--ops", type=int, default=16, help="--micro stream: GEMV ops per launch")
     ap.add_argument("--no-sync", action="store_true", help="--micro stream: no grid barrier between the ops")
-    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm", "stream", "prefill"],
+    ap.add_argument("--micro", default="", choices=["", "gemv", "gemm", "stream", "prefill", "codec"],
                     help="kernel micro-benchmark instead of the frame loop (reported separately; used for ncu captures)")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--k", type=int, default=3072)
