@@ -1020,6 +1020,12 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
         s_w2 = tc_pick_splits(on * kTcTileN, HID, m.sm_count);
         tp_epoch_kernel<<<1, 1, 0, st>>>(g_tp.epoch);
     }
+    /* Key splits of the decode attention: as many as fit the GPU in one wave. A CTA of this kernel
+     * takes 28 K registers, two fit an SM; beyond that the extra CTAs queue up behind the first
+     * wave (8 utterances x 8 KV heads x 9 splits ran as two waves: 22 us instead of 12 per layer). */
+    int attn_splits = (2 * m.sm_count) / (VB200_KV_HEADS * B);
+    if (attn_splits > kBtKeySplits) attn_splits = kBtKeySplits;
+    if (attn_splits < 1) attn_splits = 1;
     for (int l = 0; l < VB200_DEC_LAYERS; l++) {
         const LayerDev &L = m.dec[l];
         const int NL = VB200_DEC_LAYERS;      /* every exchanged buffer is filled once per layer */
@@ -1041,7 +1047,7 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
                        scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status,
                        tp_wait_for(0, TP_QKV, NL, l + 1, t.status));
         else
-            launch_pdl(bt_attn_kernel<false>, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
+            launch_pdl(bt_attn_kernel<false>, dim3(attn_splits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
                        16, (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn,
                        scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status, TcNoWait());
         g = TcGemm();

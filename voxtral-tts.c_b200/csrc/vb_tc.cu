@@ -126,7 +126,7 @@ int tc_acts(TcActs *a, uint16_t *d_buf, int rows_pad, int K) {
     a->ok = false;
     a->buf = d_buf; a->rows_pad = rows_pad; a->K = K;
     const bool big = rows_pad > 256 && rows_pad <= kTcMaxRows && rows_pad % 128 == 0;
-    if ((rows_pad != 16 && rows_pad != 64 && rows_pad != 256 && !big) || (K % kTcBlockK) != 0) return -1;
+    if ((rows_pad != 16 && rows_pad != 48 && rows_pad != 64 && rows_pad != 256 && !big) || (K % kTcBlockK) != 0) return -1;
     /* (a TMA box holds at most 256 rows: larger buffers only get the row-block kernel's map) */
     if (!big && make_map(&a->map, d_buf, (uint64_t)kTcTerms * rows_pad, (uint64_t)K, (uint32_t)rows_pad)) return -1;
     /* the row-block kernel fetches 128 rows of one term at a time */
@@ -815,6 +815,7 @@ int tc_gemm(const TcWeight &w, const TcActs &a, const TcGemm &g, cudaStream_t st
     tpa.wait.status = g.status;
     switch (a.rows_pad) {
     case 16: return launch_tc<16, 6>(w, a, ka, tpa, st);
+    case 48: return launch_tc<48, 6>(w, a, ka, tpa, st);   /* 8 utterances' acoustic rows: 34 KB stages, six of them */
     case 64: return launch_tc<64, 5>(w, a, ka, tpa, st);
     case 256:
         /* whole-launch calls on one GPU take the row-block kernel; sliced or exchanged launches
