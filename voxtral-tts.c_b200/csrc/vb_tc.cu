@@ -919,6 +919,8 @@ void tc_prepare(const TcActs &acts, const float *x, int ldx, int M, const float 
 /* y[i] = sum over the split-K partials in fixed order (+ bias[i % N]). */
 __global__ void vb_tc_reduce_kernel(float *y, const float *partials, int n_part, size_t stride, size_t count,
                                     const float *bias, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     float v = 0.0f;
@@ -930,7 +932,8 @@ __global__ void vb_tc_reduce_kernel(float *y, const float *partials, int n_part,
 void tc_reduce(float *y, const float *partials, int n_part, size_t stride, size_t count, const float *bias, int N,
                cudaStream_t st) {
     if (count == 0) return;
-    vb_tc_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(y, partials, n_part, stride, count, bias, N);
+    launch_pdl(vb_tc_reduce_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0, st, y, partials, n_part, stride, count,
+               bias, N);
 }
 
 /* ---------------------------------------------------------------- stand-alone probe */
