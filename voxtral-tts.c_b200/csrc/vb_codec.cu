@@ -132,6 +132,8 @@ __global__ void convt_w_kernel(float *dst, const float *src, int ic, int oc, int
 /* emb[t][0..255] = semantic_embedding[code], emb[t][256 + i] = FSQ level -> [-1, 1]
  * (voxtral_tts_codec.c:276-300). grid = frames, 320 threads. */
 __global__ void codec_embed_kernel(float *emb, const int *codes, const float *sem) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, d = threadIdx.x;
     const int *fc = codes + t * CCODES;
     if (d < CSEM) {
@@ -154,6 +156,8 @@ __global__ void codec_embed_kernel(float *emb, const int *codes, const float *se
  * grid = (Kpad / 1024 rounded up, T), 256 threads x 4 columns. */
 __global__ void codec_gather_kernel(uint16_t *buf, int rows_pad, int Kpad, const float *X, int ldx, int T, int Cin,
                                     int taps, int mode, int left_pad) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.y, k = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (k >= Kpad) return;
     float e[4];
@@ -213,6 +217,8 @@ __global__ void split_w_kernel(uint16_t *hi, uint16_t *lo, const float *W, int N
  * grid = (K / 1024, rows), 256 threads x 4 columns; `buf` may be null (residual update only). */
 __global__ void codec_prepare_kernel(uint16_t *buf, int rows_pad, int K, const float *x, const float *y,
                                      const float *yscale, float *x_out, const float *gain, float *ssq) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[8];
     const int m = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     float ss = 0.0f;
@@ -259,6 +265,8 @@ __global__ void codec_prepare_kernel(uint16_t *buf, int rows_pad, int K, const f
 /* QK norm in place: RMSNorm over the whole 1024-wide q row and k row (tts_qk_norm,
  * voxtral_tts_kernels.c:351-355). grid = (rows, 2), 256 threads. */
 __global__ void codec_qknorm_kernel(float *qkv, const float *qw, const float *kw, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[8];
     const float *w = blockIdx.y == 0 ? qw : kw;
     if (!w) return;
@@ -280,6 +288,8 @@ __global__ void codec_qknorm_kernel(float *qkv, const float *qw, const float *kw
  * order with the reference's running-maximum update. */
 __global__ void codec_attention_kernel(float *out, const float *qkv, int rows, int window, float scale,
                                        const float *slopes8) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= rows * CHEADS) return;
     const int i = warp / CHEADS, h = warp % CHEADS;
@@ -412,17 +422,17 @@ int layer_forward(const CodecLayer &L, int rows, const float *y_prev, const floa
     Codec &c = g_codec;
     const float scale = 1.0f / sqrtf((float)CHD);
     /* x (+ the previous layer's FFN update) -> attention-norm terms */
-    codec_prepare_kernel<<<dim3(1, rows), 256, 0, st>>>(c.tD, c.rows_pad, CD, c.x, y_prev, yscale_prev,
+    launch_pdl(codec_prepare_kernel, dim3(1, rows), dim3(256), 0, st, c.tD, c.rows_pad, CD, c.x, y_prev, yscale_prev,
                                                         y_prev ? c.x : nullptr, L.attn_norm, c.ssq);
     if (gemm(L.wqkv, c.aD, rows, TC_EPI_STORE, c.qkv, CQKV, c.ssq, CEPS, nullptr, st)) return -1;
-    if (L.q_norm || L.k_norm) codec_qknorm_kernel<<<dim3(rows, 2), 256, 0, st>>>(c.qkv, L.q_norm, L.k_norm, CQK_EPS);
-    codec_attention_kernel<<<(rows * CHEADS * 32 + 255) / 256, 256, 0, st>>>(c.attn, c.qkv, rows, L.window, scale,
+    if (L.q_norm || L.k_norm) launch_pdl(codec_qknorm_kernel, dim3(rows, 2), dim3(256), 0, st, c.qkv, L.q_norm, L.k_norm, CQK_EPS);
+    launch_pdl(codec_attention_kernel, dim3((rows * CHEADS * 32 + 255) / 256), dim3(256), 0, st, c.attn, c.qkv, rows, L.window, scale,
                                                                             c.d_slopes);
-    codec_prepare_kernel<<<dim3(1, rows), 256, 0, st>>>(c.tD, c.rows_pad, CD, c.attn, nullptr, nullptr, nullptr, nullptr,
+    launch_pdl(codec_prepare_kernel, dim3(1, rows), dim3(256), 0, st, c.tD, c.rows_pad, CD, c.attn, nullptr, nullptr, nullptr, nullptr,
                                                         nullptr);
     if (gemm(L.wo, c.aD, rows, TC_EPI_STORE, c.y, CD, nullptr, 0.0f, nullptr, st)) return -1;
     /* x += proj * attn_scale -> FFN-norm terms */
-    codec_prepare_kernel<<<dim3(1, rows), 256, 0, st>>>(c.tD, c.rows_pad, CD, c.x, c.y, L.attn_scale, c.x, L.ffn_norm,
+    launch_pdl(codec_prepare_kernel, dim3(1, rows), dim3(256), 0, st, c.tD, c.rows_pad, CD, c.x, c.y, L.attn_scale, c.x, L.ffn_norm,
                                                         c.ssq);
     if (gemm(L.w13, c.aD, rows, TC_EPI_SWIGLU_TERMS, nullptr, CH, c.ssq, CEPS, c.tH, st)) return -1;
     if (gemm(L.w2, c.aH, rows, TC_EPI_STORE, c.y, CD, nullptr, 0.0f, nullptr, st)) return -1;
@@ -472,7 +482,7 @@ int conv_setup(Codec::Conv *cv, const vb200_conv_t &w, float *stage, std::vector
  * bias into out [T][N]. */
 int conv_run(const Codec::Conv &cv, const TcActs &acts, const float *X, int ldx, int T, float *out, cudaStream_t st) {
     Codec &c = g_codec;
-    codec_gather_kernel<<<dim3((cv.Kpad + 1023) / 1024, T), 256, 0, st>>>(acts.buf, acts.rows_pad, cv.Kpad, X, ldx, T, cv.Cin,
+    launch_pdl(codec_gather_kernel, dim3((cv.Kpad + 1023) / 1024, T), dim3(256), 0, st, acts.buf, acts.rows_pad, cv.Kpad, X, ldx, T, cv.Cin,
                                                                           cv.taps, cv.mode, cv.left_pad);
     const int pairs = ((cv.N + kTcTileN - 1) / kTcTileN + 1) / 2, blocks = (T + 127) / 128;
     int splits = model().sm_count / (pairs * blocks);
@@ -593,7 +603,7 @@ static int decode_block(const int *codes, int n_frames, int skip, float *samples
     if (cudaMemcpyAsync(c.codes, codes, sizeof(int) * (size_t)n_frames * CCODES, cudaMemcpyHostToDevice, st) != cudaSuccess)
         return -1;
     cudaEventRecord(c.e0, st);
-    codec_embed_kernel<<<n_frames, 320, 0, st>>>(c.emb, c.codes, c.sem);
+    launch_pdl(codec_embed_kernel, dim3(n_frames), dim3(320), 0, st, c.emb, c.codes, c.sem);
     int rows = n_frames;
     if (conv_run(c.in_conv, c.aIn, c.emb, CEMB, rows, c.x, st)) return -1;
     int l = 0;
@@ -605,7 +615,7 @@ static int decode_block(const int *codes, int n_frames, int skip, float *samples
             sc_prev = c.L[l].ffn_scale;
         }
         /* the stage's last FFN update, no terms */
-        codec_prepare_kernel<<<dim3(1, rows), 256, 0, st>>>(nullptr, c.rows_pad, CD, c.x, y_prev, sc_prev, c.x, nullptr,
+        launch_pdl(codec_prepare_kernel, dim3(1, rows), dim3(256), 0, st, nullptr, c.rows_pad, CD, c.x, y_prev, sc_prev, c.x, nullptr,
                                                             nullptr);
         if (stage < CSTAGES - 1) {
             /* [rows][2 x 1024] row-major = [2 rows][1024] */
