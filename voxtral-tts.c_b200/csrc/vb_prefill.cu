@@ -55,6 +55,8 @@ static int run_row_blocks(VbOp proto, int M, int x_ld, int y_ld, bool res_is_y) 
  * pair of columns. */
 __global__ void pf_qkv_finish_kernel(float *qkv, const float *part, int n_part, size_t part_stride, const float *cs,
                                      float *k_rows, float *v_rows, int rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.y;
     const int col = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
     if (col >= QKV || m >= rows) return;
@@ -119,6 +121,8 @@ __global__ void __launch_bounds__(kFaThreads)
 pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc, int M, int start_pos, int ldq,
                     int ldkv, int ldo, float scale) {
     __shared__ __align__(128) unsigned char Kh[kFaKeys * 256], Kl[kFaKeys * 256], Vh[kFaKeys * 256], Vl[kFaKeys * 256];
+    pdl_launch_dependents();
+    pdl_wait();
     const int g = blockIdx.y, r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kFaRows;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
     const int h = g * 4 + warp;
@@ -370,12 +374,12 @@ static int prefill_tc(float *x, float *qkv, float *attn, const float *cs, int M,
             if (tc_gemm(t.wqkv[l], t.aD[slot], g, st)) return -1;
             float *ck = m.kv_k + ((size_t)l * m.kv_max + start_pos + r0) * KVD;
             float *cv = m.kv_v + ((size_t)l * m.kv_max + start_pos + r0) * KVD;
-            pf_qkv_finish_kernel<<<dim3(QKV / 2 / 256, rows), 256, 0, st>>>(qr, t.part, s_qkv, (size_t)rows * QKV,
-                                                                            cs + (size_t)r0 * VB200_HEAD_DIM, ck, cv, rows);
+            launch_pdl(pf_qkv_finish_kernel, dim3(QKV / 2 / 256, rows), dim3(256), 0, st, qr, (const float *)t.part, s_qkv,
+                       (size_t)rows * QKV, cs + (size_t)r0 * VB200_HEAD_DIM, ck, cv, rows);
         }
         const float *k0 = m.kv_k + (size_t)l * m.kv_max * KVD, *v0 = m.kv_v + (size_t)l * m.kv_max * KVD;
-        pf_attention_kernel<<<dim3((M + kFaRows - 1) / kFaRows, VB200_KV_HEADS), kFaThreads, 0, st>>>(
-            attn, qkv, k0, v0, M, start_pos, QKV, KVD, QD, scale);
+        launch_pdl(pf_attention_kernel, dim3((M + kFaRows - 1) / kFaRows, VB200_KV_HEADS), dim3(kFaThreads), 0, st, attn,
+                   (const float *)qkv, k0, v0, M, start_pos, QKV, KVD, QD, scale);
         if (l == VB200_DEC_LAYERS - 1) break;   /* only the cache is kept (voxtral_tts_llm.c:281) */
         for (int r0 = 0; r0 < M; r0 += kPfRows) {
             const int rows = M - r0 < kPfRows ? M - r0 : kPfRows;
