@@ -187,20 +187,22 @@ pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc
         for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
+            /* matrices per ldmatrix: (keys np*16.., dims ks*16..), (same keys, dims +8), (keys +8, dims),
+             * (keys +8, dims +8). The twelve MMAs of a k-step are issued round-robin over the four
+             * accumulators, so that no MMA waits for the one before it. */
+            uint32_t bh[2][4], bl[2][4];
 #pragma unroll
             for (int np = 0; np < 2; np++) {
-                /* matrices: (keys np*16.., dims ks*16..), (same keys, dims +8), (keys +8, dims), (keys +8, dims +8) */
                 const uint32_t off = fa_off(np * 16 + (mat >> 1) * 8 + mr, ks * 2 + (mat & 1));
-                uint32_t bh[4], bl[4];
-                fa_ldsm(bh, sKh + off);
-                fa_ldsm(bl, sKl + off);
-                fa_mma(s[2 * np], qh[ks], bh[0], bh[1]);
-                fa_mma(s[2 * np], qh[ks], bl[0], bl[1]);
-                fa_mma(s[2 * np], ql[ks], bh[0], bh[1]);
-                fa_mma(s[2 * np + 1], qh[ks], bh[2], bh[3]);
-                fa_mma(s[2 * np + 1], qh[ks], bl[2], bl[3]);
-                fa_mma(s[2 * np + 1], ql[ks], bh[2], bh[3]);
+                fa_ldsm(bh[np], sKh + off);
+                fa_ldsm(bl[np], sKl + off);
             }
+#pragma unroll
+            for (int t = 0; t < 4; t++) fa_mma(s[t], qh[ks], bh[t >> 1][(t & 1) * 2], bh[t >> 1][(t & 1) * 2 + 1]);
+#pragma unroll
+            for (int t = 0; t < 4; t++) fa_mma(s[t], qh[ks], bl[t >> 1][(t & 1) * 2], bl[t >> 1][(t & 1) * 2 + 1]);
+#pragma unroll
+            for (int t = 0; t < 4; t++) fa_mma(s[t], ql[ks], bh[t >> 1][(t & 1) * 2], bh[t >> 1][(t & 1) * 2 + 1]);
         }
         /* causal mask, running maximum and sum (rows A and B of this thread's quad) */
         float tmA = -1e30f, tmB = -1e30f;
@@ -247,22 +249,25 @@ pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc
         lB = lB * cB + sumB;
 #pragma unroll
         for (int i = 0; i < 16; i++) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
-        /* O += P . V */
+        /* O += P . V, four dim tiles (two ldmatrix pairs) at a time, MMAs round-robin over them */
 #pragma unroll
         for (int j = 0; j < 2; j++) {
 #pragma unroll
-            for (int dp = 0; dp < 8; dp++) {
-                /* matrices: (keys j*16.., dims dp*16..), (keys +8, dims), (keys, dims +8), (keys +8, dims +8) */
-                const uint32_t off = fa_off(j * 16 + (mat & 1) * 8 + mr, dp * 2 + (mat >> 1));
-                uint32_t vh[4], vl[4];
-                fa_ldsm_t(vh, sVh + off);
-                fa_ldsm_t(vl, sVl + off);
-                fa_mma(o[2 * dp], ph[j], vh[0], vh[1]);
-                fa_mma(o[2 * dp], ph[j], vl[0], vl[1]);
-                fa_mma(o[2 * dp], pl[j], vh[0], vh[1]);
-                fa_mma(o[2 * dp + 1], ph[j], vh[2], vh[3]);
-                fa_mma(o[2 * dp + 1], ph[j], vl[2], vl[3]);
-                fa_mma(o[2 * dp + 1], pl[j], vh[2], vh[3]);
+            for (int dq = 0; dq < 4; dq++) {
+                /* matrices per ldmatrix: (keys j*16.., dims dp*16..), (keys +8, dims), (keys, dims +8), (keys +8, dims +8) */
+                uint32_t vh[2][4], vl[2][4];
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const uint32_t off = fa_off(j * 16 + (mat & 1) * 8 + mr, (2 * dq + e) * 2 + (mat >> 1));
+                    fa_ldsm_t(vh[e], sVh + off);
+                    fa_ldsm_t(vl[e], sVl + off);
+                }
+#pragma unroll
+                for (int t = 0; t < 4; t++) fa_mma(o[4 * dq + t], ph[j], vh[t >> 1][(t & 1) * 2], vh[t >> 1][(t & 1) * 2 + 1]);
+#pragma unroll
+                for (int t = 0; t < 4; t++) fa_mma(o[4 * dq + t], ph[j], vl[t >> 1][(t & 1) * 2], vl[t >> 1][(t & 1) * 2 + 1]);
+#pragma unroll
+                for (int t = 0; t < 4; t++) fa_mma(o[4 * dq + t], pl[j], vh[t >> 1][(t & 1) * 2], vh[t >> 1][(t & 1) * 2 + 1]);
             }
         }
     }
