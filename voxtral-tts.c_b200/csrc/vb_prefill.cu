@@ -79,21 +79,23 @@ __global__ void pf_qkv_finish_kernel(float *qkv, const float *part, int n_part, 
 
 /* Causal attention of a block of prompt rows over the cache prefix (tts_causal_attention,
  * voxtral_tts_kernels.c:403-465) on the warp-level tensor cores; head_dim 128, four query heads
- * per KV head. A CTA owns one KV head and 16 query rows; warp w serves query head 4 g + w, so the
- * K and V rows are staged in shared memory once per KV head, 32 keys at a time.
+ * per KV head. A CTA owns one KV head and 16 query rows; warps w and w + 4 serve query head 4 g + w
+ * on the first and on the second 16 keys of every 32-key tile (two partial softmax states merged at
+ * the end), so the K and V rows are staged in shared memory once per KV head, 32 keys at a time, and
+ * every SM sub-core has two warps' worth of independent MMAs to issue.
  *
  * fp32 accuracy from BF16 MMAs: every fp32 operand is split into hi + lo BF16 halves and a
  * product a.b is taken as a_hi.b_hi + a_hi.b_lo + a_lo.b_hi (the dropped lo.lo term is 2^-16 of
- * the product). Per 32-key tile a warp issues, with mma.sync.m16n8k16:
- *   S[16 x 32]  = Q[16 x 128] . K^T     4 key tiles x 8 k-steps x 3 products
- *   O[16 x 128] += P[16 x 32] . V      16 dim tiles x 2 k-steps x 3 products
+ * the product). Per 32-key tile a warp issues, with mma.sync.m16n8k16, for its 16 keys:
+ *   S[16 x 16]  = Q[16 x 128] . K^T     2 key tiles x 8 k-steps x 3 products
+ *   O[16 x 128] += P[16 x 16] . V      16 dim tiles x 1 k-step x 3 products
  * Q lives in registers as A fragments (scaled by 1/sqrt(128) before the split); K rows [key][dim]
  * are the "column-major" B operand of Q.K^T (ldmatrix), V rows [key][dim] the row-major B operand
  * of P.V (ldmatrix.trans); both sit in shared memory as BF16 with the 16-byte chunks of a row
  * XOR-swizzled by the key index. The running maximum / sum update is the usual one per tile;
  * S's accumulator fragments become P's A fragments without leaving registers. Row blocks are
  * issued heaviest (latest rows) first. */
-constexpr int kFaRows = 16, kFaKeys = 32, kFaThreads = 128;
+constexpr int kFaRows = 16, kFaKeys = 32, kFaThreads = 256;
 
 VB_DEVINL void fa_split(float v, uint32_t &hi, uint32_t &lo) {
     uint16_t a, b, c;
@@ -120,12 +122,15 @@ VB_DEVINL uint32_t fa_off(int key, int chunk) { return (uint32_t)(key * 256 + ((
 __global__ void __launch_bounds__(kFaThreads)
 pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc, int M, int start_pos, int ldq,
                     int ldkv, int ldo, float scale) {
-    __shared__ __align__(128) unsigned char Kh[kFaKeys * 256], Kl[kFaKeys * 256], Vh[kFaKeys * 256], Vl[kFaKeys * 256];
+    __shared__ __align__(128) unsigned char tiles[4 * kFaKeys * 256];   /* K hi, K lo, V hi, V lo; reused by the final merge */
+    __shared__ float ml[4][32][4];                                      /* second half's (mA, mB, lA, lB) per head and lane */
+    unsigned char *Kh = tiles, *Kl = tiles + kFaKeys * 256, *Vh = tiles + 2 * kFaKeys * 256, *Vl = tiles + 3 * kFaKeys * 256;
     pdl_launch_dependents();
     pdl_wait();
     const int g = blockIdx.y, r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kFaRows;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
-    const int h = g * 4 + warp;
+    const int hw = warp & 3, half = warp >> 2;   /* head of the group; which 16 keys of every 32-key tile */
+    const int h = g * 4 + hw;
     const int rowA = r0 + gq, rowB = rowA + 8;
     const bool validA = rowA < M, validB = rowB < M;
     const int limA = validA ? start_pos + rowA : 0, limB = validB ? start_pos + rowB : 0;   /* last key a row sees */
@@ -181,36 +186,31 @@ pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc
         }
         __syncthreads();
 
-        /* S = Q . K^T for 4 tiles of 8 keys */
-        float s[4][4];
+        /* S = Q . K^T for this warp's 2 tiles of 8 keys */
+        float s[2][4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+        for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
-            /* matrices per ldmatrix: (keys np*16.., dims ks*16..), (same keys, dims +8), (keys +8, dims),
-             * (keys +8, dims +8). The twelve MMAs of a k-step are issued round-robin over the four
-             * accumulators, so that no MMA waits for the one before it. */
-            uint32_t bh[2][4], bl[2][4];
-#pragma unroll
-            for (int np = 0; np < 2; np++) {
-                const uint32_t off = fa_off(np * 16 + (mat >> 1) * 8 + mr, ks * 2 + (mat & 1));
-                fa_ldsm(bh[np], sKh + off);
-                fa_ldsm(bl[np], sKl + off);
-            }
-#pragma unroll
-            for (int t = 0; t < 4; t++) fa_mma(s[t], qh[ks], bh[t >> 1][(t & 1) * 2], bh[t >> 1][(t & 1) * 2 + 1]);
-#pragma unroll
-            for (int t = 0; t < 4; t++) fa_mma(s[t], qh[ks], bl[t >> 1][(t & 1) * 2], bl[t >> 1][(t & 1) * 2 + 1]);
-#pragma unroll
-            for (int t = 0; t < 4; t++) fa_mma(s[t], ql[ks], bh[t >> 1][(t & 1) * 2], bh[t >> 1][(t & 1) * 2 + 1]);
+            /* matrices: (keys half*16.., dims ks*16..), (same keys, dims +8), (keys +8, dims), (keys +8, dims +8) */
+            const uint32_t off = fa_off(half * 16 + (mat >> 1) * 8 + mr, ks * 2 + (mat & 1));
+            uint32_t bh[4], bl[4];
+            fa_ldsm(bh, sKh + off);
+            fa_ldsm(bl, sKl + off);
+            fa_mma(s[0], qh[ks], bh[0], bh[1]);
+            fa_mma(s[1], qh[ks], bh[2], bh[3]);
+            fa_mma(s[0], qh[ks], bl[0], bl[1]);
+            fa_mma(s[1], qh[ks], bl[2], bl[3]);
+            fa_mma(s[0], ql[ks], bh[0], bh[1]);
+            fa_mma(s[1], ql[ks], bh[2], bh[3]);
         }
         /* causal mask, running maximum and sum (rows A and B of this thread's quad) */
         float tmA = -1e30f, tmB = -1e30f;
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
+        for (int nt = 0; nt < 2; nt++) {
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                const int key = k0 + nt * 8 + 2 * tq + (c & 1);
+                const int key = k0 + half * 16 + nt * 8 + 2 * tq + (c & 1);
                 if (key > (c < 2 ? limA : limB)) s[nt][c] = -1e30f;
             }
             tmA = fmaxf(tmA, fmaxf(s[nt][0], s[nt][1]));
@@ -224,57 +224,79 @@ pf_attention_kernel(float *out, const float *q, const float *kc, const float *vc
         const float cA = expf(mA - nA), cB = expf(mB - nB);
         mA = nA; mB = nB;
         float sumA = 0.0f, sumB = 0.0f;
-        uint32_t ph[2][4], pl[2][4];
+        uint32_t ph[4], pl[4];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
+        for (int nt = 0; nt < 2; nt++) {
             float p[4];
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                const int key = k0 + nt * 8 + 2 * tq + (c & 1);
+                const int key = k0 + half * 16 + nt * 8 + 2 * tq + (c & 1);
                 p[c] = key > (c < 2 ? limA : limB) ? 0.0f : expf(s[nt][c] - (c < 2 ? nA : nB));
             }
             sumA += p[0] + p[1];
             sumB += p[2] + p[3];
-            /* accumulator layout of key tile nt -> A fragment of the k-step nt / 2:
-             * even tile: a0 (row A), a1 (row B); odd tile: a2 (row A), a3 (row B) */
+            /* accumulator layout of key tile nt -> A fragment of the one k-step:
+             * first tile: a0 (row A), a1 (row B); second tile: a2 (row A), a3 (row B) */
             uint32_t h0, l0, h1, l1;
             fa_split(p[0], h0, l0); fa_split(p[1], h1, l1);
-            ph[nt >> 1][(nt & 1) * 2] = h0 | (h1 << 16);
-            pl[nt >> 1][(nt & 1) * 2] = l0 | (l1 << 16);
+            ph[nt * 2] = h0 | (h1 << 16);
+            pl[nt * 2] = l0 | (l1 << 16);
             fa_split(p[2], h0, l0); fa_split(p[3], h1, l1);
-            ph[nt >> 1][(nt & 1) * 2 + 1] = h0 | (h1 << 16);
-            pl[nt >> 1][(nt & 1) * 2 + 1] = l0 | (l1 << 16);
+            ph[nt * 2 + 1] = h0 | (h1 << 16);
+            pl[nt * 2 + 1] = l0 | (l1 << 16);
         }
         lA = lA * cA + sumA;
         lB = lB * cB + sumB;
 #pragma unroll
         for (int i = 0; i < 16; i++) { o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB; }
-        /* O += P . V, four dim tiles (two ldmatrix pairs) at a time, MMAs round-robin over them */
+        /* O += P . V over this warp's 16 keys */
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-#pragma unroll
-            for (int dq = 0; dq < 4; dq++) {
-                /* matrices per ldmatrix: (keys j*16.., dims dp*16..), (keys +8, dims), (keys, dims +8), (keys +8, dims +8) */
-                uint32_t vh[2][4], vl[2][4];
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const uint32_t off = fa_off(j * 16 + (mat & 1) * 8 + mr, (2 * dq + e) * 2 + (mat >> 1));
-                    fa_ldsm_t(vh[e], sVh + off);
-                    fa_ldsm_t(vl[e], sVl + off);
-                }
-#pragma unroll
-                for (int t = 0; t < 4; t++) fa_mma(o[4 * dq + t], ph[j], vh[t >> 1][(t & 1) * 2], vh[t >> 1][(t & 1) * 2 + 1]);
-#pragma unroll
-                for (int t = 0; t < 4; t++) fa_mma(o[4 * dq + t], ph[j], vl[t >> 1][(t & 1) * 2], vl[t >> 1][(t & 1) * 2 + 1]);
-#pragma unroll
-                for (int t = 0; t < 4; t++) fa_mma(o[4 * dq + t], pl[j], vh[t >> 1][(t & 1) * 2], vh[t >> 1][(t & 1) * 2 + 1]);
-            }
+        for (int dp = 0; dp < 8; dp++) {
+            /* matrices: (keys half*16.., dims dp*16..), (keys +8, dims), (keys, dims +8), (keys +8, dims +8) */
+            const uint32_t off = fa_off(half * 16 + (mat & 1) * 8 + mr, dp * 2 + (mat >> 1));
+            uint32_t vh[4], vl[4];
+            fa_ldsm_t(vh, sVh + off);
+            fa_ldsm_t(vl, sVl + off);
+            fa_mma(o[2 * dp], ph, vh[0], vh[1]);
+            fa_mma(o[2 * dp + 1], ph, vh[2], vh[3]);
+            fa_mma(o[2 * dp], ph, vl[0], vl[1]);
+            fa_mma(o[2 * dp + 1], ph, vl[2], vl[3]);
+            fa_mma(o[2 * dp], pl, vh[0], vh[1]);
+            fa_mma(o[2 * dp + 1], pl, vh[2], vh[3]);
         }
     }
     lA += __shfl_xor_sync(0xffffffffu, lA, 1);
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    /* merge the two key halves of every head: the second half hands its (max, sum, O) over through
+     * the tile memory, the first half combines them with the usual log-sum-exp weights */
+    __syncthreads();
+    float *xo = reinterpret_cast<float *>(tiles);                 /* [head][64 values][32 lanes] */
+    if (half == 1) {
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) xo[(hw * 64 + i * 4 + c) * 32 + lane] = o[i][c];
+        ml[hw][lane][0] = mA; ml[hw][lane][1] = mB; ml[hw][lane][2] = lA; ml[hw][lane][3] = lB;
+    }
+    __syncthreads();
+    if (half == 1) return;
+    {
+        const float m2A = ml[hw][lane][0], m2B = ml[hw][lane][1], l2A = ml[hw][lane][2], l2B = ml[hw][lane][3];
+        const float MA = fmaxf(mA, m2A), MB = fmaxf(mB, m2B);
+        const float w1A = expf(mA - MA), w2A = l2A > 0.0f ? expf(m2A - MA) : 0.0f;
+        const float w1B = expf(mB - MB), w2B = l2B > 0.0f ? expf(m2B - MB) : 0.0f;
+        lA = lA * w1A + l2A * w2A;
+        lB = lB * w1B + l2B * w2B;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            o[i][0] = o[i][0] * w1A + xo[(hw * 64 + i * 4 + 0) * 32 + lane] * w2A;
+            o[i][1] = o[i][1] * w1A + xo[(hw * 64 + i * 4 + 1) * 32 + lane] * w2A;
+            o[i][2] = o[i][2] * w1B + xo[(hw * 64 + i * 4 + 2) * 32 + lane] * w2B;
+            o[i][3] = o[i][3] * w1B + xo[(hw * 64 + i * 4 + 3) * 32 + lane] * w2B;
+        }
+    }
     const float iA = lA > 0.0f ? 1.0f / lA : 0.0f, iB = lB > 0.0f ? 1.0f / lB : 0.0f;
 #pragma unroll
     for (int nt = 0; nt < 16; nt++) {
