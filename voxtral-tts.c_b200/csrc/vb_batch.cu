@@ -256,7 +256,7 @@ __global__ void bt_embed_kernel(float *X, const uint16_t *table, const int *code
  * four query heads of its KV head on one slice of the keys; the last CTA of a (utterance,
  * KV head) to finish merges the slices in fixed order and writes the result as the three
  * BF16 terms the O projection's GEMM consumes. */
-template <bool TP>
+template <bool TP, int KP>
 __global__ void __launch_bounds__(kBtAttnThreads)
 bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, size_t part_stride, float *kv_k,
                float *kv_v, size_t slab, int layer, const VbDyn *dyn, float scale, float theta, float *scratch,
@@ -278,6 +278,19 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int max_s = gridDim.x, G = gridDim.y;
+    /* The split-K partials of q (and, for the first 128 threads, of the new k and v) are requested
+     * before anything else: they depend on nothing this kernel reads, and the utterance's state
+     * below is a second trip to L2 that now overlaps the first. */
+    const float *row = part + (size_t)b * QKV;
+    const bool kv_lane = tid < kHD;
+    float pq[kTcMaxSplits], pk[kTcMaxSplits], pv[kTcMaxSplits];
+#pragma unroll
+    for (int p = 0; p < kTcMaxSplits; p++) {
+        const bool on = p < n_part;
+        pq[p] = on ? __ldcg(row + p * part_stride + (size_t)g * kGroup * kHD + tid) : 0.0f;
+        pk[p] = (on && kv_lane) ? __ldcg(row + p * part_stride + QD + g * kHD + tid) : 0.0f;
+        pv[p] = (on && kv_lane) ? __ldcg(row + p * part_stride + QD + KVD + g * kHD + tid) : 0.0f;
+    }
     if (dyn[b].done) return;
     const int pos = dyn[b].pos, kv_max = dyn[b].kv_max;
     if (pos < 0 || pos >= kv_max) {
@@ -292,20 +305,11 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     const int j0 = (int)((long long)nk * sp / S), j1 = (int)((long long)nk * (sp + 1) / S);
     float *Kc = kv_k + (size_t)b * slab + (size_t)layer * kv_max * KVD;
     float *Vc = kv_v + (size_t)b * slab + (size_t)layer * kv_max * KVD;
-    const float *row = part + (size_t)b * QKV;
     const bool writer = sp == S - 1;   /* its key range ends with the new token */
 
     {
-        /* split-K sums of q (and of the new k, v) in split order, all loads issued first */
-        const bool kv = writer && tid < kHD;
-        float pq[kTcMaxSplits], pk[kTcMaxSplits], pv[kTcMaxSplits];
-#pragma unroll
-        for (int p = 0; p < kTcMaxSplits; p++) {
-            const bool on = p < n_part;
-            pq[p] = on ? __ldcg(row + p * part_stride + (size_t)g * kGroup * kHD + tid) : 0.0f;
-            pk[p] = (on && kv) ? __ldcg(row + p * part_stride + QD + g * kHD + tid) : 0.0f;
-            pv[p] = (on && kv) ? __ldcg(row + p * part_stride + QD + KVD + g * kHD + tid) : 0.0f;
-        }
+        /* split-K sums in split order */
+        const bool kv = writer && kv_lane;
         /* the rotation table is worked out while those loads are in flight */
         if (tid < kHD / 2) {
             const float freq = 1.0f / powf(theta, (float)(2 * tid) / (float)kHD);
@@ -346,10 +350,11 @@ bt_attn_kernel(uint16_t *terms, int rows_pad, const float *part, int n_part, siz
     const float4 q4 = *reinterpret_cast<const float4 *>(&qs[hh][4 * lane]);
     float mx = -1e30f, den = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    /* four keys per pass: their eight loads are in flight together, the running-maximum update
-     * then takes them in key order as the reference does (eight per pass gained 0.3 % for one
-     * utterance and lost 4 % for eight: registers) */
-    constexpr int kKeysPerPass = 4;
+    /* KP keys per pass: their 2 KP loads are in flight together, the running-maximum update then
+     * takes them in key order as the reference does. Eight for a single utterance (one pass instead
+     * of two at 256+ cached rows; its 80 CTAs have an SM each anyway), four for several (82
+     * registers would leave one CTA per SM and a second wave of CTAs) */
+    constexpr int kKeysPerPass = KP;
     for (int jb = j0 + ss; jb < j1; jb += kKeysPerPass * kBtSubsets) {
         float4 kq[kKeysPerPass], vq[kKeysPerPass];
 #pragma unroll
@@ -1042,12 +1047,16 @@ static int enqueue_frame(Batch &t, int embed_mode, bool advance, const float *no
         if (tp) { g.tile0 = q0; g.n_tiles = qn; g.push = tp_push(0, TP_QKV, NL, l + 1); }
         if (tc_gemm(w.wqkv[l], t.aD, g, st)) return -1;
         if (tp)
-            launch_pdl(bt_attn_kernel<true>, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
+            launch_pdl(bt_attn_kernel<true, 4>, dim3(kBtKeySplits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
                        16, (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn,
                        scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status,
                        tp_wait_for(0, TP_QKV, NL, l + 1, t.status));
+        else if (B == 1)   /* one utterance: one CTA per SM at most, so eight keys per pass cost no occupancy */
+            launch_pdl(bt_attn_kernel<false, 8>, dim3(attn_splits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
+                       16, (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn,
+                       scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status, TcNoWait());
         else
-            launch_pdl(bt_attn_kernel<false>, dim3(attn_splits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
+            launch_pdl(bt_attn_kernel<false, 4>, dim3(attn_splits, VB200_KV_HEADS, B), dim3(kBtAttnThreads), 0, st, t.bQ,
                        16, (const float *)t.part_qkv, s_qkv, psQ, t.kv_k, t.kv_v, t.slab, l, (const VbDyn *)t.dyn,
                        scale, VB200_ROPE_THETA, t.attn_scratch, t.tickets, t.status, TcNoWait());
         g = TcGemm();
