@@ -277,9 +277,7 @@ static int alloc_zero(void **p, size_t bytes, std::vector<void *> *owner) {
 }
 
 int acoustic_buffers_alloc(AcBuffers *b, int B, std::vector<void *> *owner) {
-    /* 17 .. 48 rows (3 .. 8 utterances) take the 48-row tile: its stages are 6 KB smaller than the
-     * 64-row tile's, so a sixth stage fits and the weight stream keeps 96 KB in flight per SM */
-    const int rows = ROWS1 * B, rp = (rows > 16 && rows <= 48) ? 48 : tc_rows_pad(rows);
+    const int rows = ROWS1 * B, rp = tc_rows_pad_frame(rows);
     if (B < 1 || rp == 0) return -1;
     b->B = B; b->rows = rows; b->rows_pad = rp;
     if (alloc_zero((void **)&b->bD, tc_acts_bytes(rp, D), owner) || alloc_zero((void **)&b->bQ, tc_acts_bytes(rp, QD), owner) ||

@@ -110,6 +110,7 @@ size_t tc_tiled_bytes(int N, int K);
 int tc_acts(TcActs *a, uint16_t *d_buf, int rows_pad, int K);
 size_t tc_acts_bytes(int rows_pad, int K);
 int tc_rows_pad(int M);                            /* 16, 64, 256; 0 when M is too large */
+int tc_rows_pad_frame(int M);                      /* 16, 48, 64, 256: the tile of the frame's GEMMs */
 int tc_rows_pad_any(int M);                        /* same, and whole 128-row blocks beyond 256 rows */
 int tc_pick_splits(int N, int K, int n_sm);
 int tc_prepare_chunks(int K);                      /* column chunks (and ssq entries) per row */
